@@ -1,0 +1,149 @@
+/*
+ * muillm_b200 — C ABI of the B200 (sm_100a) decode hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, i.e. a
+ * cudaStream_t / CUstream; NULL = the legacy default stream) and returns a mui_status_t. Nothing
+ * here allocates device memory unless its comment says so; outputs and scratch are caller-owned.
+ * Launches are asynchronous on the given stream. A non-zero status leaves a message that
+ * mui_last_error() returns (thread-local).
+ *
+ * Citations name the file:line of the Epliz/muiLLM interface each entry point stands in for.
+ */
+#ifndef MUILLM_B200_H_
+#define MUILLM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MUI_API __attribute__((visibility("default")))
+
+typedef enum {
+  MUI_OK = 0,
+  MUI_ERR_INVALID_ARG = 1,  /* null pointer, bad size, misaligned pointer */
+  MUI_ERR_UNSUPPORTED = 2,  /* shape/dtype outside what the kernels cover */
+  MUI_ERR_CUDA = 3,         /* a CUDA runtime call failed */
+  MUI_ERR_DEVICE = 4,       /* a kernel recorded a device-side status (timeout of a bounded wait) */
+  MUI_ERR_COMM = 5          /* communicator bootstrap or peer mapping failed */
+} mui_status_t;
+
+/* 16-bit element type of activations, weights and outputs.                              */
+/* Mirrors the fp16/bf16 twin kernels of the reference (csrc/linear/linear.cu:40-70).    */
+typedef enum { MUI_F16 = 0, MUI_BF16 = 1 } mui_dtype_t;
+
+/* Activation applied to the accumulator before biases (csrc/linear/activation.h:4-7).   */
+typedef enum { MUI_ACT_IDENTITY = 0, MUI_ACT_SILU = 1 } mui_activation_t;
+
+/* Weight-only 8-bit formats.
+ *  MUI_W8_SYM_ROW   : int8, symmetric, one fp16/bf16 scale per output row  (w = s[n] * q)
+ *  MUI_W8_GROUP_MIN : uint8, asymmetric, per (row, group) {scale, min} pairs stored [N*G, 2] in the
+ *                     activation dtype (w = q * scale + min) — the layout produced by
+ *                     muillm/quantization/rtnquantizer.py:49-88 and consumed by
+ *                     csrc/int8_linear_kernels.cu:238-249. */
+typedef enum { MUI_W8_SYM_ROW = 0, MUI_W8_GROUP_MIN = 1 } mui_w8_format_t;
+
+/* Launch flags (bit set). */
+#define MUI_FLAG_PDL 1u          /* launch with programmatic stream serialization (overlaps the weight prefetch
+                                    of this kernel with the tail of the previous kernel on the stream) */
+#define MUI_FLAG_FORCE_GENERIC 2u /* use the plain-load kernel even where the bulk-copy pipeline applies */
+#define MUI_FLAG_FORCE_PIPELINE 4u /* fail with MUI_ERR_UNSUPPORTED instead of falling back to the plain-load kernel */
+
+MUI_API const char* mui_status_string(mui_status_t s);
+MUI_API const char* mui_last_error(void);
+MUI_API int mui_version(void);
+
+/* ---- engine: per-device properties (csrc/engine.cpp:3-25, csrc/gpu_info.cpp) -------------------- */
+typedef struct mui_device_props {
+  int device;
+  int sm_count;
+  int cc_major, cc_minor;
+  int smem_per_block_optin;
+  int l2_bytes;
+  size_t total_mem;
+} mui_device_props_t;
+MUI_API mui_status_t mui_device_props(int device, mui_device_props_t* out);
+
+/* Reads (and clears when `clear` != 0) the device status word that kernels set when a bounded wait
+ * ran out. Synchronises the device. *code == 0 means no kernel reported anything. */
+MUI_API mui_status_t mui_device_status(unsigned* code, int clear);
+
+/* ---- (a1) linear / GEMV --------------------------------------------------------------------------
+ * y[b, n] = act( sum_k W[n,k] * xn[b,k] ) * mul_bias[n] + add_bias[n] + residual[b, n]
+ * xn = x                                   when norm_weights == NULL
+ * xn = round16(round16(x * rsqrt(mean(x^2) + eps)) * norm_weights)   otherwise (HF RMSNorm rounding)
+ * W is row-major [N, K]; x [B, K]; y, residual [B, N]; 1 <= B <= 8. fp32 accumulation, one rounding.
+ * Replaces muillm_linear_activ_forward_{fp16,bf16} (csrc/linear/linear.cu:40-70, kernels at
+ * csrc/linear/linear_fp16_kernels.cu:164,359). */
+MUI_API mui_status_t mui_linear_forward(void* stream, mui_dtype_t dtype, int B, int N, int K,
+                                        const void* norm_weights, float epsilon, const void* weights,
+                                        mui_activation_t activ, const void* mul_bias, const void* add_bias,
+                                        const void* residual, const void* x, void* y, unsigned flags);
+
+/* ---- (a4) fused gate/up + SiLU -------------------------------------------------------------------
+ * t[b, i] = silu(sum_k G[i,k] xn[b,k]) * (sum_k U[i,k] xn[b,k]);  G,U row-major [I, H]; x [B,H]; t [B,I].
+ * Replaces muillm_gateupsilu_gemv[_norm_inputs]_{fp16,bf16}_kernel launches
+ * (csrc/ffn/gateup_fp16_kernels.cu:161,345,859-956). */
+MUI_API mui_status_t mui_gateup_silu_forward(void* stream, mui_dtype_t dtype, int B, int I, int H,
+                                             const void* norm_weights, float epsilon, const void* gate_weights,
+                                             const void* up_weights, const void* x, void* t, unsigned flags);
+
+/* Whole MLP: t = gateup_silu(x) into `scratch_t` ([B,I] elements of dtype), then
+ * y = D t + residual with D row-major [H, I]. Replaces muillm_gateupsilu_forward
+ * (csrc/ffn/gateup.cu:176-219). */
+MUI_API mui_status_t mui_gateupdown_forward(void* stream, mui_dtype_t dtype, int B, int I, int H,
+                                            const void* norm_weights, float epsilon, const void* gate_weights,
+                                            const void* up_weights, const void* down_weights, const void* residual,
+                                            const void* x, void* scratch_t, void* y, unsigned flags);
+
+/* ---- (a14) RMSNorm / L2 norm ----------------------------------------------------------------------
+ * y[r,:] = round16(round16(x[r,:] * rsqrt(mean(x[r,:]^2) + eps)) * w) ; w == NULL -> no weight (L2 norm of
+ * Llama-4, csrc/norm/l2norm_fp16_kernels.cu:35). Replaces muillm_rmsnorm_forward (csrc/norm/rmsnorm.cu:31-84). */
+MUI_API mui_status_t mui_rmsnorm_forward(void* stream, mui_dtype_t dtype, int rows, int K, const void* w,
+                                         float epsilon, const void* x, void* y, unsigned flags);
+
+/* ---- (a8) rotary embedding + static-cache write-out ----------------------------------------------
+ * q_out[b,h,t,:] = rope(q_in[b,h,t,:]);  K[b,h,cache_position[t],:] = rope(k_in[b,h,t,:]);
+ * V[b,h,cache_position[t],:] = v_in[b,h,t,:].  rope(x) = x*cos + rotate_half(x)*sin evaluated in fp32 and
+ * rounded once. q/k/v are [B,H*,T,D] views given by element strides (innermost stride 1); caches are
+ * contiguous [B,Hkv,MAX_T,D]; cos/sin tables are [S, D] indexed by position_ids[b,t] (layout 0) or
+ * [B,T,D] indexed by (b,t) (layout 1); position_ids [B,T] and cache_position [T] are int64.
+ * k_cache/v_cache may be NULL (no cache: k_out receives rope(k), contiguous [B,Hkv,T,D]).
+ * Replaces muillm_apply_rope_forward_{fp16,bf16}_static_cache / _no_cache
+ * (csrc/rope/rotary.cu:603-756, csrc/rope/rotary_fp16_kernels.cu:95,575). */
+typedef struct mui_strides3 { int64_t batch, head, tok; } mui_strides3_t;
+MUI_API mui_status_t mui_rope_forward(void* stream, mui_dtype_t dtype, int B, int T, int max_T, int Hq, int Hkv,
+                                      int D, int table_layout, const int64_t* position_ids, const void* cos_table,
+                                      const void* sin_table, const void* q_in, mui_strides3_t q_strides,
+                                      const void* k_in, mui_strides3_t k_strides, const void* v_in,
+                                      mui_strides3_t v_strides, void* q_out, void* k_out, void* k_cache,
+                                      void* v_cache, const int64_t* cache_position, unsigned flags);
+
+/* Static-cache scatter only (csrc/kvcaches/static_kvcache.cpp:35-120). */
+MUI_API mui_status_t mui_static_kvcache_update(void* stream, mui_dtype_t dtype, int B, int T, int max_T, int Hkv,
+                                               int D, const void* k_in, mui_strides3_t k_strides, const void* v_in,
+                                               mui_strides3_t v_strides, void* k_cache, void* v_cache,
+                                               const int64_t* cache_position, unsigned flags);
+
+/* ---- (a10) flash decoding -------------------------------------------------------------------------
+ * out[b, 0, h*D:(h+1)*D] = softmax_s( q[b,h,:]·K[b,h/(Hq/Hkv),s,:] * scale + mask[b,s] ) · V[b,..,s,:]
+ * for one query token. q contiguous [B,Hq,1,D]; K,V given by element strides (batch, head, token;
+ * innermost 1); out contiguous [B,1,Hq*D]. S tokens are attended; when seq_len_dev != NULL the device
+ * int32 it points to replaces S at run time (must be <= S; makes the launch replayable in a CUDA graph).
+ * mask: NULL or additive [B,S] of dtype, a position is kept iff its mask value == 0
+ * (csrc/attention/flash_decoding_fp16_kernels.cu:386-393). Split-KV with fp32 (m, l, acc) partials in
+ * `workspace` (mui_flash_decode_workspace_bytes bytes, 256-byte aligned). The first 4 KiB of the
+ * workspace hold arrival counters that must be zero before the first call; every call leaves them zero.
+ * Replaces flash_decode_no_mask / flash_decode_masked (csrc/attention/flash_decoding.cu:288-325). */
+MUI_API size_t mui_flash_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_S);
+MUI_API mui_status_t mui_flash_decode(void* stream, mui_dtype_t dtype, int B, int Hq, int Hkv, int D, int S,
+                                      const int32_t* seq_len_dev, float scale, const void* q, const void* k,
+                                      const void* v, mui_strides3_t kv_strides, const void* mask, void* out,
+                                      void* workspace, size_t workspace_bytes, unsigned flags);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUILLM_B200_H_ */

@@ -1,0 +1,124 @@
+"""ctypes binding of the C ABI declared in include/muillm_b200.h.
+
+`lib()` loads muillm_b200/lib/libmuillm_b200.so (built by `python -m muillm_b200.build`) and raises if
+it is missing: there is no fallback path. `check()` turns a non-zero mui_status_t into a RuntimeError
+carrying mui_last_error(), which is how the reference surfaces failures (TORCH_CHECK -> RuntimeError,
+csrc/linear/linear.cu:72-74).
+"""
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libmuillm_b200.so")
+
+MUI_OK = 0
+MUI_ERR_INVALID_ARG = 1
+MUI_ERR_UNSUPPORTED = 2
+MUI_ERR_CUDA = 3
+MUI_ERR_DEVICE = 4
+MUI_ERR_COMM = 5
+
+MUI_F16 = 0
+MUI_BF16 = 1
+
+MUI_ACT_IDENTITY = 0
+MUI_ACT_SILU = 1
+
+MUI_W8_SYM_ROW = 0
+MUI_W8_GROUP_MIN = 1
+
+MUI_FLAG_PDL = 1
+MUI_FLAG_FORCE_GENERIC = 2
+MUI_FLAG_FORCE_PIPELINE = 4
+
+
+class Strides3(Structure):
+    _fields_ = [("batch", c_int64), ("head", c_int64), ("tok", c_int64)]
+
+
+class DeviceProps(Structure):
+    _fields_ = [
+        ("device", c_int),
+        ("sm_count", c_int),
+        ("cc_major", c_int),
+        ("cc_minor", c_int),
+        ("smem_per_block_optin", c_int),
+        ("l2_bytes", c_int),
+        ("total_mem", c_size_t),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/muillm_b200.h declares appears here
+PROTOTYPES = {
+    "mui_status_string": (c_char_p, [c_int]),
+    "mui_last_error": (c_char_p, []),
+    "mui_version": (c_int, []),
+    "mui_device_props": (c_int, [c_int, POINTER(DeviceProps)]),
+    "mui_device_status": (c_int, [POINTER(c_uint), c_int]),
+    "mui_linear_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_uint],
+    ),
+    "mui_gateup_silu_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_gateupdown_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_uint],
+    ),
+    "mui_rmsnorm_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_uint]),
+    "mui_rope_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+         Strides3, c_void_p, Strides3, c_void_p, Strides3, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_static_kvcache_update": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, Strides3, c_void_p, Strides3, c_void_p,
+         c_void_p, c_void_p, c_uint],
+    ),
+    "mui_flash_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "mui_flash_decode": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+         Strides3, c_void_p, c_void_p, c_void_p, c_size_t, c_uint],
+    ),
+}
+
+_lib = None
+
+
+def lib():
+    """Returns the loaded library with prototypes applied; raises if the .so is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: build it with `python -m muillm_b200.build` (there is no fallback path)"
+            )
+        l = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(l, name)  # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(status):
+    if status != MUI_OK:
+        l = lib()
+        raise RuntimeError(
+            f"muillm_b200: {l.mui_status_string(status).decode()} — {l.mui_last_error().decode()}"
+        )
+
+
+def device_status(clear=True):
+    """Synchronises and returns the device status word (0 = no kernel reported a timed-out wait)."""
+    code = c_uint(0)
+    check(lib().mui_device_status(ctypes.byref(code), 1 if clear else 0))
+    return code.value

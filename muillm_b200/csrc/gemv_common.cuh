@@ -1,0 +1,212 @@
+// Argument block, activation staging (with the fused RMSNorm) and epilogues shared by the
+// GEMV-shaped kernels (linear, gate/up+SiLU, their weight-only 8-bit and MoE variants).
+#pragma once
+
+#include "common.cuh"
+
+#define GEMV_CONSUMER_THREADS 256
+#define GEMV_CONSUMER_WARPS 8
+
+// MoE addressing of the rows / reduction segments (device-side expert selection).
+#define GEMV_MOE_NONE 0
+#define GEMV_MOE_ROWS 1      // gate/up: output rows span the computed experts, out is [slots, N]
+#define GEMV_MOE_SEGMENTS 2  // down: the reduction runs over the computed experts, out is [N]
+
+struct GemvArgs {
+  const void* W;         // [N,K] (or [E*N, K] for MoE)
+  const void* W2;        // gate/up: the "up" matrix, same shape as W
+  const void* scales;    // 8-bit weights: per-row scales or per-group {scale,min} pairs (of W)
+  const void* scales2;   // 8-bit gate/up SYM_ROW: scales of W2
+  const void* x;         // [B,K] (MoE segments: [slots, K])
+  const void* norm_w;    // [K] or null
+  const void* mul_bias;  // [N] or null
+  const void* add_bias;  // [N] or null
+  const void* residual;  // [B,N] or null
+  void* y;               // [B,N] 16-bit output (may be null when y_f32 is set)
+  float* y_f32;          // optional fp32 output (tensor-parallel partial sums), same indexing as y
+  const int64_t* router_indices;  // [slots - num_shared] routed expert ids (device)
+  const void* router_scores;      // [slots - num_shared] routed scores, 16-bit (device)
+  float eps;
+  int N;           // output rows per matrix / expert
+  int K;           // reduction length (per segment)
+  int B;           // activation rows actually present (<= NB template)
+  int activ;       // mui_activation_t
+  int Kp;          // smem row stride of the staged activations, K rounded up to 8
+  int moe_mode;    // GEMV_MOE_*
+  int slots;       // computed experts (shared first, then routed), 1 when not MoE
+  int num_shared;  // shared experts among the slots
+  int group_shift; // 8-bit GROUP_MIN: log2(group size)
+};
+
+// expert whose weights serve computed slot `slot`
+__device__ __forceinline__ int gemv_slot_expert(const GemvArgs& a, int slot) {
+  if (slot < a.num_shared) return slot;
+  return a.num_shared + static_cast<int>(a.router_indices[slot - a.num_shared]);
+}
+template <typename T>
+__device__ __forceinline__ float gemv_slot_score(const GemvArgs& a, int slot) {
+  if (slot < a.num_shared) return 1.f;
+  return Elt<T>::to_f32(reinterpret_cast<const T*>(a.router_scores)[slot - a.num_shared]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stage the activations into shared memory as 16-bit values, applying the RMSNorm with the
+// roundings of the HF modules: xn = round16(round16(x * rstd) * w), rstd = rsqrt(mean(x^2) + eps)
+// computed in fp32. Rows b >= a.B (template padding) are zero filled. Called by the 256 consumer
+// threads; synchronises them on named barrier 1. `red` is NBX*8 floats of shared scratch.
+// NBX = number of activation rows staged (batch rows, or MoE segments).
+// ---------------------------------------------------------------------------------------------
+template <typename T, int NBX>
+__device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present, T* x_s, float* red, int tid) {
+  const int K = a.K, Kp = a.Kp;
+  const T* __restrict__ x = reinterpret_cast<const T*>(a.x);
+  const T* __restrict__ nw = reinterpret_cast<const T*>(a.norm_w);
+  const int warp = tid >> 5, lane = tid & 31;
+  const bool vec_ok = ((K & 7) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                      (nw == nullptr || (reinterpret_cast<uintptr_t>(nw) & 15) == 0);
+  float rstd[NBX];
+#pragma unroll
+  for (int b = 0; b < NBX; ++b) rstd[b] = 1.f;
+
+  if (nw != nullptr) {
+    float ss[NBX];
+#pragma unroll
+    for (int b = 0; b < NBX; ++b) ss[b] = 0.f;
+    if (vec_ok) {
+      for (int k = tid * 8; k < K; k += GEMV_CONSUMER_THREADS * 8) {
+#pragma unroll
+        for (int b = 0; b < NBX; ++b) {
+          if (b < rows_present) {
+            float f[8];
+            unpack8<T>(ld_cached16(x + (size_t)b * K + k), f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss[b] = fmaf(f[i], f[i], ss[b]);
+          }
+        }
+      }
+    } else {
+      for (int k = tid; k < K; k += GEMV_CONSUMER_THREADS) {
+#pragma unroll
+        for (int b = 0; b < NBX; ++b) {
+          if (b < rows_present) {
+            float v = Elt<T>::to_f32(x[(size_t)b * K + k]);
+            ss[b] = fmaf(v, v, ss[b]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < NBX; ++b) {
+      float s = warp_sum(ss[b]);
+      if (lane == 0) red[b * GEMV_CONSUMER_WARPS + warp] = s;
+    }
+    named_bar_sync(1, GEMV_CONSUMER_THREADS);
+#pragma unroll
+    for (int b = 0; b < NBX; ++b) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) s += red[b * GEMV_CONSUMER_WARPS + w];
+      rstd[b] = rsqrtf(s / static_cast<float>(K) + a.eps);
+    }
+  }
+
+  if (vec_ok) {
+    for (int k = tid * 8; k < Kp; k += GEMV_CONSUMER_THREADS * 8) {
+      float wv[8];
+      if (nw != nullptr) unpack8<T>(ld_cached16(nw + k), wv);
+#pragma unroll
+      for (int b = 0; b < NBX; ++b) {
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (b < rows_present) {
+          uint4 raw = ld_cached16(x + (size_t)b * K + k);
+          if (nw != nullptr) {
+            float f[8];
+            unpack8<T>(raw, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float n1 = Elt<T>::to_f32(Elt<T>::from_f32(f[i] * rstd[b]));
+              f[i] = n1 * wv[i];
+            }
+            out = pack8<T>(f);
+          } else {
+            out = raw;
+          }
+        }
+        *reinterpret_cast<uint4*>(x_s + (size_t)b * Kp + k) = out;
+      }
+    }
+  } else {
+    for (int k = tid; k < Kp; k += GEMV_CONSUMER_THREADS) {
+#pragma unroll
+      for (int b = 0; b < NBX; ++b) {
+        T out = Elt<T>::from_f32(0.f);
+        if (b < rows_present && k < K) {
+          T raw = x[(size_t)b * K + k];
+          if (nw != nullptr) {
+            float n1 = Elt<T>::to_f32(Elt<T>::from_f32(Elt<T>::to_f32(raw) * rstd[b]));
+            out = Elt<T>::from_f32(n1 * Elt<T>::to_f32(nw[k]));
+          } else {
+            out = raw;
+          }
+        }
+        x_s[(size_t)b * Kp + k] = out;
+      }
+    }
+  }
+  named_bar_sync(1, GEMV_CONSUMER_THREADS);
+}
+
+// Plain staging of `rows` activation rows (no norm): used by the MoE down projection whose
+// reduction runs over `rows` = computed experts. Same synchronisation contract as gemv_stage_x.
+template <typename T>
+__device__ __forceinline__ void gemv_stage_x_plain(const GemvArgs& a, int rows, T* x_s, int tid) {
+  const int K = a.K, Kp = a.Kp;
+  const T* __restrict__ x = reinterpret_cast<const T*>(a.x);
+  const bool vec_ok = ((K & 7) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  if (vec_ok) {
+    const int total = rows * K;  // Kp == K here
+    for (int i = tid * 8; i < total; i += GEMV_CONSUMER_THREADS * 8)
+      *reinterpret_cast<uint4*>(x_s + i) = ld_cached16(x + i);
+  } else {
+    for (int r = 0; r < rows; ++r)
+      for (int k = tid; k < Kp; k += GEMV_CONSUMER_THREADS)
+        x_s[(size_t)r * Kp + k] = (k < K) ? x[(size_t)r * K + k] : Elt<T>::from_f32(0.f);
+  }
+  named_bar_sync(1, GEMV_CONSUMER_THREADS);
+}
+
+// weight row that serves output row r (ROWS: r spans slots) / reduction segment seg (SEGMENTS)
+__device__ __forceinline__ size_t gemv_weight_row(const GemvArgs& a, int r, int seg) {
+  if (a.moe_mode == GEMV_MOE_NONE) return (size_t)r;
+  if (a.moe_mode == GEMV_MOE_ROWS) {
+    const int slot = r / a.N;
+    return (size_t)gemv_slot_expert(a, slot) * a.N + (r - slot * a.N);
+  }
+  return (size_t)gemv_slot_expert(a, seg) * a.N + r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// epilogues (one output element). Order follows csrc/linear/linear_fp16_kernels.cu:337-353:
+// activation, * mul_bias, + add_bias, + residual; rounded once.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int n, float v) {
+  if (a.activ == MUI_ACT_SILU) v = silu_f32(v);
+  if (a.mul_bias) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.mul_bias)[n]);
+  if (a.add_bias) v += Elt<T>::to_f32(reinterpret_cast<const T*>(a.add_bias)[n]);
+  const size_t o = (size_t)b * a.N + n;
+  if (a.residual) v += Elt<T>::to_f32(reinterpret_cast<const T*>(a.residual)[o]);
+  if (a.y_f32) a.y_f32[o] = v;
+  if (a.y) reinterpret_cast<T*>(a.y)[o] = Elt<T>::from_f32(v);
+}
+
+// gate/up: t = silu(s*g) * (s*u); s is the router score of the slot (1 for dense / shared experts),
+// applied before the SiLU as csrc/moeffn/gateupmoe_fp16_kernels.cu:355-360 does.
+template <typename T>
+__device__ __forceinline__ void gemv_store_gateup(const GemvArgs& a, int b, int out_row, int out_rows_total, float g,
+                                                  float u, float score) {
+  g *= score;
+  u *= score;
+  float t = silu_f32(g) * u;
+  reinterpret_cast<T*>(a.y)[(size_t)b * out_rows_total + out_row] = Elt<T>::from_f32(t);
+}

@@ -1,0 +1,206 @@
+"""Tensor-level entry points over the C ABI, named and shaped like the stateless functions of the
+reference's `muillm_ext` module (csrc/module.cpp:177-277): they take torch CUDA tensors, allocate the
+output with torch (device memory and streams are torch's job here) and launch on torch's current stream.
+
+Every function fails loudly when the CUDA library is missing or a tensor is not a contiguous CUDA
+tensor of a supported dtype — there is no eager/PyTorch fallback inside.
+"""
+import math
+
+import torch
+
+from . import capi
+from .capi import Strides3
+
+
+def _dtype_code(t):
+    if t.dtype == torch.float16:
+        return capi.MUI_F16
+    if t.dtype == torch.bfloat16:
+        return capi.MUI_BF16
+    raise RuntimeError(f"Unsupported dtype {t.dtype} (float16 or bfloat16 expected)")
+
+
+def _check_input(t, name):
+    if t is None:
+        return
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _rows(x):
+    """Number of activation rows: everything but the last dimension."""
+    return x.numel() // x.shape[-1] if x.numel() else 0
+
+
+def muillm_linear_forward(engine, x, weights, norm_weights=None, epsilon=0.0, mul_bias=None, add_bias=None,
+                          residual=None, activation=capi.MUI_ACT_IDENTITY, flags=0, out=None):
+    """y = act(W · rmsnorm(x)) * mul_bias + add_bias + residual (csrc/module.cpp:178, csrc/linear/linear.cu:160-207).
+
+    x [..., K] with at most 8 rows, weights [N, K]; returns [..., N]."""
+    for t, n in ((x, "x"), (weights, "weights"), (norm_weights, "norm_weights"), (mul_bias, "mul_bias"),
+                 (add_bias, "add_bias"), (residual, "residual")):
+        _check_input(t, n)
+    N, K = weights.shape
+    if x.shape[-1] != K:
+        raise RuntimeError(f"x last dim {x.shape[-1]} != K {K}")
+    if norm_weights is not None and norm_weights.numel() != K:
+        raise RuntimeError("fused normalization is not supported when sharding on dim 1 (K != NORM_K)")
+    B = _rows(x)
+    y = out if out is not None else torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_linear_forward(
+        _stream(), _dtype_code(x), B, N, K, _ptr(norm_weights), float(epsilon), _ptr(weights), int(activation),
+        _ptr(mul_bias), _ptr(add_bias), _ptr(residual), _ptr(x), _ptr(y), flags))
+    return y
+
+
+def muillm_gateupsilu_forward(engine, norm_weights, epsilon, gate_weights, up_weights, down_weights, residual, x,
+                              flags=0):
+    """down(silu(gate(xn)) * up(xn)) + residual (csrc/module.cpp:182, csrc/ffn/gateup.cu:176-219)."""
+    for t, n in ((x, "x"), (gate_weights, "gate_weights"), (up_weights, "up_weights"),
+                 (down_weights, "down_weights"), (norm_weights, "norm_weights"), (residual, "residual")):
+        _check_input(t, n)
+    I, H = gate_weights.shape
+    B = _rows(x)
+    t = torch.empty((B, I), dtype=x.dtype, device=x.device)
+    y = torch.empty(x.shape[:-1] + (down_weights.shape[0],), dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_gateupdown_forward(
+        _stream(), _dtype_code(x), B, I, H, _ptr(norm_weights), float(epsilon), _ptr(gate_weights),
+        _ptr(up_weights), _ptr(down_weights), _ptr(residual), _ptr(x), _ptr(t), _ptr(y), flags))
+    return y
+
+
+def gateup_silu(x, gate_weights, up_weights, norm_weights=None, epsilon=0.0, flags=0):
+    """t = silu(G xn) * (U xn) only (the first kernel of the MLP)."""
+    for t, n in ((x, "x"), (gate_weights, "gate_weights"), (up_weights, "up_weights"),
+                 (norm_weights, "norm_weights")):
+        _check_input(t, n)
+    I, H = gate_weights.shape
+    B = _rows(x)
+    out = torch.empty(x.shape[:-1] + (I,), dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_gateup_silu_forward(
+        _stream(), _dtype_code(x), B, I, H, _ptr(norm_weights), float(epsilon), _ptr(gate_weights),
+        _ptr(up_weights), _ptr(x), _ptr(out), flags))
+    return out
+
+
+def muillm_rmsnorm_forward(weights, x, epsilon, flags=0):
+    """RMSNorm over the last dim (csrc/module.cpp:251, csrc/norm/rmsnorm.cu:31-84). weights may be None (L2 norm)."""
+    _check_input(x, "x")
+    _check_input(weights, "weights")
+    K = x.shape[-1]
+    y = torch.empty_like(x)
+    capi.check(capi.lib().mui_rmsnorm_forward(_stream(), _dtype_code(x), _rows(x), K, _ptr(weights), float(epsilon),
+                                              _ptr(x), _ptr(y), flags))
+    return y
+
+
+def _strides3(t):
+    """(batch, head, token) element strides of a [B, H, T, D] view whose innermost stride is 1."""
+    if t.dim() != 4 or t.stride(3) != 1:
+        raise RuntimeError("expected a [B, H, T, D] tensor with innermost stride 1")
+    return Strides3(t.stride(0), t.stride(1), t.stride(2))
+
+
+def muillm_rope_forward_static_cache(position_ids, cos_cached, sin_cached, q_in, k_in, v_in, k_cache, v_cache,
+                                     cache_position, seen_tokens, flags=0):
+    """RoPE on q,k + write of k,v at cache_position; returns (q_out, K[:, :, :seen], V[:, :, :seen])
+    (csrc/rope/rotary.cu:603-756)."""
+    for t, n in ((position_ids, "position_ids"), (cos_cached, "cos_cached"), (sin_cached, "sin_cached"),
+                 (k_cache, "k_cache"), (v_cache, "v_cache"), (cache_position, "cache_position")):
+        _check_input(t, n)
+    B, Hq, T, D = q_in.shape
+    Hkv = k_in.shape[1]
+    max_T = k_cache.shape[2]
+    if cos_cached.dim() == 2:
+        layout = 0
+    elif cos_cached.dim() == 3:
+        layout = 1
+    else:
+        raise RuntimeError("Unknown rotary cache layout")
+    q_out = torch.empty((B, Hq, T, D), dtype=q_in.dtype, device=q_in.device)
+    capi.check(capi.lib().mui_rope_forward(
+        _stream(), _dtype_code(q_in), B, T, max_T, Hq, Hkv, D, layout, _ptr(position_ids), _ptr(cos_cached),
+        _ptr(sin_cached), _ptr(q_in), _strides3(q_in), _ptr(k_in), _strides3(k_in), _ptr(v_in), _strides3(v_in),
+        _ptr(q_out), None, _ptr(k_cache), _ptr(v_cache), _ptr(cache_position), flags))
+    return q_out, k_cache.narrow(2, 0, seen_tokens), v_cache.narrow(2, 0, seen_tokens)
+
+
+def muillm_rope_forward_no_cache(position_ids, cos_cached, sin_cached, q_in, k_in, flags=0):
+    """RoPE on q,k without cache (csrc/rope/rotary.cu:188)."""
+    B, Hq, T, D = q_in.shape
+    Hkv = k_in.shape[1]
+    layout = 0 if cos_cached.dim() == 2 else 1
+    q_out = torch.empty((B, Hq, T, D), dtype=q_in.dtype, device=q_in.device)
+    k_out = torch.empty((B, Hkv, T, D), dtype=k_in.dtype, device=k_in.device)
+    z = Strides3(0, 0, 0)
+    capi.check(capi.lib().mui_rope_forward(
+        _stream(), _dtype_code(q_in), B, T, 0, Hq, Hkv, D, layout, _ptr(position_ids), _ptr(cos_cached),
+        _ptr(sin_cached), _ptr(q_in), _strides3(q_in), _ptr(k_in), _strides3(k_in), None, z, _ptr(q_out),
+        _ptr(k_out), None, None, None, flags))
+    return q_out, k_out
+
+
+def muillm_static_kvcache_update(k_in, v_in, k_cache, v_cache, cache_position, seen_tokens, flags=0):
+    """Scatter of the new k,v rows at cache_position (csrc/kvcaches/static_kvcache.cpp:35-120)."""
+    B, Hkv, T, D = k_in.shape
+    max_T = k_cache.shape[2]
+    capi.check(capi.lib().mui_static_kvcache_update(
+        _stream(), _dtype_code(k_in), B, T, max_T, Hkv, D, _ptr(k_in), _strides3(k_in), _ptr(v_in),
+        _strides3(v_in), _ptr(k_cache), _ptr(v_cache), _ptr(cache_position), flags))
+    return k_cache.narrow(2, 0, seen_tokens), v_cache.narrow(2, 0, seen_tokens)
+
+
+_fd_workspaces = {}
+
+
+def _fd_workspace(device, nbytes):
+    key = (device.index, torch.cuda.current_stream().cuda_stream)
+    ws = _fd_workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _fd_workspaces[key] = ws
+    return ws
+
+
+def _flash_decode(q, k, v, mask, flags=0, seq_len_dev=None, scale=None):
+    _check_input(q, "q")
+    _check_input(mask, "m")
+    B, Hq, T, D = q.shape
+    if T != 1:
+        raise RuntimeError("flash decoding expects exactly one query token (T == 1)")
+    Hkv, S = k.shape[1], k.shape[2]
+    if k.stride() != v.stride():
+        raise RuntimeError("k and v must have the same strides")
+    if mask is not None:
+        mask = mask.reshape(B, S)
+    out = torch.empty((B, 1, Hq * D), dtype=q.dtype, device=q.device)
+    lib = capi.lib()
+    nbytes = lib.mui_flash_decode_workspace_bytes(B, Hq, Hkv, D, S)
+    ws = _fd_workspace(q.device, nbytes)
+    capi.check(lib.mui_flash_decode(
+        _stream(), _dtype_code(q), B, Hq, Hkv, D, S, _ptr(seq_len_dev),
+        float(scale if scale is not None else 1.0 / math.sqrt(D)), _ptr(q), _ptr(k), _ptr(v), _strides3(k),
+        _ptr(mask), _ptr(out), _ptr(ws), ws.numel(), flags))
+    return out
+
+
+def muillm_causal_transformer_decoding_no_mask(q, k, v, flags=0):
+    """softmax(q Kᵀ / sqrt(d)) V for one query token (csrc/module.cpp:276, csrc/attention/flash_decoding.cu:288-305)."""
+    return _flash_decode(q, k, v, None, flags)
+
+
+def muillm_causal_transformer_decoding_masked(q, k, v, m, flags=0):
+    """Same with an additive [B,1,1,S] mask; positions whose mask value is 0 are kept
+    (csrc/module.cpp:277, csrc/attention/flash_decoding.cu:307-325)."""
+    return _flash_decode(q, k, v, m, flags)

@@ -1,0 +1,152 @@
+"""GPU parity of the GEMV-shaped kernels (linear, gate/up+SiLU, MLP) against the CPU oracle, through the C ABI.
+
+Tolerance is the one the north star states for 16-bit outputs: 1e-2 relative / 1e-3 absolute.
+"""
+import pytest
+import torch
+
+from muillm_b200 import capi, ops
+from oracle import decode_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-2, 1e-3
+DTYPES = [torch.float16, torch.bfloat16]
+PATHS = {"auto": 0, "generic": capi.MUI_FLAG_FORCE_GENERIC, "pdl": capi.MUI_FLAG_PDL}
+
+
+def _gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def _close(got, want):
+    got, want = got.float().cpu(), want.float()
+    assert got.shape == want.shape
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, want, rtol=RTOL, atol=ATOL)
+
+
+def _mk(shape, g, std, dtype):
+    return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("path", list(PATHS))
+@pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 14336), (37, 1000), (33, 77), (16, 4096), (1, 8), (300, 520)])
+def test_linear_fused_norm(dtype, path, N, K):
+    """Config-1 style: y = W · rmsnorm(x), seeded N(0,1) activations, N(0,0.02) weights, norm 1+N(0,0.01)."""
+    g = _gen(0)
+    x = torch.randn(1, K, generator=g).to(dtype)
+    nw = (1 + 0.01 * torch.randn(K, generator=g)).to(dtype)
+    W = _mk((N, K), g, 0.02, dtype)
+    want = oracle.linear(x, W, norm_weights=nw, eps=1e-5)
+    got = ops.muillm_linear_forward(None, x.cuda(), W.cuda(), norm_weights=nw.cuda(), epsilon=1e-5, flags=PATHS[path])
+    _close(got, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("path", ["auto", "generic"])
+@pytest.mark.parametrize("B", [1, 2, 3, 4, 5, 8])
+def test_linear_batch_epilogue(dtype, path, B):
+    """Small batches with every epilogue term: SiLU, mul_bias, add_bias, residual."""
+    N, K = 515, 1024
+    g = _gen(B)
+    x = torch.randn(B, K, generator=g).to(dtype)
+    W = _mk((N, K), g, 0.03, dtype)
+    mb = (1 + 0.1 * torch.randn(N, generator=g)).to(dtype)
+    ab = _mk((N,), g, 0.5, dtype)
+    res = _mk((B, N), g, 1.0, dtype)
+    for act, name in ((capi.MUI_ACT_IDENTITY, "identity"), (capi.MUI_ACT_SILU, "silu")):
+        want = oracle.linear(x, W, activation=name, mul_bias=mb, add_bias=ab, residual=res)
+        got = ops.muillm_linear_forward(None, x.cuda(), W.cuda(), mul_bias=mb.cuda(), add_bias=ab.cuda(),
+                                        residual=res.cuda(), activation=act, flags=PATHS[path])
+        _close(got, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_misaligned_weights_take_generic_path(dtype):
+    """A weight view that is not 16-byte aligned must still give the right answer (scalar loads)."""
+    N, K = 64, 256
+    g = _gen(3)
+    x = torch.randn(1, K, generator=g).to(dtype)
+    Wbuf = _mk((N * K + 8,), g, 0.05, dtype).cuda()
+    W = Wbuf[1:1 + N * K].view(N, K)
+    assert W.data_ptr() % 16 != 0
+    want = oracle.linear(x, W.cpu())
+    got = ops.muillm_linear_forward(None, x.cuda(), W)
+    _close(got, want)
+    with pytest.raises(RuntimeError):
+        ops.muillm_linear_forward(None, x.cuda(), W, flags=capi.MUI_FLAG_FORCE_PIPELINE)
+
+
+def test_linear_rejects_bad_arguments():
+    x = torch.zeros(9, 64, dtype=torch.float16, device="cuda")
+    W = torch.zeros(8, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError):  # more than 8 rows is not a GEMV
+        ops.muillm_linear_forward(None, x, W)
+    with pytest.raises(RuntimeError):  # fp32 is not a supported dtype
+        ops.muillm_linear_forward(None, x[:1].float(), W.float())
+    with pytest.raises(RuntimeError):  # non-contiguous input
+        ops.muillm_linear_forward(None, x[:1, ::2], W[:, :32].contiguous())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("path", list(PATHS))
+@pytest.mark.parametrize("I,H,B", [(14336, 4096, 1), (1000, 512, 1), (77, 40, 2), (2048, 1024, 4), (520, 4096, 8)])
+def test_gateup_silu(dtype, path, I, H, B):
+    g = _gen(I + B)
+    x = torch.randn(B, H, generator=g).to(dtype)
+    nw = (1 + 0.01 * torch.randn(H, generator=g)).to(dtype)
+    G = _mk((I, H), g, 0.02, dtype)
+    U = _mk((I, H), g, 0.02, dtype)
+    want = oracle.gateup_silu(x, G, U, norm_weights=nw, eps=1e-5)
+    got = ops.gateup_silu(x.cuda(), G.cuda(), U.cuda(), norm_weights=nw.cuda(), epsilon=1e-5, flags=PATHS[path])
+    _close(got, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B", [1, 2, 4, 8])
+def test_mlp_llama3_8b_shape(dtype, B):
+    """Gate/up+SiLU then down with residual at the Llama-3-8B MLP shape (hidden 4096, intermediate 14336)."""
+    H, I = 4096, 14336
+    g = _gen(7)
+    x = torch.randn(B, H, generator=g).to(dtype)
+    nw = (1 + 0.01 * torch.randn(H, generator=g)).to(dtype)
+    G = _mk((I, H), g, 0.02, dtype)
+    U = _mk((I, H), g, 0.02, dtype)
+    Dw = _mk((H, I), g, 0.02, dtype)
+    want = oracle.mlp(x, G, U, Dw, norm_weights=nw, eps=1e-5, residual=x)
+    xc = x.cuda()
+    got = ops.muillm_gateupsilu_forward(None, nw.cuda(), 1e-5, G.cuda(), U.cuda(), Dw.cuda(), xc, xc)
+    _close(got, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_is_deterministic(dtype):
+    """Same inputs, same bits: no atomics or arrival-order dependent sums on the path."""
+    g = _gen(11)
+    x = torch.randn(1, 4096, generator=g).to(dtype).cuda()
+    W = _mk((6144, 4096), g, 0.02, dtype).cuda()
+    a = ops.muillm_linear_forward(None, x, W)
+    b = ops.muillm_linear_forward(None, x, W)
+    assert torch.equal(a, b)
+    c = ops.muillm_linear_forward(None, x, W, flags=capi.MUI_FLAG_FORCE_GENERIC)
+    _close(c, a.cpu())
+
+
+def test_linear_full_size_linearity():
+    """Size-independent property at the lm_head shape (128256 x 4096): W(x1 + x2) == W x1 + W x2 within rounding."""
+    dtype = torch.float16
+    g = _gen(5)
+    N, K = 128256, 4096
+    W = (torch.randn(N, K, generator=g, dtype=torch.float32) * 0.02).to(dtype).cuda()
+    x1 = torch.randn(1, K, generator=g).to(dtype).cuda()
+    x2 = torch.randn(1, K, generator=g).to(dtype).cuda()
+    y1 = ops.muillm_linear_forward(None, x1, W).float()
+    y2 = ops.muillm_linear_forward(None, x2, W).float()
+    y12 = ops.muillm_linear_forward(None, (x1.float() + x2.float()).to(dtype), W).float()
+    torch.testing.assert_close(y12, y1 + y2, rtol=2e-2, atol=2e-2)
+    # spot-check 64 seeded rows against the oracle
+    rows = torch.randint(0, N, (64,), generator=g)
+    want = oracle.linear(x1.cpu(), W[rows.cuda()].cpu())
+    _close(y1[:, rows.cuda()].to(dtype), want)
