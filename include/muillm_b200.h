@@ -143,6 +143,73 @@ MUI_API mui_status_t mui_flash_decode(void* stream, mui_dtype_t dtype, int B, in
                                       const void* v, mui_strides3_t kv_strides, const void* mask, void* out,
                                       void* workspace, size_t workspace_bytes, unsigned flags);
 
+/* ---- embedding row gather (csrc/embedding/embedding_xx16_kernels.cu:26,74) ------------------------
+ * out[i, :] = table[token_ids[i], :] for 16-bit tables [vocab, H]; token ids are int64 on the device and
+ * are clamped to [0, vocab). */
+MUI_API mui_status_t mui_embedding_forward(void* stream, mui_dtype_t dtype, int num_tokens, int H, int vocab,
+                                           const void* table, const int64_t* token_ids, void* out, unsigned flags);
+
+/* ---- decode stack ----------------------------------------------------------------------------------
+ * One call launches every kernel of a decode step of a Llama-architecture model for `batch` sequences:
+ * embedding, per layer {fused-norm QKV GEMV, RoPE + static-cache write, flash decoding, o_proj + residual,
+ * fused-norm gate/up + SiLU, down + residual}, final-norm lm_head GEMV, greedy arg-max. The step's token,
+ * position ids, cache position and attended length live in device memory and are advanced by the step
+ * itself, so consecutive steps need no host round trip and a step can be captured once in a CUDA graph
+ * and replayed. The reference has this level for tensor-parallel runs only
+ * (MuiLLMParallelDecoderStack::forward, csrc/modules/parallel_decoder_stack.cpp:22-45); its single-GPU
+ * decode returns to Python between layers (muillm/modules/decoder/decoder.py:95-165).
+ * All device memory is caller-owned: weights, per-layer KV caches [batch, kv_heads, max_seq, head_dim],
+ * cos/sin tables [max_seq, head_dim] and one scratch block of mui_llama_stack_scratch_bytes() bytes
+ * (256-byte aligned). create/destroy only manage a small host object (and the captured graph). */
+typedef struct mui_llama_config {
+  mui_dtype_t dtype;
+  int layers, hidden, intermediate, heads, kv_heads, head_dim, vocab;
+  int max_seq;      /* static KV-cache length */
+  int batch;        /* 1..8 sequences decoded together */
+  float rms_eps;
+  float attn_scale; /* softmax scale, normally 1/sqrt(head_dim) */
+} mui_llama_config_t;
+
+typedef struct mui_llama_weights {
+  const void* embed;            /* [vocab, hidden] */
+  const void* final_norm;       /* [hidden] */
+  const void* lm_head;          /* [vocab, hidden] */
+  const void* cos_table;        /* [max_seq, head_dim] */
+  const void* sin_table;        /* [max_seq, head_dim] */
+  const void* const* qkv;       /* per layer [(heads + 2*kv_heads)*head_dim, hidden]: q rows, then k, then v */
+  const void* const* o;         /* per layer [hidden, heads*head_dim] */
+  const void* const* gate;      /* per layer [intermediate, hidden] */
+  const void* const* up;        /* per layer [intermediate, hidden] */
+  const void* const* down;      /* per layer [hidden, intermediate] */
+  const void* const* ln1;       /* per layer input RMSNorm weight [hidden] */
+  const void* const* ln2;       /* per layer post-attention RMSNorm weight [hidden] */
+  void* const* k_cache;         /* per layer [batch, kv_heads, max_seq, head_dim] */
+  void* const* v_cache;
+} mui_llama_weights_t;
+
+typedef struct mui_llama_stack mui_llama_stack_t;
+
+MUI_API size_t mui_llama_stack_scratch_bytes(const mui_llama_config_t* cfg);
+MUI_API mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_llama_weights_t* weights,
+                                            void* scratch, size_t scratch_bytes, mui_llama_stack_t** out);
+MUI_API mui_status_t mui_llama_stack_destroy(mui_llama_stack_t* stack);
+/* Sets the device-side state: `position` tokens are already in the cache (the next step writes row `position`),
+ * per-sequence RoPE positions (host array of `batch` int64, NULL = position for all), and the device buffer
+ * [out_capacity, batch] int64 that receives each step's arg-max token (may be NULL). Drops a captured graph. */
+MUI_API mui_status_t mui_llama_stack_reset(mui_llama_stack_t* stack, void* stream, int position,
+                                           const int64_t* position_ids_host, int64_t* out_tokens_dev,
+                                           int out_capacity);
+/* Token ids (int64, `batch` of them) fed to the next step; host or device pointer. */
+MUI_API mui_status_t mui_llama_stack_set_tokens(mui_llama_stack_t* stack, void* stream, const int64_t* tokens,
+                                                int on_device);
+MUI_API mui_status_t mui_llama_stack_step(mui_llama_stack_t* stack, void* stream, unsigned flags);
+/* Captures one step on `stream` (must not be the default stream) into a graph; replay launches it `steps` times. */
+MUI_API mui_status_t mui_llama_stack_capture(mui_llama_stack_t* stack, void* stream, unsigned flags);
+MUI_API mui_status_t mui_llama_stack_replay(mui_llama_stack_t* stack, void* stream, int steps);
+/* Device pointers of the last step's logits [batch, vocab] (dtype) and of the int64 state words
+ * {step, tokens in cache, cache position, position_ids[batch], next tokens[batch]}. */
+MUI_API mui_status_t mui_llama_stack_logits(mui_llama_stack_t* stack, void** logits_dev, int64_t** state_dev);
+
 #ifdef __cplusplus
 }
 #endif

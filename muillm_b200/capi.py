@@ -49,6 +49,28 @@ class DeviceProps(Structure):
     ]
 
 
+class LlamaConfig(Structure):
+    _fields_ = [
+        ("dtype", c_int),
+        ("layers", c_int), ("hidden", c_int), ("intermediate", c_int), ("heads", c_int), ("kv_heads", c_int),
+        ("head_dim", c_int), ("vocab", c_int),
+        ("max_seq", c_int),
+        ("batch", c_int),
+        ("rms_eps", c_float),
+        ("attn_scale", c_float),
+    ]
+
+
+class LlamaWeights(Structure):
+    _fields_ = [
+        ("embed", c_void_p), ("final_norm", c_void_p), ("lm_head", c_void_p),
+        ("cos_table", c_void_p), ("sin_table", c_void_p),
+        ("qkv", POINTER(c_void_p)), ("o", POINTER(c_void_p)), ("gate", POINTER(c_void_p)),
+        ("up", POINTER(c_void_p)), ("down", POINTER(c_void_p)), ("ln1", POINTER(c_void_p)),
+        ("ln2", POINTER(c_void_p)), ("k_cache", POINTER(c_void_p)), ("v_cache", POINTER(c_void_p)),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/muillm_b200.h declares appears here
 PROTOTYPES = {
     "mui_status_string": (c_char_p, [c_int]),
@@ -87,6 +109,17 @@ PROTOTYPES = {
         [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
          Strides3, c_void_p, c_void_p, c_void_p, c_size_t, c_uint],
     ),
+    "mui_embedding_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint]),
+    "mui_llama_stack_scratch_bytes": (c_size_t, [POINTER(LlamaConfig)]),
+    "mui_llama_stack_create": (
+        c_int, [POINTER(LlamaConfig), POINTER(LlamaWeights), c_void_p, c_size_t, POINTER(c_void_p)]),
+    "mui_llama_stack_destroy": (c_int, [c_void_p]),
+    "mui_llama_stack_reset": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), c_void_p, c_int]),
+    "mui_llama_stack_set_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "mui_llama_stack_step": (c_int, [c_void_p, c_void_p, c_uint]),
+    "mui_llama_stack_capture": (c_int, [c_void_p, c_void_p, c_uint]),
+    "mui_llama_stack_replay": (c_int, [c_void_p, c_void_p, c_int]),
+    "mui_llama_stack_logits": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p)]),
 }
 
 _lib = None

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
   const int G = a.G;
 
   int S = a.S;
-  if (a.seq_len_dev != nullptr) S = min(S, max(0, *a.seq_len_dev));
+  if (a.seq_len_dev != nullptr) S = min(S, max(0, __ldcg(a.seq_len_dev)));
   int chunk = (S + (int)gridDim.x - 1) / (int)gridDim.x;
   chunk = max(FD_CHUNK_ALIGN, (chunk + FD_CHUNK_ALIGN - 1) / FD_CHUNK_ALIGN * FD_CHUNK_ALIGN);
   const int n_active = max(1, (S + chunk - 1) / chunk);
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
   for (int g = 0; g < GP; ++g) {
     if (g < G) {
       const T* qp = reinterpret_cast<const T*>(a.q) + ((size_t)b * a.Hq + (size_t)kvh * G + g) * D + d0;
-      unpack8<T>(ld_cached16(qp), qf[g]);
+      unpack8<T>(ld_act16(qp), qf[g]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) qf[g][i] *= a.scale_log2;
     } else {
@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
     for (int u = 0; u < U; ++u) {
       const int t = t0 + u * FD_WARPS * TPW + sub;
       valid[u] = t < t_end;
-      if (valid[u] && mrow != nullptr) valid[u] = (Elt<T>::to_f32(mrow[t]) == 0.f);
+      if (valid[u] && mrow != nullptr) valid[u] = (ld_act_f32<T>(mrow + t) == 0.f);
       if (valid[u]) {
         kraw[u] = __ldcg(reinterpret_cast<const uint4*>(kbase + (size_t)t * a.kvs.tok));
         vraw[u] = __ldcg(reinterpret_cast<const uint4*>(vbase + (size_t)t * a.kvs.tok));

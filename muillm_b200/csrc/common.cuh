@@ -132,9 +132,26 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
                : "l"(p));
   return v;
 }
-// 16-byte load that may be served from L1/L2 (activations, KV rows that get re-read)
+// 16-byte load through the read-only path: ONLY for data that no kernel ever writes while this one may be
+// resident (weights, norm weights, rotary tables). Under programmatic dependent launch a kernel is resident
+// before its predecessor has written the activations, so those must not take this path.
 __device__ __forceinline__ uint4 ld_cached16(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
+}
+// Loads of activations and device-side state produced by earlier kernels: served from L2 (the coherence
+// point), never from a possibly stale L1 / read-only cache line.
+__device__ __forceinline__ uint4 ld_act16(const void* p) {
+  return __ldcg(reinterpret_cast<const uint4*>(p));
+}
+template <typename T>
+__device__ __forceinline__ float ld_act_f32(const T* p) {
+  const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(p));
+  return Elt<T>::to_f32(*reinterpret_cast<const T*>(&raw));
+}
+template <typename T>
+__device__ __forceinline__ T ld_act(const T* p) {
+  const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(p));
+  return *reinterpret_cast<const T*>(&raw);
 }
 // 16-byte load with system-scope relaxed semantics (peer memory, never from a stale L1 line)
 __device__ __forceinline__ uint4 ld_sys16(const void* p) {

@@ -18,8 +18,30 @@
 #include "gemv_common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 MUI_STATUS_ACCESSOR(gemv)
+
+// Tuning knobs of the pipeline kernel, read once from the environment (for benchmarking only):
+//   MUI_PIPE_KC      row-chunk length in elements: 2048 (default) or 1024
+//   MUI_PIPE_CTAS    CTAs per SM the grid is sized for: 1 (default) or 2
+//   MUI_PIPE_SMEM_KB shared-memory budget per CTA in KiB (default 222)
+static int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return (e && *e) ? atoi(e) : dflt;
+}
+static int mui_pipe_kc() {
+  static int v = env_int("MUI_PIPE_KC", 2048);
+  return v;
+}
+static int mui_pipe_ctas() {
+  static int v = env_int("MUI_PIPE_CTAS", 1);
+  return v;
+}
+static int mui_pipe_smem_kb() {
+  static int v = env_int("MUI_PIPE_SMEM_KB", 222);
+  return v;
+}
 
 namespace {
 
@@ -40,9 +62,9 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
   const int nseg = (a.moe_mode == GEMV_MOE_SEGMENTS) ? a.slots : 1;
   const int total_rows = (a.moe_mode == GEMV_MOE_ROWS) ? a.slots * a.N : a.N;
   if (a.moe_mode == GEMV_MOE_SEGMENTS)
-    gemv_stage_x_plain<T>(a, a.slots, x_s, tid);
+    gemv_stage_x_plain<T>(a, a.slots, x_s, a.Kp, tid);
   else
-    gemv_stage_x<T, NB>(a, a.B, x_s, red, tid);
+    gemv_stage_x<T, NB>(a, a.B, x_s, a.Kp, red, tid);
 
   const int K = a.K, Kp = a.Kp;
   const T* __restrict__ W = reinterpret_cast<const T*>(a.W);
@@ -128,37 +150,74 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
 // =============================================================================================
 // bulk-copy pipeline kernel
 // =============================================================================================
-constexpr int PIPE_KC = 512;                                // elements per row chunk
-constexpr int PIPE_SLOTS = 16;                              // row chunks per stage (8 warps x 2 streams)
-constexpr int PIPE_STAGE_BYTES = PIPE_SLOTS * PIPE_KC * 2;  // 16 KiB
+// A stage holds one 16-row tile: 16 row chunks of KC elements (one bulk copy each; the copy engine's
+// per-copy cost makes copies below ~4 KiB the limiter, so KC is 2048 elements by default), each row padded
+// by 16 bytes so that ldmatrix reads of 8 rows x 16 bytes hit distinct banks. MODE 0: 16 consecutive output
+// rows. MODE 1: 8 gate rows (tile rows 0-7) and the 8 matching up rows (tile rows 8-15). The eight consumer
+// warps split the chunk's K range in steps of 16 and feed mma.sync m16n8k16 (A = weight tile from shared
+// memory, B = the staged activations, batch along n, fp32 accumulators) — no per-element conversions, so a
+// stage costs each consumer warp a few dozen instructions; at the end of a row block the warps' partial
+// tiles are summed through shared memory in a fixed order.
+constexpr int PIPE_ROWS = 16;
 constexpr int PIPE_THREADS = GEMV_CONSUMER_THREADS + 32;
 constexpr int PIPE_MAX_STAGES = 8;
+constexpr int PIPE_XPAD = 8;  // elements of padding per staged activation row (bank spread for ldmatrix)
+
+template <int KC> struct PipeGeom {
+  static constexpr int ROW_PITCH = KC * 2 + 16;               // bytes
+  static constexpr int STAGE_BYTES = PIPE_ROWS * ROW_PITCH;   // bytes
+};
 
 struct PipeLayout {
-  int stages;
-  int x_off;      // activations
+  int x_off;      // activations [x_rows][Kp + PIPE_XPAD]
   int bar_off;    // full[stages], empty[stages]
-  int red_off;    // floats
+  int red_off;    // floats: stage_x scratch, then 2 x [8 warps][16 rows][NB] partial tiles
   int abort_off;  // int
   int total;
 };
-__host__ __device__ inline PipeLayout pipe_layout(int stages, int x_rows, int Kp, int nb) {
+__host__ __device__ inline PipeLayout pipe_layout(int stage_bytes, int stages, int x_rows, int Kp, int nb) {
   PipeLayout l;
-  l.stages = stages;
-  l.x_off = stages * PIPE_STAGE_BYTES;
-  int x_bytes = ((x_rows * Kp * 2) + 15) & ~15;
+  l.x_off = stages * stage_bytes;
+  int x_bytes = ((x_rows * (Kp + PIPE_XPAD) * 2) + 15) & ~15;
   l.bar_off = l.x_off + x_bytes;
   l.red_off = l.bar_off + 2 * stages * 8;
-  l.abort_off = l.red_off + nb * GEMV_CONSUMER_WARPS * 4;
+  l.abort_off = l.red_off + 2 * GEMV_CONSUMER_WARPS * PIPE_ROWS * nb * 4;
   l.total = l.abort_off + 16;
   return l;
 }
 
-template <typename T, int NB, int MODE>
+template <typename T> struct MmaOp;
+template <> struct MmaOp<__half> {
+  static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+template <> struct MmaOp<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_addr));
+}
+
+template <typename T, int NB, int MODE, int KC>
 __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs a, const int num_stages) {
+  using G = PipeGeom<KC>;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int x_rows = (a.moe_mode == GEMV_MOE_SEGMENTS) ? a.slots : NB;
-  const PipeLayout lay = pipe_layout(num_stages, x_rows, a.Kp, NB);
+  const PipeLayout lay = pipe_layout(G::STAGE_BYTES, num_stages, x_rows, a.Kp, NB);
   unsigned char* stage_mem = smem_raw;
   T* x_s = reinterpret_cast<T*>(smem_raw + lay.x_off);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_raw + lay.bar_off);
@@ -179,14 +238,15 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
   __syncthreads();
   pdl_launch_dependents();
 
-  constexpr int ROWS_PER_STAGE = (MODE == 0) ? 16 : 8;
+  constexpr int ROWS_PER_STAGE = (MODE == 0) ? 16 : 8;  // output rows per stage
   const int K = a.K, Kp = a.Kp;
+  const int x_pitch = Kp + PIPE_XPAD;
   const int nseg = (a.moe_mode == GEMV_MOE_SEGMENTS) ? a.slots : 1;
   const int total_rows = (a.moe_mode == GEMV_MOE_ROWS) ? a.slots * a.N : a.N;
   const int r_begin = static_cast<int>((long long)total_rows * blockIdx.x / gridDim.x);
   const int r_end = static_cast<int>((long long)total_rows * (blockIdx.x + 1) / gridDim.x);
   const int nblk = (r_end - r_begin + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
-  const int nchunks = (K + PIPE_KC - 1) / PIPE_KC;
+  const int nchunks = (K + KC - 1) / KC;
   const int cpb = nseg * nchunks;  // stage items per row block
   const int total_items = nblk * cpb;
 
@@ -198,6 +258,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
     const T* __restrict__ W2 = reinterpret_cast<const T*>(a.W2);
     int issued = 0;
     bool ok = true;
+    int blk = 0, c = 0;  // item -> (row block, chunk) without divisions
     for (int it = 0; it < total_items; ++it) {
       const int s = it % num_stages;
       const uint32_t ph = (it / num_stages) & 1;
@@ -212,27 +273,29 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
         ok = false;
         break;
       }
-      const int blk = it / cpb, c = it - blk * cpb;
       const int seg = c / nchunks, kc = c - seg * nchunks;
       const int rb = r_begin + blk * ROWS_PER_STAGE;
-      const int kc_len = min(PIPE_KC, K - kc * PIPE_KC);
+      const int kc_len = min(KC, K - kc * KC);
       const uint32_t bytes = static_cast<uint32_t>(kc_len) * 2u;
       const int rows_valid = min(ROWS_PER_STAGE, r_end - rb);
       const int ncopies = (MODE == 0) ? rows_valid : 2 * rows_valid;
       if (lane == 0) mbar_arrive_expect_tx(full_bar + s, static_cast<uint32_t>(ncopies) * bytes);
       __syncwarp();
-      if (lane < PIPE_SLOTS) {
-        const int j = lane & 1, w = lane >> 1;
-        const int row = (MODE == 0) ? rb + lane : rb + w;
-        const bool valid = (MODE == 0) ? (lane < rows_valid) : (w < rows_valid);
-        if (valid) {
-          const T* src = ((MODE == 1 && j == 1) ? W2 : W) + gemv_weight_row(a, row, seg) * (size_t)K +
-                         (size_t)kc * PIPE_KC;
-          bulk_load_1d(stage_mem + (size_t)s * PIPE_STAGE_BYTES + (size_t)lane * (PIPE_KC * 2), src, bytes,
+      if (lane < PIPE_ROWS) {
+        // tile row `lane`: MODE 0 -> output row rb + lane; MODE 1 -> gate (lane < 8) / up (lane >= 8) row rb + lane%8
+        const int orow = (MODE == 0) ? lane : (lane & 7);
+        if (orow < rows_valid) {
+          const T* src = ((MODE == 1 && lane >= 8) ? W2 : W) + gemv_weight_row(a, rb + orow, seg) * (size_t)K +
+                         (size_t)kc * KC;
+          bulk_load_1d(stage_mem + (size_t)s * G::STAGE_BYTES + (size_t)lane * G::ROW_PITCH, src, bytes,
                        full_bar + s, policy);
         }
       }
       issued = it + 1;
+      if (++c == cpb) {
+        c = 0;
+        ++blk;
+      }
     }
     if (!ok && lane == 0) {
       // leave no copy in flight behind: wait (bounded) for every stage that was armed
@@ -247,14 +310,22 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
     // ------------------------------ consumer warps ------------------------------
     pdl_wait_prior_grid();
     if (a.moe_mode == GEMV_MOE_SEGMENTS)
-      gemv_stage_x_plain<T>(a, a.slots, x_s, tid);
+      gemv_stage_x_plain<T>(a, a.slots, x_s, x_pitch, tid);
     else
-      gemv_stage_x<T, NB>(a, a.B, x_s, red, tid);
+      gemv_stage_x<T, NB>(a, a.B, x_s, x_pitch, red, tid);
 
-    float acc[2][NB];
-#pragma unroll
-    for (int b = 0; b < NB; ++b) acc[0][b] = acc[1][b] = 0.f;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    // ldmatrix sources. A (weight tile, 16 rows x 16 k): lane gives tile row (lane%8) + 8*((lane/8)%2), k offset
+    // 8*(lane/16). B (activations, 16 k x 8 batch): lanes 0-15 give staged row min(lane%8, NB-1) (columns past
+    // the batch repeat the last row; their results are never read), k offset 8*((lane/8)%2).
+    const uint32_t a_lane_off = static_cast<uint32_t>(((lane & 7) + ((lane >> 3) & 1) * 8) * G::ROW_PITCH +
+                                                      (lane >> 4) * 16);
+    const int b_row = ((lane & 7) < NB) ? (lane & 7) : (NB - 1);
+    const uint32_t b_lane_off = static_cast<uint32_t>((b_row * x_pitch + ((lane >> 3) & 1) * 8) * 2);
+    const uint32_t stage_base = smem_u32(stage_mem);
+    const uint32_t x_base = smem_u32(x_s);
 
+    int blk = 0, c = 0;
     for (int it = 0; it < total_items; ++it) {
       const int s = it % num_stages;
       const uint32_t ph = (it / num_stages) & 1;
@@ -265,60 +336,62 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
         }
         break;
       }
-      const int blk = it / cpb, c = it - blk * cpb;
       const int seg = c / nchunks, kc = c - seg * nchunks;
-      const int rb = r_begin + blk * ROWS_PER_STAGE;
-      const int kc_len = min(PIPE_KC, K - kc * PIPE_KC);
-      const int row0 = (MODE == 0) ? rb + warp * 2 : rb + warp;
-      const bool valid0 = row0 < r_end;
-      const bool valid1 = (MODE == 0) ? (row0 + 1 < r_end) : valid0;
-
-      if (valid0) {
-        const T* ws0 = reinterpret_cast<const T*>(stage_mem + (size_t)s * PIPE_STAGE_BYTES) +
-                       (size_t)(warp * 2) * PIPE_KC;
-        const T* ws1 = ws0 + PIPE_KC;
-        const T* xs = x_s + (size_t)seg * Kp + (size_t)kc * PIPE_KC;
-#pragma unroll
-        for (int k = lane * 8; k < PIPE_KC; k += 256) {
-          if (k < kc_len) {
-            const uint4 v0 = *reinterpret_cast<const uint4*>(ws0 + k);
-            const uint4 v1 = valid1 ? *reinterpret_cast<const uint4*>(ws1 + k) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-              float f[8];
-              unpack8<T>(*reinterpret_cast<const uint4*>(xs + (size_t)b * Kp + k), f);
-              acc[0][b] = dot8<T>(v0, f, acc[0][b]);
-              acc[1][b] = dot8<T>(v1, f, acc[1][b]);
-            }
-          }
-        }
+      const int kc_len = min(KC, K - kc * KC);
+      const int nsteps = kc_len >> 4;
+      const uint32_t a_addr = stage_base + static_cast<uint32_t>(s) * G::STAGE_BYTES + a_lane_off;
+      // MoE segments: segment `seg` multiplies activation row `seg` (NB == 1 there)
+      const uint32_t b_addr = x_base + b_lane_off + static_cast<uint32_t>((seg * x_pitch + kc * KC) * 2);
+#pragma unroll 4
+      for (int j = warp; j < nsteps; j += GEMV_CONSUMER_WARPS) {
+        uint32_t af[4], b0, b1;
+        ldmatrix_x4(af, a_addr + j * 32);
+        ldmatrix_x2(b0, b1, b_addr + j * 32);
+        MmaOp<T>::run(d, af, b0, b1);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar + s);
 
-      if (c == cpb - 1) {
-        // rows of this block are complete: finish them inside the warp
-        if (MODE == 0) {
+      if (++c == cpb) {
+        // row block complete: sum the eight warps' partial tiles in a fixed order, then the epilogue
+        c = 0;
+        const int rb = r_begin + blk * ROWS_PER_STAGE;
+        float* rbuf = red + (blk & 1) * (GEMV_CONSUMER_WARPS * PIPE_ROWS * NB);
+        // this thread holds D[tile row lane/4 (+8)][batch (lane%4)*2 + {0,1}]
+        const int trow = lane >> 2, n0 = (lane & 3) * 2;
+        if (n0 < NB) {
+          rbuf[(warp * PIPE_ROWS + trow) * NB + n0] = d[0];
+          rbuf[(warp * PIPE_ROWS + trow + 8) * NB + n0] = d[2];
+        }
+        if (n0 + 1 < NB) {
+          rbuf[(warp * PIPE_ROWS + trow) * NB + n0 + 1] = d[1];
+          rbuf[(warp * PIPE_ROWS + trow + 8) * NB + n0 + 1] = d[3];
+        }
+        d[0] = d[1] = d[2] = d[3] = 0.f;
+        named_bar_sync(1, GEMV_CONSUMER_THREADS);
+        if (tid < ROWS_PER_STAGE * NB) {
+          const int r = tid / NB, b = tid - r * NB;
+          const int row = rb + r;
+          if (row < r_end && b < a.B) {
+            if (MODE == 0) {
+              float v = 0.f;
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
+              for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) v += rbuf[(w * PIPE_ROWS + r) * NB + b];
+              gemv_store_linear<T>(a, b, row, v);
+            } else {
+              float g = 0.f, u = 0.f;
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-              const float v = warp_sum(acc[j][b]);
-              const bool valid = (j == 0) ? valid0 : valid1;
-              if (lane == j * NB + b && valid && b < a.B) gemv_store_linear<T>(a, b, row0 + j, v);
+              for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) {
+                g += rbuf[(w * PIPE_ROWS + r) * NB + b];
+                u += rbuf[(w * PIPE_ROWS + r + 8) * NB + b];
+              }
+              float score = 1.f;
+              if (a.moe_mode == GEMV_MOE_ROWS) score = gemv_slot_score<T>(a, row / a.N);
+              gemv_store_gateup<T>(a, b, row, total_rows, g, u, score);
             }
-        } else {
-          float score = 1.f;
-          if (a.moe_mode == GEMV_MOE_ROWS && valid0) score = gemv_slot_score<T>(a, row0 / a.N);
-#pragma unroll
-          for (int b = 0; b < NB; ++b) {
-            const float g = warp_sum(acc[0][b]);
-            const float u = warp_sum(acc[1][b]);
-            if (lane == b && valid0 && b < a.B) gemv_store_gateup<T>(a, b, row0, total_rows, g, u, score);
           }
         }
-#pragma unroll
-        for (int b = 0; b < NB; ++b) acc[0][b] = acc[1][b] = 0.f;
+        ++blk;
       }
     }
   }
@@ -327,6 +400,41 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
 // =============================================================================================
 // host dispatch
 // =============================================================================================
+template <typename T, int NB, int MODE, int KC>
+mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int total_rows, int x_rows,
+                         const MuiDeviceInfo* dev, bool* applicable) {
+  using G = PipeGeom<KC>;
+  // One CTA per SM with (nearly) all of its shared memory: ~190 KiB of copies in flight per SM is what keeps
+  // HBM busy; with half of that the kernel runs ~25 % slower.
+  const int budget_small = std::min(mui_pipe_smem_kb(), 222) * 1024, budget_full = 222 * 1024;
+  const int fixed = pipe_layout(G::STAGE_BYTES, 0, x_rows, a.Kp, NB).total;
+  int ctas_per_sm = std::max(1, std::min(2, mui_pipe_ctas()));
+  int stages = (budget_small - fixed) / G::STAGE_BYTES;
+  if (stages < 2) {
+    ctas_per_sm = 1;
+    stages = (budget_full - fixed) / G::STAGE_BYTES;
+  }
+  stages = std::min(stages, PIPE_MAX_STAGES);
+  if (stages < 2) {
+    *applicable = false;
+    return MUI_OK;
+  }
+  *applicable = true;
+  auto kern = gemv_pipe_kernel<T, NB, MODE, KC>;
+  const PipeLayout lay = pipe_layout(G::STAGE_BYTES, stages, x_rows, a.Kp, NB);
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared));
+    configured = true;
+  }
+  const int units = (total_rows + 7) / 8;  // at least one row block per CTA
+  const int grid = std::max(1, std::min(units, dev->sm_count * ctas_per_sm));
+  MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(PIPE_THREADS), (size_t)lay.total, stream, pdl, a, stages));
+  return MUI_OK;
+}
+
 template <typename T, int NB, int MODE>
 mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flags, const MuiDeviceInfo* dev) {
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
@@ -334,53 +442,38 @@ mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flag
   const int x_rows = (a.moe_mode == GEMV_MOE_SEGMENTS) ? a.slots : NB;
   const size_t x_bytes = (size_t)x_rows * a.Kp * 2;
 
-  const bool aligned = ((a.K & 7) == 0) && ((reinterpret_cast<uintptr_t>(a.W) & 15) == 0) &&
+  // the pipeline needs 16-byte aligned rows for the bulk copies and whole k16 steps for the mma
+  const bool aligned = ((a.K & 15) == 0) && ((reinterpret_cast<uintptr_t>(a.W) & 15) == 0) &&
                        (MODE == 0 || (reinterpret_cast<uintptr_t>(a.W2) & 15) == 0);
   bool use_pipe = aligned && !(flags & MUI_FLAG_FORCE_GENERIC);
-  int stages = 0, ctas_per_sm = 2;
   if (use_pipe) {
-    // two CTAs per SM when the activations are small enough to leave room for >= 3 stages each
-    const int budget2 = 110 * 1024, budget1 = 220 * 1024;
-    const int fixed = pipe_layout(0, x_rows, a.Kp, NB).total;
-    stages = (budget2 - fixed) / PIPE_STAGE_BYTES;
-    if (stages < 3) {
-      ctas_per_sm = 1;
-      stages = (budget1 - fixed) / PIPE_STAGE_BYTES;
+    bool applicable = false;
+    mui_status_t st;
+    const int kc = mui_pipe_kc();
+    if (kc >= 2048) {
+      st = launch_pipe<T, NB, MODE, 2048>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
+      if (st != MUI_OK || applicable) return st;
     }
-    stages = std::min(stages, PIPE_MAX_STAGES);
-    if (stages < 2) use_pipe = false;
+    // smaller stages when the staged activations leave no room for two 64 KiB ones
+    st = launch_pipe<T, NB, MODE, 1024>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
+    if (st != MUI_OK || applicable) return st;
   }
-  if (!use_pipe && (flags & MUI_FLAG_FORCE_PIPELINE)) {
+  if (flags & MUI_FLAG_FORCE_PIPELINE) {
     mui_set_error("bulk-copy pipeline not applicable (K=%d, alignment or activation size)", a.K);
     return MUI_ERR_UNSUPPORTED;
-  }
-
-  if (use_pipe) {
-    auto kern = gemv_pipe_kernel<T, NB, MODE>;
-    const PipeLayout lay = pipe_layout(stages, x_rows, a.Kp, NB);
-    static int configured_smem = 0;  // per instantiation
-    if (lay.total > configured_smem) {
-      MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024));
-      MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                          cudaSharedmemCarveoutMaxShared));
-      configured_smem = 222 * 1024;
-    }
-    const int grid = std::max(1, std::min(total_rows, dev->sm_count * ctas_per_sm));
-    MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(PIPE_THREADS), (size_t)lay.total, stream, pdl, a, stages));
-    return MUI_OK;
   }
 
   // generic
   MUI_REQUIRE(x_bytes <= 200 * 1024, MUI_ERR_UNSUPPORTED,
               "activations (%zu bytes) do not fit the shared-memory staging of the GEMV", x_bytes);
   auto kern = gemv_generic_kernel<T, NB, MODE>;
-  static int configured_smem_g = 0;
-  if ((int)x_bytes > 48 * 1024 && (int)x_bytes > configured_smem_g) {
+  static bool configured_g = false;
+  if (x_bytes > 48 * 1024 && !configured_g) {
     MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    configured_smem_g = 200 * 1024;
+    configured_g = true;
   }
   const int num_items = (MODE == 0) ? (total_rows + 1) / 2 : total_rows;
-  int per_sm = (int)std::min<size_t>(8, (size_t)(224 * 1024) / (x_bytes + 2048));
+  int per_sm = (int)std::min<size_t>(6, (size_t)(224 * 1024) / (x_bytes + 2048));
   per_sm = std::max(per_sm, 1);
   const int grid = std::max(1, std::min(num_items, dev->sm_count * per_sm));
   MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(GEMV_CONSUMER_THREADS), x_bytes, stream, pdl, a));
@@ -404,6 +497,21 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
   const MuiDeviceInfo* dev = mui_current_device_info();
   if (!dev) return MUI_ERR_CUDA;
   const int nb = a.B <= 1 ? 1 : (a.B <= 2 ? 2 : (a.B <= 4 ? 4 : 8));
+  // Activations of all batch rows are staged in shared memory; when they cannot fit (large K with B > 1), run
+  // the batch in two halves (the weights are then streamed twice).
+  if (a.B > 1 && a.moe_mode == GEMV_MOE_NONE && (size_t)nb * (a.Kp + 8) * 2 > 150 * 1024) {
+    const int h = a.B / 2;
+    GemvArgs lo = a, hi = a;
+    lo.B = h;
+    hi.B = a.B - h;
+    hi.x = reinterpret_cast<const unsigned char*>(a.x) + (size_t)h * a.K * 2;
+    if (a.y) hi.y = reinterpret_cast<unsigned char*>(a.y) + (size_t)h * a.N * 2;
+    if (a.y_f32) hi.y_f32 = a.y_f32 + (size_t)h * a.N;
+    if (a.residual) hi.residual = reinterpret_cast<const unsigned char*>(a.residual) + (size_t)h * a.N * 2;
+    mui_status_t st = mui_launch_gemv16(stream, dtype, mode, lo, flags);
+    if (st != MUI_OK) return st;
+    return mui_launch_gemv16(stream, dtype, mode, hi, flags);
+  }
   if (dtype == MUI_F16) {
     return mode == 0 ? launch_gemv_nb<__half, 0>(stream, a, nb, flags, dev)
                      : launch_gemv_nb<__half, 1>(stream, a, nb, flags, dev);

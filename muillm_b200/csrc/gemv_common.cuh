@@ -41,23 +41,25 @@ struct GemvArgs {
 // expert whose weights serve computed slot `slot`
 __device__ __forceinline__ int gemv_slot_expert(const GemvArgs& a, int slot) {
   if (slot < a.num_shared) return slot;
-  return a.num_shared + static_cast<int>(a.router_indices[slot - a.num_shared]);
+  return a.num_shared + static_cast<int>(__ldcg(a.router_indices + (slot - a.num_shared)));
 }
 template <typename T>
 __device__ __forceinline__ float gemv_slot_score(const GemvArgs& a, int slot) {
   if (slot < a.num_shared) return 1.f;
-  return Elt<T>::to_f32(reinterpret_cast<const T*>(a.router_scores)[slot - a.num_shared]);
+  return ld_act_f32<T>(reinterpret_cast<const T*>(a.router_scores) + (slot - a.num_shared));
 }
 
 // ---------------------------------------------------------------------------------------------
 // Stage the activations into shared memory as 16-bit values, applying the RMSNorm with the
 // roundings of the HF modules: xn = round16(round16(x * rstd) * w), rstd = rsqrt(mean(x^2) + eps)
 // computed in fp32. Rows b >= a.B (template padding) are zero filled. Called by the 256 consumer
-// threads; synchronises them on named barrier 1. `red` is NBX*8 floats of shared scratch.
+// threads; synchronises them on named barrier 1. `red` is NBX*8 floats of shared scratch; `pitch` is the
+// element stride between staged rows (>= Kp).
 // NBX = number of activation rows staged (batch rows, or MoE segments).
 // ---------------------------------------------------------------------------------------------
 template <typename T, int NBX>
-__device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present, T* x_s, float* red, int tid) {
+__device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present, T* x_s, int pitch, float* red,
+                                             int tid) {
   const int K = a.K, Kp = a.Kp;
   const T* __restrict__ x = reinterpret_cast<const T*>(a.x);
   const T* __restrict__ nw = reinterpret_cast<const T*>(a.norm_w);
@@ -78,7 +80,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
         for (int b = 0; b < NBX; ++b) {
           if (b < rows_present) {
             float f[8];
-            unpack8<T>(ld_cached16(x + (size_t)b * K + k), f);
+            unpack8<T>(ld_act16(x + (size_t)b * K + k), f);
 #pragma unroll
             for (int i = 0; i < 8; ++i) ss[b] = fmaf(f[i], f[i], ss[b]);
           }
@@ -89,7 +91,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
 #pragma unroll
         for (int b = 0; b < NBX; ++b) {
           if (b < rows_present) {
-            float v = Elt<T>::to_f32(x[(size_t)b * K + k]);
+            float v = ld_act_f32<T>(x + (size_t)b * K + k);
             ss[b] = fmaf(v, v, ss[b]);
           }
         }
@@ -118,7 +120,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
       for (int b = 0; b < NBX; ++b) {
         uint4 out = make_uint4(0, 0, 0, 0);
         if (b < rows_present) {
-          uint4 raw = ld_cached16(x + (size_t)b * K + k);
+          uint4 raw = ld_act16(x + (size_t)b * K + k);
           if (nw != nullptr) {
             float f[8];
             unpack8<T>(raw, f);
@@ -132,7 +134,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
             out = raw;
           }
         }
-        *reinterpret_cast<uint4*>(x_s + (size_t)b * Kp + k) = out;
+        *reinterpret_cast<uint4*>(x_s + (size_t)b * pitch + k) = out;
       }
     }
   } else {
@@ -141,7 +143,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
       for (int b = 0; b < NBX; ++b) {
         T out = Elt<T>::from_f32(0.f);
         if (b < rows_present && k < K) {
-          T raw = x[(size_t)b * K + k];
+          T raw = ld_act<T>(x + (size_t)b * K + k);
           if (nw != nullptr) {
             float n1 = Elt<T>::to_f32(Elt<T>::from_f32(Elt<T>::to_f32(raw) * rstd[b]));
             out = Elt<T>::from_f32(n1 * Elt<T>::to_f32(nw[k]));
@@ -149,7 +151,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
             out = raw;
           }
         }
-        x_s[(size_t)b * Kp + k] = out;
+        x_s[(size_t)b * pitch + k] = out;
       }
     }
   }
@@ -159,18 +161,18 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
 // Plain staging of `rows` activation rows (no norm): used by the MoE down projection whose
 // reduction runs over `rows` = computed experts. Same synchronisation contract as gemv_stage_x.
 template <typename T>
-__device__ __forceinline__ void gemv_stage_x_plain(const GemvArgs& a, int rows, T* x_s, int tid) {
+__device__ __forceinline__ void gemv_stage_x_plain(const GemvArgs& a, int rows, T* x_s, int pitch, int tid) {
   const int K = a.K, Kp = a.Kp;
   const T* __restrict__ x = reinterpret_cast<const T*>(a.x);
   const bool vec_ok = ((K & 7) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
   if (vec_ok) {
-    const int total = rows * K;  // Kp == K here
-    for (int i = tid * 8; i < total; i += GEMV_CONSUMER_THREADS * 8)
-      *reinterpret_cast<uint4*>(x_s + i) = ld_cached16(x + i);
+    for (int r = 0; r < rows; ++r)
+      for (int k = tid * 8; k < K; k += GEMV_CONSUMER_THREADS * 8)
+        *reinterpret_cast<uint4*>(x_s + (size_t)r * pitch + k) = ld_act16(x + (size_t)r * K + k);
   } else {
     for (int r = 0; r < rows; ++r)
       for (int k = tid; k < Kp; k += GEMV_CONSUMER_THREADS)
-        x_s[(size_t)r * Kp + k] = (k < K) ? x[(size_t)r * K + k] : Elt<T>::from_f32(0.f);
+        x_s[(size_t)r * pitch + k] = (k < K) ? ld_act<T>(x + (size_t)r * K + k) : Elt<T>::from_f32(0.f);
   }
   named_bar_sync(1, GEMV_CONSUMER_THREADS);
 }
@@ -195,7 +197,7 @@ __device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int 
   if (a.mul_bias) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.mul_bias)[n]);
   if (a.add_bias) v += Elt<T>::to_f32(reinterpret_cast<const T*>(a.add_bias)[n]);
   const size_t o = (size_t)b * a.N + n;
-  if (a.residual) v += Elt<T>::to_f32(reinterpret_cast<const T*>(a.residual)[o]);
+  if (a.residual) v += ld_act_f32<T>(reinterpret_cast<const T*>(a.residual) + o);
   if (a.y_f32) a.y_f32[o] = v;
   if (a.y) reinterpret_cast<T*>(a.y)[o] = Elt<T>::from_f32(v);
 }

@@ -25,13 +25,13 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(const T* __restri
   if (vec_ok) {
     for (int k = tid * 8; k < K; k += NORM_THREADS * 8) {
       float f[8];
-      unpack8<T>(ld_cached16(xr + k), f);
+      unpack8<T>(ld_act16(xr + k), f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
     }
   } else {
     for (int k = tid; k < K; k += NORM_THREADS) {
-      const float v = Elt<T>::to_f32(xr[k]);
+      const float v = ld_act_f32<T>(xr + k);
       ss = fmaf(v, v, ss);
     }
   }
@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(const T* __restri
   if (vec_ok) {
     for (int k = tid * 8; k < K; k += NORM_THREADS * 8) {
       float f[8], wv[8];
-      unpack8<T>(ld_cached16(xr + k), f);
+      unpack8<T>(ld_act16(xr + k), f);
       if (w != nullptr) unpack8<T>(ld_cached16(w + k), wv);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(const T* __restri
     }
   } else {
     for (int k = tid; k < K; k += NORM_THREADS) {
-      float n1 = Elt<T>::to_f32(Elt<T>::from_f32(Elt<T>::to_f32(xr[k]) * rstd));
+      float n1 = Elt<T>::to_f32(Elt<T>::from_f32(ld_act_f32<T>(xr + k) * rstd));
       if (w != nullptr) n1 *= Elt<T>::to_f32(w[k]);
       yr[k] = Elt<T>::from_f32(n1);
     }
@@ -69,9 +69,9 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(const T* __restri
 extern "C" mui_status_t mui_rmsnorm_forward(void* stream, mui_dtype_t dtype, int rows, int K, const void* w,
                                             float epsilon, const void* x, void* y, unsigned flags) {
   MUI_REQUIRE(dtype == MUI_F16 || dtype == MUI_BF16, MUI_ERR_UNSUPPORTED, "dtype %d unsupported", (int)dtype);
-  MUI_REQUIRE(x && y, MUI_ERR_INVALID_ARG, "x and y must be non-null");
   MUI_REQUIRE(rows >= 0 && K >= 1, MUI_ERR_INVALID_ARG, "rows=%d, K=%d", rows, K);
   if (rows == 0) return MUI_OK;
+  MUI_REQUIRE(x && y, MUI_ERR_INVALID_ARG, "x and y must be non-null");
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
   if (dtype == MUI_F16) {
     MUI_CUDA_CHECK(mui_launch(rmsnorm_kernel<__half>, dim3(rows), dim3(NORM_THREADS), 0, (cudaStream_t)stream, pdl,

@@ -52,32 +52,32 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) rope_kernel(const RopeArgs a)
     if (a.k_out) out_plain = reinterpret_cast<T*>(a.k_out) + (((size_t)b * a.Hkv + head) * a.T + t) * D;
     if (a.k_cache)
       out_cache = reinterpret_cast<T*>(a.k_cache) +
-                  (((size_t)b * a.Hkv + head) * a.max_T + static_cast<size_t>(a.cache_position[t])) * D;
+                  (((size_t)b * a.Hkv + head) * a.max_T + static_cast<size_t>(__ldcg(a.cache_position + t))) * D;
     rotate = a.apply_rope != 0;
   } else {
     head -= a.Hq + a.Hkv;
     if (a.v_in == nullptr || a.v_cache == nullptr) return;
     in = reinterpret_cast<const T*>(a.v_in) + b * a.vs.batch + head * a.vs.head + t * a.vs.tok;
     out_cache = reinterpret_cast<T*>(a.v_cache) +
-                (((size_t)b * a.Hkv + head) * a.max_T + static_cast<size_t>(a.cache_position[t])) * D;
+                (((size_t)b * a.Hkv + head) * a.max_T + static_cast<size_t>(__ldcg(a.cache_position + t))) * D;
     rotate = false;
   }
 
   if (!rotate) {
     for (int i = lane; i < D; i += 32) {
-      const T v = in[i];
+      const T v = ld_act<T>(in + i);
       if (out_plain) out_plain[i] = v;
       if (out_cache) out_cache[i] = v;
     }
     return;
   }
 
-  const size_t pos = (a.table_layout == 0) ? static_cast<size_t>(a.position_ids[(size_t)b * a.T + t])
+  const size_t pos = (a.table_layout == 0) ? static_cast<size_t>(__ldcg(a.position_ids + (size_t)b * a.T + t))
                                            : ((size_t)b * a.T + t);
   const T* cs = reinterpret_cast<const T*>(a.cos_t) + pos * D;
   const T* sn = reinterpret_cast<const T*>(a.sin_t) + pos * D;
   for (int i = lane; i < half; i += 32) {
-    const float x1 = Elt<T>::to_f32(in[i]), x2 = Elt<T>::to_f32(in[i + half]);
+    const float x1 = ld_act_f32<T>(in + i), x2 = ld_act_f32<T>(in + i + half);
     const float c1 = Elt<T>::to_f32(cs[i]), c2 = Elt<T>::to_f32(cs[i + half]);
     const float s1 = Elt<T>::to_f32(sn[i]), s2 = Elt<T>::to_f32(sn[i + half]);
     const T o1 = Elt<T>::from_f32(fmaf(x1, c1, -x2 * s1));

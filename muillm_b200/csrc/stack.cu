@@ -1,0 +1,289 @@
+// Llama-architecture decode stack: one call launches every kernel of a decode step (embedding, per layer
+// fused-norm QKV GEMV -> RoPE + cache write -> flash decoding -> o_proj + residual -> fused-norm gate/up
+// + SiLU -> down + residual, then final-norm lm_head GEMV and greedy arg-max). Positions, sequence length
+// and the token fed to the next step live in device memory, so a step is replayable from a CUDA graph
+// and consecutive steps need no host round trip. Host-side C++ only; all kernels are reached through
+// the same entry points the C ABI exports.
+//
+// The reference has this level only for tensor-parallel runs (MuiLLMParallelDecoderStack::forward,
+// csrc/modules/parallel_decoder_stack.cpp:22-45, MuiLLMParallelDecoder::forward,
+// csrc/modules/parallel_decoder_module.cpp:22-62); single-GPU decode goes through Python per layer there
+// (muillm/modules/decoder/decoder.py:95-165).
+#include "common.cuh"
+
+#include <cstring>
+#include <new>
+#include <vector>
+
+mui_status_t mui_launch_embedding(cudaStream_t stream, const void* table, const int64_t* tokens, void* out, int B,
+                                  int H, int vocab, int pdl);
+mui_status_t mui_launch_argmax_advance(cudaStream_t stream, mui_dtype_t dtype, const void* logits, int V, int B,
+                                       long long* state, int32_t* seq_len32, long long* out_tokens, int out_capacity,
+                                       int pdl);
+
+struct mui_llama_stack {
+  mui_llama_config_t cfg;
+  std::vector<const void*> qkv, o, gate, up, down, ln1, ln2;
+  std::vector<void*> k_cache, v_cache;
+  const void *embed, *final_norm, *lm_head, *cos_t, *sin_t;
+  // scratch carve-up (device)
+  unsigned char* scratch;
+  long long* state;      // [3 + 2B] int64: step, tokens in cache, cache_position, position_ids[B], tokens[B]
+  int32_t* seq_len32;    // tokens attended by the current step (= tokens in cache + 1)
+  void *h, *qkv_out, *q_rot, *attn, *t, *logits;
+  void* fd_ws;
+  size_t fd_ws_bytes;
+  long long* out_tokens;
+  int out_capacity;
+  cudaGraphExec_t graph_exec;
+  unsigned graph_flags;
+};
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct ScratchLayout {
+  size_t state, seq_len, h, qkv, q_rot, attn, t, logits, fd_ws, fd_ws_bytes, total;
+};
+
+ScratchLayout scratch_layout(const mui_llama_config_t& c) {
+  ScratchLayout l;
+  const size_t B = c.batch, e = 2;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = off;
+    off = align_up(off + bytes, 256);
+    return at;
+  };
+  l.state = take((3 + 2 * B) * sizeof(long long));
+  l.seq_len = take(sizeof(int32_t));
+  l.h = take(B * c.hidden * e);
+  l.qkv = take(B * (size_t)(c.heads + 2 * c.kv_heads) * c.head_dim * e);
+  l.q_rot = take(B * (size_t)c.heads * c.head_dim * e);
+  l.attn = take(B * (size_t)c.heads * c.head_dim * e);
+  l.t = take(B * (size_t)c.intermediate * e);
+  l.logits = take(B * (size_t)c.vocab * e);
+  l.fd_ws_bytes = mui_flash_decode_workspace_bytes(c.batch, c.heads, c.kv_heads, c.head_dim, c.max_seq);
+  l.fd_ws = take(l.fd_ws_bytes);
+  l.total = off;
+  return l;
+}
+
+mui_status_t validate_cfg(const mui_llama_config_t* c) {
+  MUI_REQUIRE(c != nullptr, MUI_ERR_INVALID_ARG, "config is null");
+  MUI_REQUIRE(c->dtype == MUI_F16 || c->dtype == MUI_BF16, MUI_ERR_UNSUPPORTED, "dtype %d unsupported", (int)c->dtype);
+  MUI_REQUIRE(c->layers >= 1 && c->hidden >= 8 && c->intermediate >= 8 && c->vocab >= 1, MUI_ERR_INVALID_ARG,
+              "bad model sizes");
+  MUI_REQUIRE(c->heads >= 1 && c->kv_heads >= 1 && c->heads % c->kv_heads == 0, MUI_ERR_INVALID_ARG,
+              "heads=%d kv_heads=%d", c->heads, c->kv_heads);
+  MUI_REQUIRE(c->head_dim == 64 || c->head_dim == 128, MUI_ERR_UNSUPPORTED, "head_dim %d unsupported", c->head_dim);
+  MUI_REQUIRE(c->batch >= 1 && c->batch <= 8, MUI_ERR_UNSUPPORTED, "batch %d outside 1..8", c->batch);
+  MUI_REQUIRE(c->max_seq >= 1, MUI_ERR_INVALID_ARG, "max_seq must be positive");
+  return MUI_OK;
+}
+
+mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags) {
+  const mui_llama_config_t& c = s->cfg;
+  const int B = c.batch, H = c.hidden, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim;
+  const int qkv_n = (Hq + 2 * Hkv) * D;
+  const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
+  const long long* tokens = s->state + 3 + B;
+  const long long* position_ids = s->state + 3;
+  const long long* cache_position = s->state + 2;
+  mui_status_t st;
+  st = mui_launch_embedding(stream, s->embed, (const int64_t*)tokens, s->h, B, H, c.vocab, pdl);
+  if (st != MUI_OK) return st;
+  // q,k,v are slices of the packed qkv row: [B, 1, (Hq+2Hkv)*D] viewed as [B, H*, 1, D]
+  const mui_strides3_t qs = {(int64_t)qkv_n, (int64_t)D, (int64_t)qkv_n};
+  const mui_strides3_t kvs = {(int64_t)Hkv * c.max_seq * D, (int64_t)c.max_seq * D, (int64_t)D};
+  const size_t e = 2;
+  for (int l = 0; l < c.layers; ++l) {
+    st = mui_linear_forward(stream, c.dtype, B, qkv_n, H, s->ln1[l], c.rms_eps, s->qkv[l], MUI_ACT_IDENTITY, nullptr,
+                            nullptr, nullptr, s->h, s->qkv_out, flags);
+    if (st != MUI_OK) return st;
+    const unsigned char* qp = (const unsigned char*)s->qkv_out;
+    st = mui_rope_forward(stream, c.dtype, B, 1, c.max_seq, Hq, Hkv, D, 0, (const int64_t*)position_ids, s->cos_t,
+                          s->sin_t, qp, qs, qp + (size_t)Hq * D * e, qs, qp + (size_t)(Hq + Hkv) * D * e, qs,
+                          s->q_rot, nullptr, s->k_cache[l], s->v_cache[l], (const int64_t*)cache_position, flags);
+    if (st != MUI_OK) return st;
+    st = mui_flash_decode(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->seq_len32, c.attn_scale, s->q_rot,
+                          s->k_cache[l], s->v_cache[l], kvs, nullptr, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
+    if (st != MUI_OK) return st;
+    st = mui_linear_forward(stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr, nullptr,
+                            s->h, s->attn, s->h, flags);
+    if (st != MUI_OK) return st;
+    st = mui_gateup_silu_forward(stream, c.dtype, B, c.intermediate, H, s->ln2[l], c.rms_eps, s->gate[l], s->up[l],
+                                 s->h, s->t, flags);
+    if (st != MUI_OK) return st;
+    st = mui_linear_forward(stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l], MUI_ACT_IDENTITY,
+                            nullptr, nullptr, s->h, s->t, s->h, flags);
+    if (st != MUI_OK) return st;
+  }
+  st = mui_linear_forward(stream, c.dtype, B, c.vocab, H, s->final_norm, c.rms_eps, s->lm_head, MUI_ACT_IDENTITY,
+                          nullptr, nullptr, nullptr, s->h, s->logits, flags);
+  if (st != MUI_OK) return st;
+  return mui_launch_argmax_advance(stream, c.dtype, s->logits, c.vocab, B, s->state, s->seq_len32, s->out_tokens,
+                                   s->out_capacity, pdl);
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t mui_llama_stack_scratch_bytes(const mui_llama_config_t* cfg) {
+  if (validate_cfg(cfg) != MUI_OK) return 0;
+  return scratch_layout(*cfg).total;
+}
+
+mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_llama_weights_t* w, void* scratch,
+                                    size_t scratch_bytes, mui_llama_stack_t** out) {
+  if (mui_status_t s = validate_cfg(cfg)) return s;
+  MUI_REQUIRE(w && scratch && out, MUI_ERR_INVALID_ARG, "weights, scratch and out must be non-null");
+  MUI_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255) == 0, MUI_ERR_INVALID_ARG, "scratch must be 256-byte aligned");
+  const ScratchLayout lay = scratch_layout(*cfg);
+  MUI_REQUIRE(scratch_bytes >= lay.total, MUI_ERR_INVALID_ARG, "scratch too small: %zu < %zu", scratch_bytes, lay.total);
+  MUI_REQUIRE(w->embed && w->final_norm && w->lm_head && w->cos_table && w->sin_table, MUI_ERR_INVALID_ARG,
+              "embed, final_norm, lm_head, cos_table and sin_table must be non-null");
+  MUI_REQUIRE(w->qkv && w->o && w->gate && w->up && w->down && w->ln1 && w->ln2 && w->k_cache && w->v_cache,
+              MUI_ERR_INVALID_ARG, "per-layer pointer arrays must be non-null");
+  mui_llama_stack* s = new (std::nothrow) mui_llama_stack();
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "out of host memory");
+  s->cfg = *cfg;
+  for (int l = 0; l < cfg->layers; ++l) {
+    const void* ptrs[] = {w->qkv[l], w->o[l], w->gate[l], w->up[l], w->down[l], w->ln1[l], w->ln2[l],
+                          w->k_cache[l], w->v_cache[l]};
+    for (const void* p : ptrs) {
+      if (p == nullptr) {
+        delete s;
+        mui_set_error("layer %d has a null weight or cache pointer", l);
+        return MUI_ERR_INVALID_ARG;
+      }
+    }
+    s->qkv.push_back(w->qkv[l]);
+    s->o.push_back(w->o[l]);
+    s->gate.push_back(w->gate[l]);
+    s->up.push_back(w->up[l]);
+    s->down.push_back(w->down[l]);
+    s->ln1.push_back(w->ln1[l]);
+    s->ln2.push_back(w->ln2[l]);
+    s->k_cache.push_back(w->k_cache[l]);
+    s->v_cache.push_back(w->v_cache[l]);
+  }
+  s->embed = w->embed;
+  s->final_norm = w->final_norm;
+  s->lm_head = w->lm_head;
+  s->cos_t = w->cos_table;
+  s->sin_t = w->sin_table;
+  unsigned char* base = reinterpret_cast<unsigned char*>(scratch);
+  s->scratch = base;
+  s->state = reinterpret_cast<long long*>(base + lay.state);
+  s->seq_len32 = reinterpret_cast<int32_t*>(base + lay.seq_len);
+  s->h = base + lay.h;
+  s->qkv_out = base + lay.qkv;
+  s->q_rot = base + lay.q_rot;
+  s->attn = base + lay.attn;
+  s->t = base + lay.t;
+  s->logits = base + lay.logits;
+  s->fd_ws = base + lay.fd_ws;
+  s->fd_ws_bytes = lay.fd_ws_bytes;
+  s->out_tokens = nullptr;
+  s->out_capacity = 0;
+  s->graph_exec = nullptr;
+  s->graph_flags = 0;
+  *out = s;
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_destroy(mui_llama_stack_t* s) {
+  if (s == nullptr) return MUI_OK;
+  if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
+  delete s;
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_reset(mui_llama_stack_t* s, void* stream, int position, const int64_t* position_ids_host,
+                                   int64_t* out_tokens_dev, int out_capacity) {
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  MUI_REQUIRE(position >= 0 && position < s->cfg.max_seq, MUI_ERR_INVALID_ARG, "position %d outside the cache (%d)",
+              position, s->cfg.max_seq);
+  const int B = s->cfg.batch;
+  std::vector<long long> st(3 + 2 * B, 0);
+  st[0] = 0;
+  st[1] = position;
+  st[2] = position;
+  for (int b = 0; b < B; ++b) st[3 + b] = position_ids_host ? position_ids_host[b] : position;
+  cudaStream_t cs = (cudaStream_t)stream;
+  // pageable host memory: the runtime stages the copy before returning, the vector may go out of scope
+  MUI_CUDA_CHECK(cudaMemcpyAsync(s->state, st.data(), st.size() * sizeof(long long), cudaMemcpyHostToDevice, cs));
+  const int32_t sl = position + 1;
+  MUI_CUDA_CHECK(cudaMemcpyAsync(s->seq_len32, &sl, sizeof(sl), cudaMemcpyHostToDevice, cs));
+  // flash-decoding arrival counters start at zero
+  MUI_CUDA_CHECK(cudaMemsetAsync(s->fd_ws, 0, 4096, cs));
+  s->out_tokens = reinterpret_cast<long long*>(out_tokens_dev);
+  s->out_capacity = out_tokens_dev ? out_capacity : 0;
+  if (s->graph_exec) {  // the captured argmax node holds the old output pointer
+    cudaGraphExecDestroy(s->graph_exec);
+    s->graph_exec = nullptr;
+  }
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_set_tokens(mui_llama_stack_t* s, void* stream, const int64_t* tokens, int on_device) {
+  MUI_REQUIRE(s && tokens, MUI_ERR_INVALID_ARG, "null pointer");
+  const int B = s->cfg.batch;
+  MUI_CUDA_CHECK(cudaMemcpyAsync(s->state + 3 + B, tokens, B * sizeof(long long),
+                                 on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_step(mui_llama_stack_t* s, void* stream, unsigned flags) {
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  return launch_step(s, (cudaStream_t)stream, flags);
+}
+
+mui_status_t mui_llama_stack_capture(mui_llama_stack_t* s, void* stream, unsigned flags) {
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  MUI_REQUIRE(stream != nullptr, MUI_ERR_INVALID_ARG, "capture needs a non-default stream");
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (s->graph_exec) {
+    cudaGraphExecDestroy(s->graph_exec);
+    s->graph_exec = nullptr;
+  }
+  MUI_CUDA_CHECK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
+  mui_status_t st = launch_step(s, cs, flags);
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(cs, &graph);
+  if (st != MUI_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    return st;
+  }
+  if (e != cudaSuccess) {
+    mui_set_error("cudaStreamEndCapture failed: %s", cudaGetErrorString(e));
+    return MUI_ERR_CUDA;
+  }
+  e = cudaGraphInstantiate(&s->graph_exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    s->graph_exec = nullptr;
+    mui_set_error("cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+    return MUI_ERR_CUDA;
+  }
+  s->graph_flags = flags;
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_replay(mui_llama_stack_t* s, void* stream, int steps) {
+  MUI_REQUIRE(s != nullptr && s->graph_exec != nullptr, MUI_ERR_INVALID_ARG, "no captured graph (call capture first)");
+  for (int i = 0; i < steps; ++i) MUI_CUDA_CHECK(cudaGraphLaunch(s->graph_exec, (cudaStream_t)stream));
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_logits(mui_llama_stack_t* s, void** logits_dev, int64_t** state_dev) {
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  if (logits_dev) *logits_dev = s->logits;
+  if (state_dev) *state_dev = reinterpret_cast<int64_t*>(s->state);
+  return MUI_OK;
+}
+
+}  // extern "C"

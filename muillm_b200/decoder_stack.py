@@ -1,0 +1,145 @@
+"""Host-side wrapper of the C decode stack (mui_llama_stack_*): owns the device tensors (weights, KV caches,
+scratch, output tokens) through torch and drives prefill/greedy decoding.
+
+It plays the role the reference gives to `_MuiParallelDecoderStack` + the model forward for q_len == 1
+(muillm/modules/models/llama/model.py:332-357, muillm/modules/decoder/paralleldecoderstack.py): one call per
+token instead of one Python dispatch per layer, here also for a single GPU and replayable from a CUDA graph.
+"""
+import ctypes
+import math
+from ctypes import c_int64, c_void_p
+
+import torch
+
+from . import capi
+
+
+def rope_tables(max_pos, dim, theta, dtype, device):
+    """cos/sin tables [max_pos, dim] of the default Llama RoPE, as HF's LlamaRotaryEmbedding computes them
+    (fp32 math, cast to the model dtype; muillm/modules/attention/rotaryembedding.py:313-337)."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float() / dim))
+    t = torch.arange(max_pos, dtype=torch.float32)
+    freqs = torch.outer(t, inv_freq)
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return emb.cos().to(dtype).to(device), emb.sin().to(dtype).to(device)
+
+
+class LlamaDecodeStack:
+    """weights: dict with 'embed', 'lm_head', 'norm' tensors and per-layer lists 'qkv', 'o', 'gate', 'up',
+    'down', 'ln1', 'ln2' (CUDA, contiguous, fp16 or bf16). cfg: dict with layers, hidden, intermediate, heads,
+    kv_heads, head_dim, vocab, eps, rope_theta."""
+
+    def __init__(self, weights, cfg, max_seq, batch=1, max_new_tokens=4096, flags=0):
+        self.lib = capi.lib()
+        self.cfg = dict(cfg)
+        self.w = weights
+        dev = weights["embed"].device
+        dt = weights["embed"].dtype
+        self.device, self.dtype = dev, dt
+        self.batch, self.max_seq = batch, max_seq
+        self.flags = flags
+        L, Hkv, D = cfg["layers"], cfg["kv_heads"], cfg["head_dim"]
+        for name in ("embed", "lm_head", "norm"):
+            assert weights[name].is_cuda and weights[name].is_contiguous() and weights[name].dtype == dt
+        self.k_cache = [torch.zeros(batch, Hkv, max_seq, D, dtype=dt, device=dev) for _ in range(L)]
+        self.v_cache = [torch.zeros(batch, Hkv, max_seq, D, dtype=dt, device=dev) for _ in range(L)]
+        self.cos, self.sin = rope_tables(max_seq, D, cfg["rope_theta"], dt, dev)
+        c = capi.LlamaConfig(
+            capi.MUI_F16 if dt == torch.float16 else capi.MUI_BF16, L, cfg["hidden"], cfg["intermediate"],
+            cfg["heads"], Hkv, D, cfg["vocab"], max_seq, batch, float(cfg["eps"]), 1.0 / math.sqrt(D))
+        self._c = c
+        nbytes = self.lib.mui_llama_stack_scratch_bytes(ctypes.byref(c))
+        if nbytes == 0:
+            raise RuntimeError("muillm_b200: " + self.lib.mui_last_error().decode())
+        self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        self.out_tokens = torch.zeros(max_new_tokens, batch, dtype=torch.int64, device=dev)
+
+        def arr(tensors):
+            for t in tensors:
+                assert t.is_cuda and t.is_contiguous() and t.dtype == dt
+            return (c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+        self._arrays = {k: arr(weights[k]) for k in ("qkv", "o", "gate", "up", "down", "ln1", "ln2")}
+        self._arrays["k_cache"] = arr(self.k_cache)
+        self._arrays["v_cache"] = arr(self.v_cache)
+        w = capi.LlamaWeights(
+            weights["embed"].data_ptr(), weights["norm"].data_ptr(), weights["lm_head"].data_ptr(),
+            self.cos.data_ptr(), self.sin.data_ptr(),
+            self._arrays["qkv"], self._arrays["o"], self._arrays["gate"], self._arrays["up"], self._arrays["down"],
+            self._arrays["ln1"], self._arrays["ln2"], self._arrays["k_cache"], self._arrays["v_cache"])
+        h = c_void_p()
+        capi.check(self.lib.mui_llama_stack_create(ctypes.byref(c), ctypes.byref(w), self.scratch.data_ptr(),
+                                                   self.scratch.numel(), ctypes.byref(h)))
+        self._h = h
+        self._captured = False
+        self.reset(0)
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self.lib.mui_llama_stack_destroy(h)
+            self._h = None
+
+    def _stream(self):
+        return torch.cuda.current_stream().cuda_stream
+
+    def reset(self, position=0, position_ids=None):
+        pid = None
+        if position_ids is not None:
+            pid = (c_int64 * self.batch)(*[int(p) for p in position_ids])
+        capi.check(self.lib.mui_llama_stack_reset(self._h, self._stream(), int(position), pid,
+                                                  self.out_tokens.data_ptr(), self.out_tokens.shape[0]))
+        self._captured = False
+
+    def set_tokens(self, tokens):
+        """tokens: int64 tensor [batch] on the host (pinned or not) or on the device."""
+        assert tokens.dtype == torch.int64 and tokens.numel() == self.batch
+        capi.check(self.lib.mui_llama_stack_set_tokens(self._h, self._stream(), tokens.data_ptr(),
+                                                       1 if tokens.is_cuda else 0))
+
+    def step(self):
+        capi.check(self.lib.mui_llama_stack_step(self._h, self._stream(), self.flags))
+
+    def capture(self):
+        capi.check(self.lib.mui_llama_stack_capture(self._h, self._stream(), self.flags))
+        self._captured = True
+
+    def replay(self, steps=1):
+        capi.check(self.lib.mui_llama_stack_replay(self._h, self._stream(), steps))
+
+    def logits(self):
+        """View of the last step's logits [batch, vocab] (model dtype)."""
+        lp, sp = c_void_p(), c_void_p()
+        capi.check(self.lib.mui_llama_stack_logits(self._h, ctypes.byref(lp), ctypes.byref(sp)))
+        off = lp.value - self.scratch.data_ptr()
+        n = self.batch * self.cfg["vocab"]
+        return self.scratch[off: off + 2 * n].view(self.dtype).view(self.batch, self.cfg["vocab"])
+
+    def prefill(self, prompt):
+        """Feeds prompt [batch, T] token by token through the decode step; the arg-max after the last prompt
+        token is the first generated token (row 0 of out_tokens after reset counts steps, so callers read
+        out_tokens[T-1])."""
+        T = prompt.shape[1]
+        for t in range(T):
+            self.set_tokens(prompt[:, t].contiguous())
+            self.step()
+
+    def greedy(self, prompt, new_tokens, use_graph=True):
+        """Greedy decoding: returns int64 [batch, new_tokens] (device)."""
+        self.reset(0)
+        T = prompt.shape[1]
+        self.prefill(prompt)
+        remaining = new_tokens - 1
+        if remaining > 0:
+            if use_graph:
+                s = torch.cuda.Stream()
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    if not self._captured:
+                        self.capture()
+                    self.replay(remaining)
+                torch.cuda.current_stream().wait_stream(s)
+            else:
+                for _ in range(remaining):
+                    self.step()
+        return self.out_tokens[T - 1: T - 1 + new_tokens].transpose(0, 1).contiguous()
