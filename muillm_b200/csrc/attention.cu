@@ -25,6 +25,7 @@ constexpr int FD_WARPS = 8;
 constexpr int FD_MAX_SPLITS = 64;
 constexpr int FD_COUNTER_BYTES = 4096;
 constexpr int FD_CHUNK_ALIGN = 16;
+constexpr int FD_MIN_CHUNK = 64;  // tokens per split at least: one load round of the 8 warps (8 x 2 x 4 tokens at D=128)
 
 struct FdArgs {
   const void *q, *k, *v, *mask;
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
   int S = a.S;
   if (a.seq_len_dev != nullptr) S = min(S, max(0, __ldcg(a.seq_len_dev)));
   int chunk = (S + (int)gridDim.x - 1) / (int)gridDim.x;
-  chunk = max(FD_CHUNK_ALIGN, (chunk + FD_CHUNK_ALIGN - 1) / FD_CHUNK_ALIGN * FD_CHUNK_ALIGN);
+  chunk = max(FD_MIN_CHUNK, (chunk + FD_CHUNK_ALIGN - 1) / FD_CHUNK_ALIGN * FD_CHUNK_ALIGN);
   const int n_active = max(1, (S + chunk - 1) / chunk);
   if (split >= n_active) return;
   const int t_begin = split * chunk;
@@ -238,14 +239,36 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
     const int g = idx / D, d = idx - g * D;
     const size_t head = (size_t)b * a.Hq + (size_t)kvh * G + g;
     const float* p = part + head * a.max_splits * (D + 2);
-    float mm = -INFINITY;
-    for (int s = 0; s < n_active; ++s) mm = fmaxf(mm, __ldcg(p + (size_t)s * (D + 2)));
-    float ll = 0.f, aa = 0.f;
-    for (int s = 0; s < n_active; ++s) {
-      const float ms = __ldcg(p + (size_t)s * (D + 2));
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-      ll = fmaf(__ldcg(p + (size_t)s * (D + 2) + 1), f, ll);
-      aa = fmaf(__ldcg(p + (size_t)s * (D + 2) + 2 + d), f, aa);
+    // splits in batches of 8: issue the batch's loads back to back, then fold them (a dependent
+    // load-then-max loop would pay one L2 round trip per split)
+    float mm = -INFINITY, ll = 0.f, aa = 0.f;
+    for (int s0 = 0; s0 < n_active; s0 += 8) {
+      float ms[8], ls[8], as[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int s = min(s0 + i, n_active - 1);
+        const float* ps = p + (size_t)s * (D + 2);
+        ms[i] = __ldcg(ps);
+        ls[i] = __ldcg(ps + 1);
+        as[i] = __ldcg(ps + 2 + d);
+      }
+      float bm = mm;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (s0 + i < n_active) bm = fmaxf(bm, ms[i]);
+      if (bm == -INFINITY) continue;
+      const float c = (mm == -INFINITY) ? 0.f : exp2f(mm - bm);
+      ll *= c;
+      aa *= c;
+      mm = bm;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (s0 + i < n_active && ms[i] != -INFINITY) {
+          const float f = exp2f(ms[i] - bm);
+          ll = fmaf(ls[i], f, ll);
+          aa = fmaf(as[i], f, aa);
+        }
+      }
     }
     out[head * D + d] = Elt<T>::from_f32(ll > 0.f ? aa / ll : 0.f);
   }
@@ -307,7 +330,7 @@ mui_status_t mui_flash_decode(void* stream, mui_dtype_t dtype, int B, int Hq, in
   const MuiDeviceInfo* dev = mui_current_device_info();
   if (!dev) return MUI_ERR_CUDA;
   int splits = (2 * dev->sm_count + B * Hkv - 1) / (B * Hkv);
-  splits = std::min(splits, (S + FD_CHUNK_ALIGN - 1) / FD_CHUNK_ALIGN);
+  splits = std::min(splits, (S + FD_MIN_CHUNK - 1) / FD_MIN_CHUNK);
   splits = std::max(1, std::min(splits, FD_MAX_SPLITS));
 
   FdArgs a;

@@ -28,37 +28,73 @@ __global__ void __launch_bounds__(256) embedding_kernel(const uint16_t* __restri
   }
 }
 
-constexpr int ARGMAX_THREADS = 1024;
+constexpr int ARGMAX_THREADS = 256;
+constexpr int ARGMAX_CTAS = 32;  // CTAs per row
 
-// One CTA per row: arg-max over V 16-bit logits, lowest index wins ties. Then (thread 0 of row 0) advances
-// the decode state. state layout (int64 words): [0] step, [1] tokens in the cache before the step,
-// [2] cache_position (row this step wrote), [3..3+B) position_ids, [3+B..3+2B) tokens fed to the step.
+__device__ __forceinline__ bool argmax_better(float v, int i, float bv, int bi) {
+  return v > bv || (v == bv && i < bi);
+}
+
+// ARGMAX_CTAS CTAs per row scan slices of the V 16-bit logits (16-byte loads); lowest index wins ties. Each
+// CTA leaves its (value, index) in `partials`; the last CTA of the launch to arrive (arrival counter in
+// `counters[0]`, left at zero again) picks every row's winner and advances the decode state.
+// state layout (int64 words): [0] step, [1] tokens in the cache before the step, [2] cache_position (row this
+// step wrote), [3..3+B) position_ids, [3+B..3+2B) tokens fed to the step.
 template <typename T>
-__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_advance_kernel(const T* __restrict__ logits, int V, int B,
-                                                                        long long* __restrict__ state,
-                                                                        int32_t* __restrict__ seq_len32,
-                                                                        long long* __restrict__ out_tokens,
-                                                                        int out_capacity) {
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_advance_kernel(const T* logits, int V, int B,
+                                                                        long long* state, int32_t* seq_len32,
+                                                                        long long* out_tokens, int out_capacity,
+                                                                        float* partial_val, int* partial_idx,
+                                                                        unsigned int* counters) {
   __shared__ float s_val[ARGMAX_THREADS / 32];
   __shared__ int s_idx[ARGMAX_THREADS / 32];
+  __shared__ int s_last;
   pdl_wait_prior_grid();
   pdl_launch_dependents();
-  const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const T* row = logits + (size_t)b * V;
+  // slice of this CTA, in units of 8 elements
+  const int vec_total = V >> 3;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = tid; i < V; i += ARGMAX_THREADS) {
-    const float v = ld_act_f32<T>(row + i);
-    if (v > best || (v == best && i < best_i)) {
-      best = v;
-      best_i = i;
+  if (vec_ok) {
+    const int v_begin = static_cast<int>((long long)vec_total * blockIdx.x / gridDim.x);
+    const int v_end = static_cast<int>((long long)vec_total * (blockIdx.x + 1) / gridDim.x);
+    for (int v = v_begin + tid; v < v_end; v += ARGMAX_THREADS) {
+      float f[8];
+      unpack8<T>(ld_act16(row + (size_t)v * 8), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (argmax_better(f[i], v * 8 + i, best, best_i)) {
+          best = f[i];
+          best_i = v * 8 + i;
+        }
+    }
+    if (blockIdx.x == gridDim.x - 1)  // tail elements
+      for (int i = vec_total * 8 + tid; i < V; i += ARGMAX_THREADS) {
+        const float v = ld_act_f32<T>(row + i);
+        if (argmax_better(v, i, best, best_i)) {
+          best = v;
+          best_i = i;
+        }
+      }
+  } else {
+    const int e_begin = static_cast<int>((long long)V * blockIdx.x / gridDim.x);
+    const int e_end = static_cast<int>((long long)V * (blockIdx.x + 1) / gridDim.x);
+    for (int i = e_begin + tid; i < e_end; i += ARGMAX_THREADS) {
+      const float v = ld_act_f32<T>(row + i);
+      if (argmax_better(v, i, best, best_i)) {
+        best = v;
+        best_i = i;
+      }
     }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(MUI_FULL_MASK, best, o);
     const int oi = __shfl_xor_sync(MUI_FULL_MASK, best_i, o);
-    if (ov > best || (ov == best && oi < best_i)) {
+    if (argmax_better(ov, oi, best, best_i)) {
       best = ov;
       best_i = oi;
     }
@@ -69,24 +105,58 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_advance_kernel(const T*
   }
   __syncthreads();
   if (tid == 0) {
-    for (int w = 1; w < ARGMAX_THREADS / 32; ++w) {
-      if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) {
+    for (int w = 1; w < ARGMAX_THREADS / 32; ++w)
+      if (argmax_better(s_val[w], s_idx[w], best, best_i)) {
         best = s_val[w];
         best_i = s_idx[w];
       }
+    partial_val[b * gridDim.x + blockIdx.x] = best;
+    partial_idx[b * gridDim.x + blockIdx.x] = best_i;
+    __threadfence();
+    const unsigned prev = atomicAdd(&counters[0], 1u);
+    s_last = (prev == gridDim.x * gridDim.y - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // the last CTA of the whole launch finishes every row (warp w takes row w; B <= 8 warps)
+  __threadfence();
+  const long long step = __ldcg(state);
+  if (warp < B) {
+    const int r = warp;
+    best = -INFINITY;
+    best_i = 0x7fffffff;
+    for (int c = lane; c < (int)gridDim.x; c += 32) {
+      const float v = __ldcg(partial_val + r * gridDim.x + c);
+      const int i = __ldcg(partial_idx + r * gridDim.x + c);
+      if (argmax_better(v, i, best, best_i)) {
+        best = v;
+        best_i = i;
+      }
     }
-    if (best_i == 0x7fffffff) best_i = 0;  // all NaN / empty
-    const long long step = __ldcg(state);
-    state[3 + B + b] = best_i;  // token fed to the next step
-    if (out_tokens != nullptr && step < out_capacity) out_tokens[step * B + b] = best_i;
-    state[3 + b] = __ldcg(state + 3 + b) + 1;  // position id of this sequence
-    if (b == 0) {
-      const long long in_cache = __ldcg(state + 1) + 1;
-      state[0] = step + 1;
-      state[1] = in_cache;
-      state[2] = __ldcg(state + 2) + 1;
-      *seq_len32 = static_cast<int32_t>(in_cache + 1);  // the next step attends its own new token too
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(MUI_FULL_MASK, best, o);
+      const int oi = __shfl_xor_sync(MUI_FULL_MASK, best_i, o);
+      if (argmax_better(ov, oi, best, best_i)) {
+        best = ov;
+        best_i = oi;
+      }
     }
+    if (lane == 0) {
+      if (best_i == 0x7fffffff) best_i = 0;  // all NaN / empty
+      state[3 + B + r] = best_i;             // token fed to the next step
+      if (out_tokens != nullptr && step < out_capacity) out_tokens[step * B + r] = best_i;
+      state[3 + r] = __ldcg(state + 3 + r) + 1;  // position id of this sequence
+    }
+  }
+  __syncthreads();  // every warp has read `step` before it moves
+  if (tid == 0) {
+    counters[0] = 0u;
+    const long long in_cache = __ldcg(state + 1) + 1;
+    state[0] = step + 1;
+    state[1] = in_cache;
+    state[2] = __ldcg(state + 2) + 1;
+    *seq_len32 = static_cast<int32_t>(in_cache + 1);  // the next step attends its own new token too
   }
 }
 
@@ -99,15 +169,25 @@ mui_status_t mui_launch_embedding(cudaStream_t stream, const void* table, const 
   return MUI_OK;
 }
 
+// `work`: device scratch of mui_argmax_work_bytes(B) bytes whose first 64 bytes (arrival counters) are zero
+// before the first call; every call leaves them zero.
+size_t mui_argmax_work_bytes(int B) { return 64 + (size_t)B * ARGMAX_CTAS * 8; }
+
 mui_status_t mui_launch_argmax_advance(cudaStream_t stream, mui_dtype_t dtype, const void* logits, int V, int B,
                                        long long* state, int32_t* seq_len32, long long* out_tokens, int out_capacity,
-                                       int pdl) {
+                                       void* work, int pdl) {
+  unsigned int* counters = reinterpret_cast<unsigned int*>(work);
+  float* pval = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(work) + 64);
+  int* pidx = reinterpret_cast<int*>(pval + (size_t)B * ARGMAX_CTAS);
+  const dim3 grid(ARGMAX_CTAS, B);
   if (dtype == MUI_F16) {
-    MUI_CUDA_CHECK(mui_launch(argmax_advance_kernel<__half>, dim3(B), dim3(ARGMAX_THREADS), 0, stream, pdl,
-                              (const __half*)logits, V, B, state, seq_len32, out_tokens, out_capacity));
+    MUI_CUDA_CHECK(mui_launch(argmax_advance_kernel<__half>, grid, dim3(ARGMAX_THREADS), 0, stream, pdl,
+                              (const __half*)logits, V, B, state, seq_len32, out_tokens, out_capacity, pval, pidx,
+                              counters));
   } else {
-    MUI_CUDA_CHECK(mui_launch(argmax_advance_kernel<__nv_bfloat16>, dim3(B), dim3(ARGMAX_THREADS), 0, stream, pdl,
-                              (const __nv_bfloat16*)logits, V, B, state, seq_len32, out_tokens, out_capacity));
+    MUI_CUDA_CHECK(mui_launch(argmax_advance_kernel<__nv_bfloat16>, grid, dim3(ARGMAX_THREADS), 0, stream, pdl,
+                              (const __nv_bfloat16*)logits, V, B, state, seq_len32, out_tokens, out_capacity, pval,
+                              pidx, counters));
   }
   return MUI_OK;
 }

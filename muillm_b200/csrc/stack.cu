@@ -19,7 +19,8 @@ mui_status_t mui_launch_embedding(cudaStream_t stream, const void* table, const 
                                   int H, int vocab, int pdl);
 mui_status_t mui_launch_argmax_advance(cudaStream_t stream, mui_dtype_t dtype, const void* logits, int V, int B,
                                        long long* state, int32_t* seq_len32, long long* out_tokens, int out_capacity,
-                                       int pdl);
+                                       void* work, int pdl);
+size_t mui_argmax_work_bytes(int B);
 
 struct mui_llama_stack {
   mui_llama_config_t cfg;
@@ -33,6 +34,7 @@ struct mui_llama_stack {
   void *h, *qkv_out, *q_rot, *attn, *t, *logits;
   void* fd_ws;
   size_t fd_ws_bytes;
+  void* argmax_work;
   long long* out_tokens;
   int out_capacity;
   cudaGraphExec_t graph_exec;
@@ -44,7 +46,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct ScratchLayout {
-  size_t state, seq_len, h, qkv, q_rot, attn, t, logits, fd_ws, fd_ws_bytes, total;
+  size_t state, seq_len, h, qkv, q_rot, attn, t, logits, fd_ws, fd_ws_bytes, argmax_work, total;
 };
 
 ScratchLayout scratch_layout(const mui_llama_config_t& c) {
@@ -66,6 +68,7 @@ ScratchLayout scratch_layout(const mui_llama_config_t& c) {
   l.logits = take(B * (size_t)c.vocab * e);
   l.fd_ws_bytes = mui_flash_decode_workspace_bytes(c.batch, c.heads, c.kv_heads, c.head_dim, c.max_seq);
   l.fd_ws = take(l.fd_ws_bytes);
+  l.argmax_work = take(mui_argmax_work_bytes(c.batch));
   l.total = off;
   return l;
 }
@@ -124,7 +127,7 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
                           nullptr, nullptr, nullptr, s->h, s->logits, flags);
   if (st != MUI_OK) return st;
   return mui_launch_argmax_advance(stream, c.dtype, s->logits, c.vocab, B, s->state, s->seq_len32, s->out_tokens,
-                                   s->out_capacity, pdl);
+                                   s->out_capacity, s->argmax_work, pdl);
 }
 
 }  // namespace
@@ -187,6 +190,7 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
   s->logits = base + lay.logits;
   s->fd_ws = base + lay.fd_ws;
   s->fd_ws_bytes = lay.fd_ws_bytes;
+  s->argmax_work = base + lay.argmax_work;
   s->out_tokens = nullptr;
   s->out_capacity = 0;
   s->graph_exec = nullptr;
@@ -218,8 +222,9 @@ mui_status_t mui_llama_stack_reset(mui_llama_stack_t* s, void* stream, int posit
   MUI_CUDA_CHECK(cudaMemcpyAsync(s->state, st.data(), st.size() * sizeof(long long), cudaMemcpyHostToDevice, cs));
   const int32_t sl = position + 1;
   MUI_CUDA_CHECK(cudaMemcpyAsync(s->seq_len32, &sl, sizeof(sl), cudaMemcpyHostToDevice, cs));
-  // flash-decoding arrival counters start at zero
+  // flash-decoding and arg-max arrival counters start at zero
   MUI_CUDA_CHECK(cudaMemsetAsync(s->fd_ws, 0, 4096, cs));
+  MUI_CUDA_CHECK(cudaMemsetAsync(s->argmax_work, 0, 64, cs));
   s->out_tokens = reinterpret_cast<long long*>(out_tokens_dev);
   s->out_capacity = out_tokens_dev ? out_capacity : 0;
   if (s->graph_exec) {  // the captured argmax node holds the old output pointer

@@ -115,6 +115,24 @@ class LlamaDecodeStack:
         n = self.batch * self.cfg["vocab"]
         return self.scratch[off: off + 2 * n].view(self.dtype).view(self.batch, self.cfg["vocab"])
 
+    def state(self):
+        """View of the int64 device state: [step, tokens in cache, cache position, position_ids[batch],
+        next tokens[batch]]."""
+        lp, sp = c_void_p(), c_void_p()
+        capi.check(self.lib.mui_llama_stack_logits(self._h, ctypes.byref(lp), ctypes.byref(sp)))
+        off = sp.value - self.scratch.data_ptr()
+        n = 3 + 2 * self.batch
+        return self.scratch[off: off + 8 * n].view(torch.int64)
+
+    def next_tokens(self):
+        """View of the tokens the next step will consume (the last step's arg-max), int64 [batch]."""
+        return self.state()[3 + self.batch:]
+
+    @property
+    def launches_per_step(self):
+        """Kernels one decode step launches: embedding + 6 per layer + lm_head + arg-max."""
+        return 3 + 6 * self.cfg["layers"]
+
     def prefill(self, prompt):
         """Feeds prompt [batch, T] token by token through the decode step; the arg-max after the last prompt
         token is the first generated token (row 0 of out_tokens after reset counts steps, so callers read
