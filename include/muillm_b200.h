@@ -143,6 +143,25 @@ MUI_API mui_status_t mui_flash_decode(void* stream, mui_dtype_t dtype, int B, in
                                       const void* v, mui_strides3_t kv_strides, const void* mask, void* out,
                                       void* workspace, size_t workspace_bytes, unsigned flags);
 
+/* Flash decoding for callers that may not allocate device memory. No counterpart in the reference (there,
+ * torch allocates the partial buffers on every call, csrc/attention/flash_decoding.cu:154-158). Meant for hosts
+ * that pass this library nothing but input and output buffers because all device memory is already carved up by
+ * their own arena, and for loops that must not reach cudaMalloc since it synchronises the whole device. Same
+ * arguments and results as mui_flash_decode minus the workspace: the split-KV partials and arrival counters live
+ * in a static __device__ array inside the library (about 2.04 MiB that every GPU loading the library holds until
+ * the process exits), which limits the problem to B * Hq * (D + 2) <= MUI_FD_STATIC_MAX_ROW_FLOATS (e.g. 64 heads
+ * of head dim 128 in total); larger problems are rejected with MUI_ERR_UNSUPPORTED. It calls no cudaMalloc,
+ * cudaFree or other allocating routine. The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and clears the counters on `stream`; make that first call
+ * outside any stream capture. All calls share the one array and it keeps the previous call's partials, so two
+ * calls that overlap on the GPU (different streams, or different threads on one device) race; calls ordered on
+ * one stream are safe. */
+#define MUI_FD_STATIC_MAX_ROW_FLOATS (64 * 130)
+MUI_API mui_status_t mui_flash_decode_static_scratch(void* stream, mui_dtype_t dtype, int B, int Hq, int Hkv, int D,
+                                                     int S, const int32_t* seq_len_dev, float scale, const void* q,
+                                                     const void* k, const void* v, mui_strides3_t kv_strides,
+                                                     const void* mask, void* out, unsigned flags);
+
 /* ---- embedding row gather (csrc/embedding/embedding_xx16_kernels.cu:26,74) ------------------------
  * out[i, :] = table[token_ids[i], :] for 16-bit tables [vocab, H]; token ids are int64 on the device and
  * are clamped to [0, vocab). */

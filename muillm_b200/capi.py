@@ -109,6 +109,11 @@ PROTOTYPES = {
         [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
          Strides3, c_void_p, c_void_p, c_void_p, c_size_t, c_uint],
     ),
+    "mui_flash_decode_static_scratch": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+         Strides3, c_void_p, c_void_p, c_uint],
+    ),
     "mui_embedding_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_scratch_bytes": (c_size_t, [POINTER(LlamaConfig)]),
     "mui_llama_stack_create": (

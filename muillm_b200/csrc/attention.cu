@@ -15,6 +15,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <mutex>
 
 MUI_STATUS_ACCESSOR(attention)
 
@@ -350,3 +351,52 @@ mui_status_t mui_flash_decode(void* stream, mui_dtype_t dtype, int B, int Hq, in
 }
 
 }  // extern "C"
+
+// =============================================================================================
+// Flash decoding without caller-provided scratch
+// =============================================================================================
+// Same kernel and same results as mui_flash_decode, for callers that cannot hand over a workspace because
+// they are not allowed to allocate device memory themselves: a plugin host that gives the library only input
+// and output buffers out of an arena it has already carved up completely, or a serving loop that must never
+// reach cudaMalloc because that call synchronises the whole device. The split-KV partials and arrival
+// counters live in the array below, which every GPU that loads this library keeps until the process exits.
+// Its size bounds the problem: B * Hq * (D + 2) <= MUI_FD_STATIC_MAX_ROW_FLOATS (64 heads of head dim 128).
+namespace {
+constexpr size_t FD_STATIC_BYTES =
+    (size_t)FD_COUNTER_BYTES + (size_t)MUI_FD_STATIC_MAX_ROW_FLOATS * FD_MAX_SPLITS * sizeof(float);
+}
+static __device__ __align__(256) unsigned char g_fd_static_ws[FD_STATIC_BYTES];
+
+extern "C" mui_status_t mui_flash_decode_static_scratch(void* stream, mui_dtype_t dtype, int B, int Hq, int Hkv,
+                                                        int D, int S, const int32_t* seq_len_dev, float scale,
+                                                        const void* q, const void* k, const void* v,
+                                                        mui_strides3_t kv_strides, const void* mask, void* out,
+                                                        unsigned flags) {
+  MUI_REQUIRE(B >= 0 && Hq >= 1 && D >= 1, MUI_ERR_INVALID_ARG, "bad sizes B=%d Hq=%d D=%d", B, Hq, D);
+  const long long row_floats = (long long)B * Hq * (D + 2);
+  MUI_REQUIRE(row_floats <= MUI_FD_STATIC_MAX_ROW_FLOATS, MUI_ERR_UNSUPPORTED,
+              "B*Hq*(D+2) = %lld exceeds the built-in scratch (limit %d, i.e. %zu bytes); use mui_flash_decode with a "
+              "caller-provided workspace",
+              row_floats, MUI_FD_STATIC_MAX_ROW_FLOATS, FD_STATIC_BYTES);
+  // Set-up, once per device and with that device current: `g_fd_static_ws` is a host-side stand-in in this
+  // code, the kernel needs the device address behind it. The arrival counters at the front must start at
+  // zero; every launch leaves them zero again.
+  static void* dev_ptr[64] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  MUI_CUDA_CHECK(cudaGetDevice(&dev));
+  MUI_REQUIRE(dev >= 0 && dev < 64, MUI_ERR_UNSUPPORTED, "device ordinal %d outside 0..63", dev);
+  void* ws = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      MUI_CUDA_CHECK(cudaGetSymbolAddress(&p, g_fd_static_ws));
+      MUI_CUDA_CHECK(cudaMemsetAsync(p, 0, FD_COUNTER_BYTES, (cudaStream_t)stream));
+      dev_ptr[dev] = p;
+    }
+    ws = dev_ptr[dev];
+  }
+  return mui_flash_decode(stream, dtype, B, Hq, Hkv, D, S, seq_len_dev, scale, q, k, v, kv_strides, mask, out, ws,
+                          FD_STATIC_BYTES, flags);
+}
