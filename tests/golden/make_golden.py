@@ -1,0 +1,177 @@
+"""Generates the golden fixtures under tests/golden/ (run once in the authoring container; needs the reference
+checkout at /root/reference and transformers). Committed beside the fixtures it made.
+
+Sources of truth, in order of authority:
+ * the reference's own Python, imported unmodified with a stub `muillm_ext` (the CPU branches never call it):
+   `muillm.quantization.rtnquantizer.RTNQuantizer` (quantise / de-quantise), `MuiRMSNorm.forward` CPU branch
+   (muillm/modules/norm/rmsnorm.py:138-146), `topk_sigmoid` non-fp16 branch (muillm/modules/topk.py:39-44);
+ * the HF modules the reference's tests compare against (tests/test_linear.py, test_gateupdownmlp.py,
+   test_rmsnorm.py, test_rotaryembedding.py): LlamaRMSNorm, nn.Linear, LlamaMLP, LlamaRotaryEmbedding +
+   apply_rotary_pos_emb, eager attention with repeat_kv, LlamaForCausalLM greedy generation.
+Inputs are seeded; outputs are stored in fp32 (and int for quantised weights / tokens).
+"""
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = "/root/reference"
+
+
+class _Stub(types.ModuleType):
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+
+        def _f(*a, **k):
+            raise RuntimeError("muillm_ext stub called: " + name)
+
+        return _f
+
+
+def reference_fixtures(out):
+    sys.modules["muillm_ext"] = _Stub("muillm_ext")
+    sys.path.insert(0, REF)
+    from muillm.quantization.rtnquantizer import RTNQuantizer
+    from muillm.modules.topk import topk_sigmoid
+    from muillm.modules.norm.rmsnorm import MuiRMSNorm
+    from muillm.engineconfig import MuiEngineConfig  # noqa: F401  (import check only)
+
+    g = torch.Generator().manual_seed(0)
+    # RTN group quantiser: fp16 weights [24, 256], group 128 and group 32
+    w = (torch.randn(24, 256, generator=g) * 0.02).to(torch.float16)
+    w[3, :128] = 0.0125  # a constant group exercises the range clamp
+    for gs in (128, 32):
+        q = RTNQuantizer(n_bit=8, groupsize=gs)
+        wq, sm = q.group_quantize_tensor(w)
+        wd = q.group_dequantize_tensor(wq, sm, dtype=torch.float16)
+        out[f"rtn_g{gs}_w"] = w.float().numpy()
+        out[f"rtn_g{gs}_q"] = wq.numpy()
+        out[f"rtn_g{gs}_scales_min"] = sm.float().numpy()
+        out[f"rtn_g{gs}_dequant_f16"] = wd.float().numpy()
+
+    # top-k sigmoid, bf16 branch (torch.topk + fp32 sigmoid)
+    logits = torch.randn(3, 1, 16, generator=g).to(torch.bfloat16)
+    for k in (1, 2):
+        v, i = topk_sigmoid(logits, k)
+        out[f"topk{k}_logits"] = logits.float().numpy()
+        out[f"topk{k}_values"] = v.float().numpy()
+        out[f"topk{k}_indices"] = i.numpy()
+
+    # MuiRMSNorm CPU branch (built without the engine: only weight/eps/dispatchable are touched by forward)
+    norm = MuiRMSNorm.__new__(MuiRMSNorm)
+    torch.nn.Module.__init__(norm)
+    norm.weight = torch.nn.Parameter((1 + 0.01 * torch.randn(320, generator=g)).to(torch.float16))
+    norm.variance_epsilon = 1e-5
+    norm.dispatchable = False
+    x = torch.randn(5, 320, generator=g).to(torch.float16)
+    out["ref_rmsnorm_x"] = x.float().numpy()
+    out["ref_rmsnorm_w"] = norm.weight.detach().float().numpy()
+    out["ref_rmsnorm_y"] = norm(x).detach().float().numpy()
+
+
+def hf_fixtures(out):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from transformers.models.llama.modeling_llama import (LlamaMLP, LlamaRMSNorm, LlamaRotaryEmbedding,
+                                                          apply_rotary_pos_emb, repeat_kv)
+
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(1)
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=8,
+                      num_key_value_heads=2, head_dim=32, vocab_size=512, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      max_position_embeddings=128, attention_bias=False, mlp_bias=False, tie_word_embeddings=False)
+    small = LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=32, vocab_size=256, rms_norm_eps=1e-5, rope_theta=500000.0,
+                        max_position_embeddings=128, attention_bias=False, mlp_bias=False,
+                        tie_word_embeddings=False)
+
+    # fused RMSNorm -> linear (config-1 style), fp16 modules evaluated by HF in fp16 on CPU
+    norm = LlamaRMSNorm(256, eps=1e-5)
+    norm.weight.data = 1 + 0.01 * torch.randn(256, generator=g)
+    lin = torch.nn.Linear(256, 384, bias=True)
+    lin.weight.data = torch.randn(384, 256, generator=g) * 0.05
+    lin.bias.data = torch.randn(384, generator=g) * 0.1
+    x = torch.randn(2, 256, generator=g)
+    out["hf_normlinear_x"] = x.numpy()
+    out["hf_normlinear_nw"] = norm.weight.detach().clone().numpy()
+    out["hf_normlinear_w"] = lin.weight.detach().clone().numpy()
+    out["hf_normlinear_b"] = lin.bias.detach().clone().numpy()
+    import copy
+    for dt, tag in ((torch.float32, "f32"), (torch.float16, "f16")):
+        n, l, xx = copy.deepcopy(norm).to(dt), copy.deepcopy(lin).to(dt), x.to(dt)
+        y = l(n(xx))
+        out[f"hf_normlinear_{tag}_y"] = y.detach().float().numpy()
+
+    # MLP
+    mlp = LlamaMLP(cfg)
+    for p in mlp.parameters():
+        p.data = torch.randn(p.shape, generator=g) * 0.05
+    xm = torch.randn(3, 256, generator=g)
+    out["hf_mlp_x"] = xm.numpy()
+    out["hf_mlp_gate"] = mlp.gate_proj.weight.detach().numpy()
+    out["hf_mlp_up"] = mlp.up_proj.weight.detach().numpy()
+    out["hf_mlp_down"] = mlp.down_proj.weight.detach().numpy()
+    out["hf_mlp_y"] = mlp(xm).detach().numpy()
+
+    # rotary embedding tables + application, and eager GQA attention for one query token
+    rot = LlamaRotaryEmbedding(cfg)
+    B, Hq, Hkv, D, S = 2, 8, 2, 32, 37
+    pos = torch.arange(S)[None, :].expand(B, S)
+    cos, sin = rot(torch.zeros(1, dtype=torch.float32), pos)
+    out["hf_rope_cos"] = cos[0].numpy()
+    out["hf_rope_sin"] = sin[0].numpy()
+    q = torch.randn(B, Hq, S, D, generator=g)
+    k = torch.randn(B, Hkv, S, D, generator=g)
+    v = torch.randn(B, Hkv, S, D, generator=g)
+    qr, kr = apply_rotary_pos_emb(q, k, cos, sin)
+    out["hf_rope_q"], out["hf_rope_k"] = q.numpy(), k.numpy()
+    out["hf_rope_q_rot"], out["hf_rope_k_rot"] = qr.numpy(), kr.numpy()
+    q1 = qr[:, :, -1:, :]
+    kk, vv = repeat_kv(kr, Hq // Hkv), repeat_kv(v, Hq // Hkv)
+    att = torch.softmax(torch.matmul(q1, kk.transpose(2, 3)) / (D ** 0.5), dim=-1, dtype=torch.float32)
+    o = torch.matmul(att, vv).transpose(1, 2).reshape(B, 1, Hq * D)
+    out["hf_attn_v"] = v.numpy()
+    out["hf_attn_out"] = o.numpy()
+
+    # whole model: greedy tokens and last-position logits of the prompt
+    # (weights are rounded to fp16 values so that the fixture can store them exactly in 16 bits)
+    model = LlamaForCausalLM(small).eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() > 1:
+                p.copy_((torch.randn(p.shape, generator=g) * 0.08).half().float())
+            else:
+                p.copy_((1 + 0.01 * torch.randn(p.shape, generator=g)).half().float())
+    prompt = torch.randint(0, 256, (1, 16), generator=g)
+    with torch.no_grad():
+        gen = model.generate(prompt, max_new_tokens=32, do_sample=False, pad_token_id=0)
+        logits = model(prompt).logits[:, -1]
+    out["hf_model_prompt"] = prompt.numpy()
+    out["hf_model_tokens"] = gen[:, 16:].numpy()
+    out["hf_model_prompt_logits"] = logits.numpy()
+    sd = model.state_dict()
+    for name, t in sd.items():
+        out["hf_model_sd/" + name] = t.half().numpy()
+
+
+def main():
+    ref, hf = {}, {}
+    # HF first: in this container, running the reference's bf16/fp16 CPU branches first left the later fp32
+    # batched matmul inside LlamaRotaryEmbedding at reduced precision (cos/sin off by 2e-4); in a fresh
+    # interpreter state the tables are exact, which the check below enforces.
+    hf_fixtures(hf)
+    inv = 1.0 / (500000.0 ** (torch.arange(0, 32, 2, dtype=torch.int64).float() / 32))
+    fr = torch.outer(torch.arange(37).float(), inv)
+    assert np.array_equal(hf["hf_rope_cos"], torch.cat((fr, fr), -1).cos().numpy()), "rope tables not exact"
+    reference_fixtures(ref)
+    np.savez_compressed(os.path.join(HERE, "reference_python.npz"), **ref)
+    np.savez_compressed(os.path.join(HERE, "hf_modules.npz"), **hf)
+    for f in ("reference_python.npz", "hf_modules.npz"):
+        print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")
+
+
+if __name__ == "__main__":
+    main()
