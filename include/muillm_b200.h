@@ -98,6 +98,30 @@ MUI_API mui_status_t mui_gateupdown_forward(void* stream, mui_dtype_t dtype, int
                                             const void* up_weights, const void* down_weights, const void* residual,
                                             const void* x, void* scratch_t, void* y, unsigned flags);
 
+/* ---- (a3/a5) weight-only 8-bit GEMV and gate/up ---------------------------------------------------
+ * Same math as mui_linear_forward / mui_gateup_silu_forward on de-quantised weights.
+ * scales: SYM_ROW -> [N] of dtype; GROUP_MIN -> [N * (K >> group_shift), 2] of dtype (scale, min).
+ * Replaces muillm_int8_linear_activ_forward (csrc/int8_linear_kernels.cu:703-784) and
+ * muillm_int8_gateupsilu_forward (csrc/int8_gateup_kernels.cu:871-940). Gate and up are separate [I, H]
+ * matrices with separate scale arrays in both formats; the reference's interleaved [I, H, 2] pack with
+ * [I, G, 2, 2] scale/min (muillm/modules/quantized/int8gateupdownmlp.py:211-230) is split once at load time
+ * (gate = pack[:, :, 0], up = pack[:, :, 1]). SYM_ROW with K % 32 == 0 runs on the bulk-copy pipeline;
+ * GROUP_MIN runs on the plain-load kernel. */
+MUI_API mui_status_t mui_linear_w8_forward(void* stream, mui_dtype_t dtype, mui_w8_format_t fmt, int group_shift,
+                                           int B, int N, int K, const void* norm_weights, float epsilon,
+                                           const void* qweights, const void* scales, mui_activation_t activ,
+                                           const void* mul_bias, const void* add_bias, const void* residual,
+                                           const void* x, void* y, unsigned flags);
+MUI_API mui_status_t mui_gateup_silu_w8_forward(void* stream, mui_dtype_t dtype, mui_w8_format_t fmt,
+                                                int group_shift, int B, int I, int H, const void* norm_weights,
+                                                float epsilon, const void* gate_q, const void* gate_scales,
+                                                const void* up_q, const void* up_scales, const void* x, void* t,
+                                                unsigned flags);
+/* Full de-quantisation to [N,K] of dtype (batched fallback of the reference,
+ * csrc/int8_dequantization_kernel.cu:74). */
+MUI_API mui_status_t mui_w8_dequantize(void* stream, mui_dtype_t dtype, mui_w8_format_t fmt, int group_shift, int N,
+                                       int K, const void* qweights, const void* scales, void* out);
+
 /* ---- (a14) RMSNorm / L2 norm ----------------------------------------------------------------------
  * y[r,:] = round16(round16(x[r,:] * rsqrt(mean(x[r,:]^2) + eps)) * w) ; w == NULL -> no weight (L2 norm of
  * Llama-4, csrc/norm/l2norm_fp16_kernels.cu:35). Replaces muillm_rmsnorm_forward (csrc/norm/rmsnorm.cu:31-84). */
@@ -161,6 +185,41 @@ MUI_API mui_status_t mui_flash_decode_static_scratch(void* stream, mui_dtype_t d
                                                      int S, const int32_t* seq_len_dev, float scale, const void* q,
                                                      const void* k, const void* v, mui_strides3_t kv_strides,
                                                      const void* mask, void* out, unsigned flags);
+
+/* ---- (a6) router top-k + sigmoid -------------------------------------------------------------------
+ * For each of `rows` rows of logits [rows, M] (M <= 4096): the k largest values (ties -> lowest index, as a
+ * stable descending sort orders them), sigmoid in fp32, rounded to dtype; indices int64.
+ * Replaces muillm_topk_sigmoid_forward (csrc/topk/topk.cu:34-93). */
+MUI_API mui_status_t mui_topk_sigmoid_forward(void* stream, mui_dtype_t dtype, int rows, int M, int k,
+                                              const void* logits, void* values, int64_t* indices, unsigned flags);
+
+/* ---- (a7) MoE MLP for one token -------------------------------------------------------------------
+ * Computed experts = the num_shared shared ones (score 1) followed by the top_k routed ones named by
+ * router_indices[top_k] (int64, device; expert e of the routed set uses rows num_shared + e of the packs) with
+ * router_scores[top_k] (dtype, device). gate/up packs are [(num_shared + num_routed) * I, H], the down pack is
+ * [(num_shared + num_routed) * H, I].
+ *   t[s, :] = silu(score_s * G_e xn) * (score_s * U_e xn)        (the score scales the pre-activations,
+ *                                                                  csrc/moeffn/gateupmoe_fp16_kernels.cu:355-360)
+ *   y = sum_s D_e t[s, :] + residual                              (summed inside the down kernel in fp32; the
+ *                                                                  reference writes per-expert rows and reduces,
+ *                                                                  csrc/moeffn/moelinear_fp16_kernels.cu:363-375,
+ *                                                                  csrc/reduce/reduce_fp16_kernels.cu:32)
+ * t is [num_shared + top_k, I] of dtype. mui_moe_down_forward can also leave fp32 sums in y_f32 (tensor-parallel
+ * partials). Replaces muillm_gateupsilumoe_forward (csrc/moeffn/gateupmoe.cu:115-290). */
+MUI_API mui_status_t mui_moe_gateup_silu_forward(void* stream, mui_dtype_t dtype, int num_shared, int num_routed,
+                                                 int top_k, int I, int H, const void* norm_weights, float epsilon,
+                                                 const void* gate_weights, const void* up_weights, const void* x,
+                                                 const void* router_scores, const int64_t* router_indices, void* t,
+                                                 unsigned flags);
+MUI_API mui_status_t mui_moe_down_forward(void* stream, mui_dtype_t dtype, int num_shared, int num_routed, int top_k,
+                                          int H, int I, const void* down_weights, const void* residual,
+                                          const void* t, const int64_t* router_indices, void* y, float* y_f32,
+                                          unsigned flags);
+MUI_API mui_status_t mui_moe_mlp_forward(void* stream, mui_dtype_t dtype, int num_shared, int num_routed, int top_k,
+                                         int I, int H, const void* norm_weights, float epsilon,
+                                         const void* gate_weights, const void* up_weights, const void* down_weights,
+                                         const void* residual, const void* x, const void* router_scores,
+                                         const int64_t* router_indices, void* scratch_t, void* y, unsigned flags);
 
 /* ---- embedding row gather (csrc/embedding/embedding_xx16_kernels.cu:26,74) ------------------------
  * out[i, :] = table[token_ids[i], :] for 16-bit tables [vocab, H]; token ids are int64 on the device and

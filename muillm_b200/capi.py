@@ -92,6 +92,17 @@ PROTOTYPES = {
         [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_uint],
     ),
+    "mui_linear_w8_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_gateup_silu_w8_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_w8_dequantize": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "mui_rmsnorm_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_uint]),
     "mui_rope_forward": (
         c_int,
@@ -113,6 +124,22 @@ PROTOTYPES = {
         c_int,
         [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
          Strides3, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_topk_sigmoid_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint]),
+    "mui_moe_gateup_silu_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_moe_down_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_uint],
+    ),
+    "mui_moe_mlp_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint],
     ),
     "mui_embedding_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_scratch_bytes": (c_size_t, [POINTER(LlamaConfig)]),

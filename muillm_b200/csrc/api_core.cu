@@ -136,6 +136,7 @@ mui_status_t mui_linear_forward(void* stream, mui_dtype_t dtype, int B, int N, i
   a.Kp = (K + 7) & ~7;
   a.moe_mode = GEMV_MOE_NONE;
   a.slots = 1;
+  a.w8_fmt = -1;
   return mui_launch_gemv16((cudaStream_t)stream, dtype, 0, a, flags);
 }
 
@@ -161,6 +162,7 @@ mui_status_t mui_gateup_silu_forward(void* stream, mui_dtype_t dtype, int B, int
   a.Kp = (H + 7) & ~7;
   a.moe_mode = GEMV_MOE_NONE;
   a.slots = 1;
+  a.w8_fmt = -1;
   return mui_launch_gemv16((cudaStream_t)stream, dtype, 1, a, flags);
 }
 

@@ -1,20 +1,20 @@
-// GEMV-shaped kernels on 16-bit weights for one to eight activation rows:
+// GEMV-shaped kernels for one to eight activation rows on 16-bit weights, or on 8-bit weight-only
+// quantised weights (WB = 8; symmetric per-row int8, or uint8 with per-group scale/min):
 //   MODE 0  linear      y = act(W xn) * mul_bias + add_bias + residual
 //   MODE 1  gate/up     t = silu(G xn) * (U xn)
 // plus MoE addressing of either (device-side expert selection).
 //
 // Two implementations of the same math:
-//  * gemv_pipe_kernel    — persistent CTAs (two per SM). One producer warp streams 16 row chunks of
-//                          512 elements per stage into a shared-memory ring with 1-D bulk async copies
-//                          (TMA) completing on mbarriers; eight consumer warps each own two row
-//                          streams, multiply against the activations staged in shared memory and
-//                          finish their rows with warp shuffles — no cross-warp reduction. The weight
-//                          prefetch does not depend on the previous kernel, so under programmatic
-//                          dependent launch it overlaps that kernel's tail.
+//  * gemv_pipe_kernel    — persistent, one CTA per SM. A producer warp streams 16-row tiles in 4 KiB row
+//                          chunks into a shared-memory ring with 1-D bulk async copies (TMA) completing on
+//                          mbarriers; eight consumer warps feed the tiles to mma.sync through ldmatrix
+//                          (8-bit weights are widened in registers with a byte-permute + subtract, no
+//                          conversion instructions). The weight prefetch does not depend on the previous
+//                          kernel, so under programmatic dependent launch it overlaps that kernel's tail.
 //  * gemv_generic_kernel — plain 16-byte streaming loads, the 256 threads of a CTA split K, cross-warp
-//                          reduction in shared memory. Covers any K / alignment.
+//                          reduction in shared memory. Covers any K / alignment and the per-group format.
 //
-// HBM traffic per call: N*K*2 (weights, read once) + activations; fp32 accumulation.
+// HBM traffic per call: N*K*WB/8 (weights, read once) + scales + activations; fp32 accumulation.
 #include "gemv_common.cuh"
 
 #include <algorithm>
@@ -48,7 +48,7 @@ namespace {
 // =============================================================================================
 // generic kernel
 // =============================================================================================
-template <typename T, int NB, int MODE>
+template <typename T, int NB, int MODE, int WB>
 __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   T* x_s = reinterpret_cast<T*>(smem_raw);
@@ -67,10 +67,17 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
     gemv_stage_x<T, NB>(a, a.B, x_s, a.Kp, red, tid);
 
   const int K = a.K, Kp = a.Kp;
-  const T* __restrict__ W = reinterpret_cast<const T*>(a.W);
-  const T* __restrict__ W2 = reinterpret_cast<const T*>(a.W2);
-  const bool vec_ok = ((K & 7) == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0) &&
-                      (MODE == 0 || (reinterpret_cast<uintptr_t>(W2) & 15) == 0);
+  const unsigned char* __restrict__ W = reinterpret_cast<const unsigned char*>(a.W);
+  const unsigned char* __restrict__ W2 = reinterpret_cast<const unsigned char*>(a.W2);
+  constexpr int EB = WB / 8;           // bytes per weight
+  constexpr int VEC = 16 / EB;         // weights per 16-byte load
+  const bool group_fmt = (WB == 8) && (a.w8_fmt == MUI_W8_GROUP_MIN);
+  const bool vec_ok = ((K % VEC) == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0) &&
+                      (MODE == 0 || (reinterpret_cast<uintptr_t>(W2) & 15) == 0) &&
+                      (!group_fmt || a.group_shift >= 4);
+  const int groups_per_row = group_fmt ? (K >> a.group_shift) : 0;
+  const T* __restrict__ SM1 = reinterpret_cast<const T*>(a.scales);
+  const T* __restrict__ SM2 = reinterpret_cast<const T*>(MODE == 0 ? a.scales : a.scales2);
 
   const int num_items = (MODE == 0) ? (total_rows + 1) / 2 : total_rows;
   for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
@@ -83,26 +90,75 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
     for (int b = 0; b < NB; ++b) acc[0][b] = acc[1][b] = 0.f;
 
     for (int seg = 0; seg < nseg; ++seg) {
-      const T* __restrict__ wa = W + gemv_weight_row(a, ra, seg) * (size_t)K;
-      const T* __restrict__ wb = ((MODE == 0) ? W : W2) + gemv_weight_row(a, rb, seg) * (size_t)K;
+      const size_t wrow_a = gemv_weight_row(a, ra, seg), wrow_b = gemv_weight_row(a, rb, seg);
+      const unsigned char* __restrict__ wa = W + wrow_a * (size_t)K * EB;
+      const unsigned char* __restrict__ wb = ((MODE == 0) ? W : W2) + wrow_b * (size_t)K * EB;
       const T* xs = x_s + (size_t)seg * Kp;
       if (vec_ok) {
 #pragma unroll 2
-        for (int k = tid * 8; k < K; k += GEMV_CONSUMER_THREADS * 8) {
-          const uint4 va = ld_stream16(wa + k);
-          const uint4 vb = ld_stream16(wb + k);
+        for (int k = tid * VEC; k < K; k += GEMV_CONSUMER_THREADS * VEC) {
+          const uint4 va = ld_stream16(wa + (size_t)k * EB);
+          const uint4 vb = ld_stream16(wb + (size_t)k * EB);
+          if (WB == 16) {
 #pragma unroll
-          for (int b = 0; b < NB; ++b) {
-            float f[8];
-            unpack8<T>(*reinterpret_cast<const uint4*>(xs + (size_t)b * Kp + k), f);
-            acc[0][b] = dot8<T>(va, f, acc[0][b]);
-            acc[1][b] = dot8<T>(vb, f, acc[1][b]);
+            for (int b = 0; b < NB; ++b) {
+              float f[8];
+              unpack8<T>(*reinterpret_cast<const uint4*>(xs + (size_t)b * Kp + k), f);
+              acc[0][b] = dot8<T>(va, f, acc[0][b]);
+              acc[1][b] = dot8<T>(vb, f, acc[1][b]);
+            }
+          } else {
+            float sa = 1.f, ma = 0.f, sb = 1.f, mb = 0.f;
+            if (group_fmt) {
+              const int g = k >> a.group_shift;
+              sa = Elt<T>::to_f32(SM1[(wrow_a * groups_per_row + g) * 2]);
+              ma = Elt<T>::to_f32(SM1[(wrow_a * groups_per_row + g) * 2 + 1]);
+              sb = Elt<T>::to_f32(SM2[(wrow_b * groups_per_row + g) * 2]);
+              mb = Elt<T>::to_f32(SM2[(wrow_b * groups_per_row + g) * 2 + 1]);
+            }
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+              float f[16];
+              {
+                float lo[8], hi[8];
+                unpack8<T>(*reinterpret_cast<const uint4*>(xs + (size_t)b * Kp + k), lo);
+                unpack8<T>(*reinterpret_cast<const uint4*>(xs + (size_t)b * Kp + k + 8), hi);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  f[i] = lo[i];
+                  f[8 + i] = hi[i];
+                }
+              }
+              if (group_fmt) {
+                // w = q*scale + min inside a group: sum(w x) = scale * sum(q x) + min * sum(x)
+                float xsum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) xsum += f[i];
+                acc[0][b] += sa * dot16_w8<false>(va, f) + ma * xsum;
+                acc[1][b] += sb * dot16_w8<false>(vb, f) + mb * xsum;
+              } else {
+                acc[0][b] += dot16_w8<true>(va, f);
+                acc[1][b] += dot16_w8<true>(vb, f);
+              }
+            }
           }
         }
       } else {
         for (int k = tid; k < K; k += GEMV_CONSUMER_THREADS) {
-          const float fa = Elt<T>::to_f32(wa[k]);
-          const float fb = Elt<T>::to_f32(wb[k]);
+          float fa, fb;
+          if (WB == 16) {
+            fa = Elt<T>::to_f32(reinterpret_cast<const T*>(wa)[k]);
+            fb = Elt<T>::to_f32(reinterpret_cast<const T*>(wb)[k]);
+          } else if (group_fmt) {
+            const int g = k >> a.group_shift;
+            fa = fmaf(static_cast<float>(wa[k]), Elt<T>::to_f32(SM1[(wrow_a * groups_per_row + g) * 2]),
+                      Elt<T>::to_f32(SM1[(wrow_a * groups_per_row + g) * 2 + 1]));
+            fb = fmaf(static_cast<float>(wb[k]), Elt<T>::to_f32(SM2[(wrow_b * groups_per_row + g) * 2]),
+                      Elt<T>::to_f32(SM2[(wrow_b * groups_per_row + g) * 2 + 1]));
+          } else {
+            fa = static_cast<float>(static_cast<signed char>(wa[k]));
+            fb = static_cast<float>(static_cast<signed char>(wb[k]));
+          }
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
             const float xv = Elt<T>::to_f32(xs[(size_t)b * Kp + k]);
@@ -163,8 +219,8 @@ constexpr int PIPE_THREADS = GEMV_CONSUMER_THREADS + 32;
 constexpr int PIPE_MAX_STAGES = 8;
 constexpr int PIPE_XPAD = 8;  // elements of padding per staged activation row (bank spread for ldmatrix)
 
-template <int KC> struct PipeGeom {
-  static constexpr int ROW_PITCH = KC * 2 + 16;               // bytes
+template <int KC, int WB> struct PipeGeom {
+  static constexpr int ROW_PITCH = KC * (WB / 8) + 16;        // bytes
   static constexpr int STAGE_BYTES = PIPE_ROWS * ROW_PITCH;   // bytes
 };
 
@@ -212,9 +268,10 @@ __device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_addr));
 }
 
-template <typename T, int NB, int MODE, int KC>
+template <typename T, int NB, int MODE, int KC, int WB>
 __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs a, const int num_stages) {
-  using G = PipeGeom<KC>;
+  using G = PipeGeom<KC, WB>;
+  constexpr int EB = WB / 8;  // bytes per weight
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int x_rows = (a.moe_mode == GEMV_MOE_SEGMENTS) ? a.slots : NB;
   const PipeLayout lay = pipe_layout(G::STAGE_BYTES, num_stages, x_rows, a.Kp, NB);
@@ -254,8 +311,8 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
     // ------------------------------ producer warp ------------------------------
     if (a.moe_mode != GEMV_MOE_NONE) pdl_wait_prior_grid();  // expert ids come from the previous kernel
     const uint64_t policy = l2_policy_evict_first();
-    const T* __restrict__ W = reinterpret_cast<const T*>(a.W);
-    const T* __restrict__ W2 = reinterpret_cast<const T*>(a.W2);
+    const unsigned char* __restrict__ W = reinterpret_cast<const unsigned char*>(a.W);
+    const unsigned char* __restrict__ W2 = reinterpret_cast<const unsigned char*>(a.W2);
     int issued = 0;
     bool ok = true;
     int blk = 0, c = 0;  // item -> (row block, chunk) without divisions
@@ -276,7 +333,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
       const int seg = c / nchunks, kc = c - seg * nchunks;
       const int rb = r_begin + blk * ROWS_PER_STAGE;
       const int kc_len = min(KC, K - kc * KC);
-      const uint32_t bytes = static_cast<uint32_t>(kc_len) * 2u;
+      const uint32_t bytes = static_cast<uint32_t>(kc_len) * EB;
       const int rows_valid = min(ROWS_PER_STAGE, r_end - rb);
       const int ncopies = (MODE == 0) ? rows_valid : 2 * rows_valid;
       if (lane == 0) mbar_arrive_expect_tx(full_bar + s, static_cast<uint32_t>(ncopies) * bytes);
@@ -285,8 +342,8 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
         // tile row `lane`: MODE 0 -> output row rb + lane; MODE 1 -> gate (lane < 8) / up (lane >= 8) row rb + lane%8
         const int orow = (MODE == 0) ? lane : (lane & 7);
         if (orow < rows_valid) {
-          const T* src = ((MODE == 1 && lane >= 8) ? W2 : W) + gemv_weight_row(a, rb + orow, seg) * (size_t)K +
-                         (size_t)kc * KC;
+          const unsigned char* src = ((MODE == 1 && lane >= 8) ? W2 : W) +
+                                     (gemv_weight_row(a, rb + orow, seg) * (size_t)K + (size_t)kc * KC) * EB;
           bulk_load_1d(stage_mem + (size_t)s * G::STAGE_BYTES + (size_t)lane * G::ROW_PITCH, src, bytes,
                        full_bar + s, policy);
         }
@@ -338,16 +395,56 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
       }
       const int seg = c / nchunks, kc = c - seg * nchunks;
       const int kc_len = min(KC, K - kc * KC);
-      const int nsteps = kc_len >> 4;
       const uint32_t a_addr = stage_base + static_cast<uint32_t>(s) * G::STAGE_BYTES + a_lane_off;
-      // MoE segments: segment `seg` multiplies activation row `seg` (NB == 1 there)
-      const uint32_t b_addr = x_base + b_lane_off + static_cast<uint32_t>((seg * x_pitch + kc * KC) * 2);
+      if (WB == 16) {
+        const int nsteps = kc_len >> 4;
+        // MoE segments: segment `seg` multiplies activation row `seg` (NB == 1 there)
+        const uint32_t b_addr = x_base + b_lane_off + static_cast<uint32_t>((seg * x_pitch + kc * KC) * 2);
 #pragma unroll 4
-      for (int j = warp; j < nsteps; j += GEMV_CONSUMER_WARPS) {
-        uint32_t af[4], b0, b1;
-        ldmatrix_x4(af, a_addr + j * 32);
-        ldmatrix_x2(b0, b1, b_addr + j * 32);
-        MmaOp<T>::run(d, af, b0, b1);
+        for (int j = warp; j < nsteps; j += GEMV_CONSUMER_WARPS) {
+          uint32_t af[4], b0, b1;
+          ldmatrix_x4(af, a_addr + j * 32);
+          ldmatrix_x2(b0, b1, b_addr + j * 32);
+          MmaOp<T>::run(d, af, b0, b1);
+        }
+      } else {
+        // 8-bit weights: one ldmatrix.x4 brings 16 rows x 32 bytes; this thread gets bytes 4q..4q+3 (q = lane%4)
+        // of k-blocks [0,16) and [16,32) for tile rows lane/4 and lane/4+8. The four bytes become the k-slots
+        // {2q,2q+1} and {2q+8,2q+9} of one mma, so the activations are read as x[4q..4q+3] in the same order.
+        const int nsteps = kc_len >> 5;
+        const int n_row = ((lane >> 2) < NB) ? (lane >> 2) : (NB - 1);
+        const T* xrow = x_s + (size_t)(n_row + seg) * x_pitch + (size_t)kc * KC + (lane & 3) * 4;
+        const bool sgn = (a.w8_fmt == MUI_W8_SYM_ROW);
+#pragma unroll 2
+        for (int j = warp; j < nsteps; j += GEMV_CONSUMER_WARPS) {
+          uint32_t r[4];
+          ldmatrix_x4(r, a_addr + j * 32);
+          const uint2 xa = *reinterpret_cast<const uint2*>(xrow + j * 32);
+          const uint2 xb = *reinterpret_cast<const uint2*>(xrow + j * 32 + 16);
+          uint32_t lo0, hi0, lo1, hi1;
+          if (sgn) {
+            W8Cvt<T>::template cvt4<true>(r[0], lo0, hi0);
+            W8Cvt<T>::template cvt4<true>(r[1], lo1, hi1);
+          } else {
+            W8Cvt<T>::template cvt4<false>(r[0], lo0, hi0);
+            W8Cvt<T>::template cvt4<false>(r[1], lo1, hi1);
+          }
+          {
+            const uint32_t af[4] = {lo0, lo1, hi0, hi1};
+            MmaOp<T>::run(d, af, xa.x, xa.y);
+          }
+          if (sgn) {
+            W8Cvt<T>::template cvt4<true>(r[2], lo0, hi0);
+            W8Cvt<T>::template cvt4<true>(r[3], lo1, hi1);
+          } else {
+            W8Cvt<T>::template cvt4<false>(r[2], lo0, hi0);
+            W8Cvt<T>::template cvt4<false>(r[3], lo1, hi1);
+          }
+          {
+            const uint32_t af[4] = {lo0, lo1, hi0, hi1};
+            MmaOp<T>::run(d, af, xb.x, xb.y);
+          }
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar + s);
@@ -400,10 +497,10 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
 // =============================================================================================
 // host dispatch
 // =============================================================================================
-template <typename T, int NB, int MODE, int KC>
+template <typename T, int NB, int MODE, int KC, int WB>
 mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int total_rows, int x_rows,
                          const MuiDeviceInfo* dev, bool* applicable) {
-  using G = PipeGeom<KC>;
+  using G = PipeGeom<KC, WB>;
   // One CTA per SM with (nearly) all of its shared memory: ~190 KiB of copies in flight per SM is what keeps
   // HBM busy; with half of that the kernel runs ~25 % slower.
   const int budget_small = std::min(mui_pipe_smem_kb(), 222) * 1024, budget_full = 222 * 1024;
@@ -420,7 +517,7 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
     return MUI_OK;
   }
   *applicable = true;
-  auto kern = gemv_pipe_kernel<T, NB, MODE, KC>;
+  auto kern = gemv_pipe_kernel<T, NB, MODE, KC, WB>;
   const PipeLayout lay = pipe_layout(G::STAGE_BYTES, stages, x_rows, a.Kp, NB);
   static bool configured = false;  // per instantiation
   if (!configured) {
@@ -435,27 +532,31 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   return MUI_OK;
 }
 
-template <typename T, int NB, int MODE>
+template <typename T, int NB, int MODE, int WB>
 mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flags, const MuiDeviceInfo* dev) {
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
   const int total_rows = (a.moe_mode == GEMV_MOE_ROWS) ? a.slots * a.N : a.N;
   const int x_rows = (a.moe_mode == GEMV_MOE_SEGMENTS) ? a.slots : NB;
   const size_t x_bytes = (size_t)x_rows * a.Kp * 2;
 
-  // the pipeline needs 16-byte aligned rows for the bulk copies and whole k16 steps for the mma
-  const bool aligned = ((a.K & 15) == 0) && ((reinterpret_cast<uintptr_t>(a.W) & 15) == 0) &&
-                       (MODE == 0 || (reinterpret_cast<uintptr_t>(a.W2) & 15) == 0);
+  // The pipeline needs 16-byte aligned rows for the bulk copies and whole mma k-steps (16 weights of 16 bits,
+  // 32 of 8 bits); the per-group 8-bit format runs on the plain-load kernel.
+  const int kstep = (WB == 16) ? 16 : 32;
+  const bool aligned = ((a.K % kstep) == 0) && ((reinterpret_cast<uintptr_t>(a.W) & 15) == 0) &&
+                       (MODE == 0 || (reinterpret_cast<uintptr_t>(a.W2) & 15) == 0) &&
+                       (WB == 16 || a.w8_fmt == MUI_W8_SYM_ROW);
   bool use_pipe = aligned && !(flags & MUI_FLAG_FORCE_GENERIC);
   if (use_pipe) {
     bool applicable = false;
     mui_status_t st;
     const int kc = mui_pipe_kc();
+    // row chunks of 4 KiB: 2048 16-bit or 4096 8-bit weights
     if (kc >= 2048) {
-      st = launch_pipe<T, NB, MODE, 2048>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
+      st = launch_pipe<T, NB, MODE, 2048 * (16 / WB), WB>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
       if (st != MUI_OK || applicable) return st;
     }
     // smaller stages when the staged activations leave no room for two 64 KiB ones
-    st = launch_pipe<T, NB, MODE, 1024>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
+    st = launch_pipe<T, NB, MODE, 1024 * (16 / WB), WB>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
     if (st != MUI_OK || applicable) return st;
   }
   if (flags & MUI_FLAG_FORCE_PIPELINE) {
@@ -466,7 +567,7 @@ mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flag
   // generic
   MUI_REQUIRE(x_bytes <= 200 * 1024, MUI_ERR_UNSUPPORTED,
               "activations (%zu bytes) do not fit the shared-memory staging of the GEMV", x_bytes);
-  auto kern = gemv_generic_kernel<T, NB, MODE>;
+  auto kern = gemv_generic_kernel<T, NB, MODE, WB>;
   static bool configured_g = false;
   if (x_bytes > 48 * 1024 && !configured_g) {
     MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -480,19 +581,29 @@ mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flag
   return MUI_OK;
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, int WB>
 mui_status_t launch_gemv_nb(cudaStream_t stream, const GemvArgs& a, int nb, unsigned flags, const MuiDeviceInfo* dev) {
   switch (nb) {
-    case 1: return launch_gemv_t<T, 1, MODE>(stream, a, flags, dev);
-    case 2: return launch_gemv_t<T, 2, MODE>(stream, a, flags, dev);
-    case 4: return launch_gemv_t<T, 4, MODE>(stream, a, flags, dev);
-    default: return launch_gemv_t<T, 8, MODE>(stream, a, flags, dev);
+    case 1: return launch_gemv_t<T, 1, MODE, WB>(stream, a, flags, dev);
+    case 2: return launch_gemv_t<T, 2, MODE, WB>(stream, a, flags, dev);
+    case 4: return launch_gemv_t<T, 4, MODE, WB>(stream, a, flags, dev);
+    default: return launch_gemv_t<T, 8, MODE, WB>(stream, a, flags, dev);
   }
+}
+
+template <typename T>
+mui_status_t launch_gemv_dt(cudaStream_t stream, int mode, const GemvArgs& a, int nb, unsigned flags,
+                            const MuiDeviceInfo* dev) {
+  if (a.w8_fmt < 0)
+    return mode == 0 ? launch_gemv_nb<T, 0, 16>(stream, a, nb, flags, dev)
+                     : launch_gemv_nb<T, 1, 16>(stream, a, nb, flags, dev);
+  return mode == 0 ? launch_gemv_nb<T, 0, 8>(stream, a, nb, flags, dev)
+                   : launch_gemv_nb<T, 1, 8>(stream, a, nb, flags, dev);
 }
 
 }  // namespace
 
-// Launches MODE 0 (linear) or MODE 1 (gate/up) on validated arguments.
+// Launches MODE 0 (linear) or MODE 1 (gate/up) on validated arguments; a.w8_fmt < 0 means 16-bit weights.
 mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode, const GemvArgs& a, unsigned flags) {
   const MuiDeviceInfo* dev = mui_current_device_info();
   if (!dev) return MUI_ERR_CUDA;
@@ -512,11 +623,6 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
     if (st != MUI_OK) return st;
     return mui_launch_gemv16(stream, dtype, mode, hi, flags);
   }
-  if (dtype == MUI_F16) {
-    return mode == 0 ? launch_gemv_nb<__half, 0>(stream, a, nb, flags, dev)
-                     : launch_gemv_nb<__half, 1>(stream, a, nb, flags, dev);
-  } else {
-    return mode == 0 ? launch_gemv_nb<__nv_bfloat16, 0>(stream, a, nb, flags, dev)
-                     : launch_gemv_nb<__nv_bfloat16, 1>(stream, a, nb, flags, dev);
-  }
+  if (dtype == MUI_F16) return launch_gemv_dt<__half>(stream, mode, a, nb, flags, dev);
+  return launch_gemv_dt<__nv_bfloat16>(stream, mode, a, nb, flags, dev);
 }

@@ -36,6 +36,7 @@ struct GemvArgs {
   int slots;       // computed experts (shared first, then routed), 1 when not MoE
   int num_shared;  // shared experts among the slots
   int group_shift; // 8-bit GROUP_MIN: log2(group size)
+  int w8_fmt;      // -1: 16-bit weights; else mui_w8_format_t of the 8-bit weights
 };
 
 // expert whose weights serve computed slot `slot`
@@ -188,11 +189,62 @@ __device__ __forceinline__ size_t gemv_weight_row(const GemvArgs& a, int r, int 
 }
 
 // ---------------------------------------------------------------------------------------------
+// 8-bit weight helpers
+// ---------------------------------------------------------------------------------------------
+// dot of 16 8-bit weights (signed for SYM_ROW, unsigned for GROUP_MIN) with 16 fp32 activations
+template <bool SIGNED>
+__device__ __forceinline__ float dot16_w8(const uint4& w, const float (&x)[16]) {
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t byte = (ww[i] >> (8 * j)) & 0xffu;
+      const int q = SIGNED ? static_cast<int>(static_cast<signed char>(byte)) : static_cast<int>(byte);
+      acc = fmaf(static_cast<float>(q), x[i * 4 + j], acc);
+    }
+  return acc;
+}
+
+// Four 8-bit integers (one 32-bit register) -> two packed 16-bit pairs {q0,q1}, {q2,q3}, exactly, without
+// integer-to-float conversion instructions: the byte is planted in the mantissa of a constant and the
+// constant subtracted (fp16: 1024 + u; bf16: through fp32 8388608 + u, then one packing conversion).
+template <typename T> struct W8Cvt;
+template <> struct W8Cvt<__half> {
+  template <bool SIGNED>
+  static __device__ __forceinline__ void cvt4(uint32_t r, uint32_t& lo, uint32_t& hi) {
+    const uint32_t v = SIGNED ? (r ^ 0x80808080u) : r;
+    const uint32_t plo = __byte_perm(v, 0x64646464u, 0x5140);
+    const uint32_t phi = __byte_perm(v, 0x64646464u, 0x5342);
+    const __half2 bias = SIGNED ? __floats2half2_rn(1152.f, 1152.f) : __floats2half2_rn(1024.f, 1024.f);
+    __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&plo), bias);
+    __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&phi), bias);
+    lo = *reinterpret_cast<uint32_t*>(&a);
+    hi = *reinterpret_cast<uint32_t*>(&b);
+  }
+};
+template <> struct W8Cvt<__nv_bfloat16> {
+  template <bool SIGNED>
+  static __device__ __forceinline__ void cvt4(uint32_t r, uint32_t& lo, uint32_t& hi) {
+    const uint32_t v = SIGNED ? (r ^ 0x80808080u) : r;
+    const float bias = SIGNED ? 8388736.f : 8388608.f;
+    const float f0 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650)) - bias;
+    const float f1 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7651)) - bias;
+    const float f2 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7652)) - bias;
+    const float f3 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7653)) - bias;
+    lo = Elt<__nv_bfloat16>::pack2(f0, f1);
+    hi = Elt<__nv_bfloat16>::pack2(f2, f3);
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
 // epilogues (one output element). Order follows csrc/linear/linear_fp16_kernels.cu:337-353:
 // activation, * mul_bias, + add_bias, + residual; rounded once.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int n, float v) {
+  if (a.w8_fmt == MUI_W8_SYM_ROW) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[n]);
   if (a.activ == MUI_ACT_SILU) v = silu_f32(v);
   if (a.mul_bias) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.mul_bias)[n]);
   if (a.add_bias) v += Elt<T>::to_f32(reinterpret_cast<const T*>(a.add_bias)[n]);
@@ -207,6 +259,10 @@ __device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int 
 template <typename T>
 __device__ __forceinline__ void gemv_store_gateup(const GemvArgs& a, int b, int out_row, int out_rows_total, float g,
                                                   float u, float score) {
+  if (a.w8_fmt == MUI_W8_SYM_ROW) {
+    g *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[out_row]);
+    u *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales2)[out_row]);
+  }
   g *= score;
   u *= score;
   float t = silu_f32(g) * u;

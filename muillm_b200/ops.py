@@ -204,3 +204,93 @@ def muillm_causal_transformer_decoding_masked(q, k, v, m, flags=0):
     """Same with an additive [B,1,1,S] mask; positions whose mask value is 0 are kept
     (csrc/module.cpp:277, csrc/attention/flash_decoding.cu:307-325)."""
     return _flash_decode(q, k, v, m, flags)
+
+
+def muillm_topk_sigmoid_forward(router_logits, top_k, flags=0):
+    """(sigmoid(top-k values), int64 indices) over the last dim (csrc/module.cpp:253, csrc/topk/topk.cu:34-93)."""
+    _check_input(router_logits, "router_logits")
+    M = router_logits.shape[-1]
+    rows = _rows(router_logits)
+    values = torch.empty(router_logits.shape[:-1] + (top_k,), dtype=router_logits.dtype, device=router_logits.device)
+    indices = torch.empty(router_logits.shape[:-1] + (top_k,), dtype=torch.int64, device=router_logits.device)
+    capi.check(capi.lib().mui_topk_sigmoid_forward(_stream(), _dtype_code(router_logits), rows, M, int(top_k),
+                                                   _ptr(router_logits), _ptr(values), _ptr(indices), flags))
+    return values, indices
+
+
+def muillm_gateupsilumoe_forward(engine, num_shared_experts, num_dynamic_experts, norm_weights, epsilon, gate_weights,
+                                 up_weights, down_weights, residual, x, router_scores, router_indices, flags=0):
+    """MoE MLP for one token (csrc/module.cpp:183, csrc/moeffn/gateupmoe.cu:221-272)."""
+    for t, n in ((x, "x"), (gate_weights, "gate_weights"), (up_weights, "up_weights"), (down_weights, "down_weights"),
+                 (norm_weights, "norm_weights"), (residual, "residual"), (router_scores, "router_scores"),
+                 (router_indices, "router_indices")):
+        _check_input(t, n)
+    if _rows(x) != 1:
+        raise RuntimeError("the MoE kernels serve one token (B*T == 1); batches go to the batched fallback")
+    E = num_shared_experts + num_dynamic_experts
+    H = x.shape[-1]
+    I = gate_weights.shape[0] // E
+    top_k = router_indices.numel()
+    if router_indices.dtype != torch.int64:
+        raise RuntimeError("router_indices must be int64")
+    t = torch.empty((num_shared_experts + top_k, I), dtype=x.dtype, device=x.device)
+    y = torch.empty_like(x)
+    capi.check(capi.lib().mui_moe_mlp_forward(
+        _stream(), _dtype_code(x), num_shared_experts, num_dynamic_experts, top_k, I, H, _ptr(norm_weights),
+        float(epsilon), _ptr(gate_weights), _ptr(up_weights), _ptr(down_weights), _ptr(residual), _ptr(x),
+        _ptr(router_scores), _ptr(router_indices), _ptr(t), _ptr(y), flags))
+    return y
+
+
+def _w8_fmt(qweights):
+    if qweights.dtype == torch.int8:
+        return capi.MUI_W8_SYM_ROW
+    if qweights.dtype == torch.uint8:
+        return capi.MUI_W8_GROUP_MIN
+    raise RuntimeError("quantised weights must be int8 (symmetric per-row) or uint8 (per-group scale/min)")
+
+
+def muillm_int8_linear_forward(x, weights, scales_min_vals, group_size_shift, norm_weights=None, epsilon=0.0,
+                               mul_bias=None, add_bias=None, residual=None, flags=0):
+    """Linear on weight-only 8-bit weights (csrc/module.cpp:181, csrc/int8_linear_kernels.cu:703-784). uint8 weights
+    take the reference's [N*G, 2] scale/min pairs; int8 weights take one scale per output row."""
+    for t, n in ((x, "x"), (weights, "weights"), (scales_min_vals, "scales_min_vals"),
+                 (norm_weights, "norm_weights"), (mul_bias, "mul_bias"), (add_bias, "add_bias"),
+                 (residual, "residual")):
+        _check_input(t, n)
+    N, K = weights.shape
+    B = _rows(x)
+    y = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_linear_w8_forward(
+        _stream(), _dtype_code(x), _w8_fmt(weights), int(group_size_shift), B, N, K, _ptr(norm_weights),
+        float(epsilon), _ptr(weights), _ptr(scales_min_vals), capi.MUI_ACT_IDENTITY, _ptr(mul_bias), _ptr(add_bias),
+        _ptr(residual), _ptr(x), _ptr(y), flags))
+    return y
+
+
+def int8_gateup_silu(x, gate_q, gate_scales, up_q, up_scales, group_size_shift=0, norm_weights=None, epsilon=0.0,
+                     flags=0):
+    """t = silu(G xn) * (U xn) on 8-bit gate/up weights (first kernel of muillm_int8_gateupsilu_forward,
+    csrc/int8_gateup_kernels.cu:871-940)."""
+    for t, n in ((x, "x"), (gate_q, "gate_q"), (up_q, "up_q"), (gate_scales, "gate_scales"),
+                 (up_scales, "up_scales"), (norm_weights, "norm_weights")):
+        _check_input(t, n)
+    I, H = gate_q.shape
+    B = _rows(x)
+    out = torch.empty(x.shape[:-1] + (I,), dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_gateup_silu_w8_forward(
+        _stream(), _dtype_code(x), _w8_fmt(gate_q), int(group_size_shift), B, I, H, _ptr(norm_weights),
+        float(epsilon), _ptr(gate_q), _ptr(gate_scales), _ptr(up_q), _ptr(up_scales), _ptr(x), _ptr(out), flags))
+    return out
+
+
+def muillm_int8_dequantize_forward(weights, scales_min_vals, group_size_shift, dtype=None):
+    """Whole-matrix de-quantisation (csrc/module.cpp:180, csrc/int8_dequantization_kernel.cu:74)."""
+    _check_input(weights, "weights")
+    _check_input(scales_min_vals, "scales_min_vals")
+    N, K = weights.shape
+    out = torch.empty((N, K), dtype=scales_min_vals.dtype, device=weights.device)
+    capi.check(capi.lib().mui_w8_dequantize(_stream(), _dtype_code(scales_min_vals), _w8_fmt(weights),
+                                            int(group_size_shift), N, K, _ptr(weights), _ptr(scales_min_vals),
+                                            _ptr(out)))
+    return out
