@@ -221,6 +221,54 @@ MUI_API mui_status_t mui_moe_mlp_forward(void* stream, mui_dtype_t dtype, int nu
                                          const void* residual, const void* x, const void* router_scores,
                                          const int64_t* router_indices, void* scratch_t, void* y, unsigned flags);
 
+/* ---- (a11/a12) tensor-parallel communicator, one node, one process per GPU ------------------------------
+ * Stands in for muillm_comm_* (csrc/comms/comm.h:12-56, csrc/comms/comm_p2p.cu). Each rank owns a device segment
+ * (allocated by mui_comm_create with cudaMalloc — the only allocation in this library besides the static
+ * scratch above) of 2 generations x world slots x capacity fp32 elements plus per-rank flags; peers map it with
+ * CUDA IPC. Collectives are one-shot: every rank stores its fp32 partials into its slot of every rank's segment
+ * over NVLink, publishes a flag, waits (bounded, 2 s) for all flags and sums the slots of its own segment in rank
+ * order — bit-identical results on all ranks, one rounding. All ranks must issue collectives in the same order
+ * (one host thread per rank), like the reference (csrc/comms/comm_p2p.cu:178-184,1033-1035).
+ * mui_comm_init_local = create + handle exchange over a UNIX socket in /tmp keyed by `key` (rank 0 listens; every
+ * socket wait is bounded by timeout_s, default 60) + open. The three-step form lets the caller move the 64-byte
+ * handles over any transport it has (e.g. torch.distributed). */
+typedef struct mui_comm mui_comm_t;
+#define MUI_COMM_F32 2 /* dtype code of fp32 payloads for mui_comm_all_reduce_sum (besides MUI_F16 / MUI_BF16) */
+MUI_API mui_status_t mui_bootstrap_allgather(int rank, int world, const char* key, const void* blob,
+                                             size_t blob_bytes, void* out, double timeout_s);
+MUI_API size_t mui_comm_ipc_handle_bytes(void);
+MUI_API mui_status_t mui_comm_create(int rank, int world, size_t capacity_elems, mui_comm_t** out);
+MUI_API mui_status_t mui_comm_ipc_handle(mui_comm_t* comm, void* handle_out);
+MUI_API mui_status_t mui_comm_open_peers(mui_comm_t* comm, const void* handles /* world x handle bytes */);
+MUI_API mui_status_t mui_comm_init_local(int rank, int world, const char* key, size_t capacity_elems,
+                                         double timeout_s, mui_comm_t** out);
+MUI_API mui_status_t mui_comm_destroy(mui_comm_t* comm);
+MUI_API mui_status_t mui_comm_info(mui_comm_t* comm, int* rank, int* world, size_t* capacity_elems);
+/* dst = sum over ranks of src, `count` elements of dtype (MUI_F16, MUI_BF16 or MUI_COMM_F32); in place allowed.
+ * Replaces muillm_comm_all_reduce_sum (csrc/comms/comm_p2p.cu:1494-1526). */
+MUI_API mui_status_t mui_comm_all_reduce_sum(mui_comm_t* comm, void* stream, int dtype, const void* src, void* dst,
+                                             size_t count, unsigned flags);
+/* dst (all ranks) = src of rank `root`; bytes a multiple of 4. Replaces muillm_comm_broadcast
+ * (csrc/comms/comm_p2p.cu:1571-1615). */
+MUI_API mui_status_t mui_comm_broadcast(mui_comm_t* comm, void* stream, int root, const void* src, void* dst,
+                                        size_t bytes, unsigned flags);
+/* K-sharded linear with the all-reduce fused into the GEMV kernel: every rank multiplies its [N, K_local] weight
+ * shard with its slice of x, pushes the fp32 partial rows straight from the GEMV epilogue into all ranks' slots,
+ * and the same kernel's tail reduces them into y [B, N] (identical on all ranks). mul_bias applies to every
+ * partial; add_bias and residual enter once, on rank 0 (csrc/parallel_linear_kernels.cu:131-133). Replaces
+ * muillm_parallel_linear_activ_forward with sharding_dim == 1 (csrc/parallel_linear_kernels.cu:50-173). */
+MUI_API mui_status_t mui_parallel_linear_forward(mui_comm_t* comm, void* stream, mui_dtype_t dtype, int B, int N,
+                                                 int K_local, const void* norm_weights, float epsilon,
+                                                 const void* weights, const void* mul_bias, const void* add_bias,
+                                                 const void* residual, const void* x, void* y, unsigned flags);
+/* Sharded MLP: gate/up row-sharded [I_local, H] (no collective), down K-sharded [H, I_local] + fused all-reduce.
+ * Replaces muillm_parallel_gateupsilu_forward (csrc/parallel_gateup_kernels.cu:6-112). */
+MUI_API mui_status_t mui_parallel_gateupdown_forward(mui_comm_t* comm, void* stream, mui_dtype_t dtype, int B,
+                                                     int I_local, int H, const void* norm_weights, float epsilon,
+                                                     const void* gate_weights, const void* up_weights,
+                                                     const void* down_weights, const void* residual, const void* x,
+                                                     void* scratch_t, void* y, unsigned flags);
+
 /* ---- embedding row gather (csrc/embedding/embedding_xx16_kernels.cu:26,74) ------------------------
  * out[i, :] = table[token_ids[i], :] for 16-bit tables [vocab, H]; token ids are int64 on the device and
  * are clamped to [0, vocab). */

@@ -21,6 +21,7 @@ MUI_ERR_COMM = 5
 
 MUI_F16 = 0
 MUI_BF16 = 1
+MUI_COMM_F32 = 2
 
 MUI_ACT_IDENTITY = 0
 MUI_ACT_SILU = 1
@@ -140,6 +141,26 @@ PROTOTYPES = {
         c_int,
         [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_bootstrap_allgather": (c_int, [c_int, c_int, c_char_p, c_void_p, c_size_t, c_void_p, ctypes.c_double]),
+    "mui_comm_ipc_handle_bytes": (c_size_t, []),
+    "mui_comm_create": (c_int, [c_int, c_int, c_size_t, POINTER(c_void_p)]),
+    "mui_comm_ipc_handle": (c_int, [c_void_p, c_void_p]),
+    "mui_comm_open_peers": (c_int, [c_void_p, c_void_p]),
+    "mui_comm_init_local": (c_int, [c_int, c_int, c_char_p, c_size_t, ctypes.c_double, POINTER(c_void_p)]),
+    "mui_comm_destroy": (c_int, [c_void_p]),
+    "mui_comm_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_size_t)]),
+    "mui_comm_all_reduce_sum": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_uint]),
+    "mui_comm_broadcast": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_uint]),
+    "mui_parallel_linear_forward": (
+        c_int,
+        [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_uint],
+    ),
+    "mui_parallel_gateupdown_forward": (
+        c_int,
+        [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_uint],
     ),
     "mui_embedding_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_scratch_bytes": (c_size_t, [POINTER(LlamaConfig)]),

@@ -201,6 +201,10 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
     }
     __syncthreads();
   }
+  if (MODE == 0 && a.use_comm) {
+    __shared__ int s_comm_ok;
+    gemv_comm_tail<T>(a, tid, GEMV_CONSUMER_THREADS, 1, &s_comm_ok);
+  }
 }
 
 // =============================================================================================
@@ -491,6 +495,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
         ++blk;
       }
     }
+    if (MODE == 0 && a.use_comm) gemv_comm_tail<T>(a, tid, GEMV_CONSUMER_THREADS, 1, const_cast<int*>(abort_flag) + 1);
   }
 }
 

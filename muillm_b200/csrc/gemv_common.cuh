@@ -2,7 +2,7 @@
 // GEMV-shaped kernels (linear, gate/up+SiLU, their weight-only 8-bit and MoE variants).
 #pragma once
 
-#include "common.cuh"
+#include "comm_dev.cuh"
 
 #define GEMV_CONSUMER_THREADS 256
 #define GEMV_CONSUMER_WARPS 8
@@ -37,6 +37,8 @@ struct GemvArgs {
   int num_shared;  // shared experts among the slots
   int group_shift; // 8-bit GROUP_MIN: log2(group size)
   int w8_fmt;      // -1: 16-bit weights; else mui_w8_format_t of the 8-bit weights
+  int use_comm;    // tensor-parallel: push the fp32 results to every rank, then all-reduce into y
+  CommDev comm;
 };
 
 // expert whose weights serve computed slot `slot`
@@ -250,8 +252,29 @@ __device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int 
   if (a.add_bias) v += Elt<T>::to_f32(reinterpret_cast<const T*>(a.add_bias)[n]);
   const size_t o = (size_t)b * a.N + n;
   if (a.residual) v += ld_act_f32<T>(reinterpret_cast<const T*>(a.residual) + o);
+  if (a.use_comm) {
+    comm_push(a.comm, o, v);
+    return;
+  }
   if (a.y_f32) a.y_f32[o] = v;
   if (a.y) reinterpret_cast<T*>(a.y)[o] = Elt<T>::from_f32(v);
+}
+
+// Tail of a tensor-parallel GEMV: called by all `nthreads` threads that ran the epilogues (they synchronise on
+// named barrier `bar_id`), after the CTA's last push. Publishes this rank's flags once the whole grid has
+// pushed, waits for every rank, then this CTA reduces its slice of the B*N outputs into y.
+template <typename T>
+__device__ __forceinline__ void gemv_comm_tail(const GemvArgs& a, int tid, int nthreads, int bar_id, int* s_ok) {
+  if (tid == 0) *s_ok = 1;
+  named_bar_sync(bar_id, nthreads);
+  if (tid == 0) comm_cta_arrive_and_publish(a.comm, gridDim.x);
+  if (tid < a.comm.world && !comm_wait_rank(a.comm, tid)) *s_ok = 0;
+  named_bar_sync(bar_id, nthreads);
+  if (!*s_ok) return;
+  const long long total = (long long)a.B * a.N;
+  const long long e0 = total * blockIdx.x / gridDim.x, e1 = total * (blockIdx.x + 1) / gridDim.x;
+  T* y = reinterpret_cast<T*>(a.y);
+  for (long long i = e0 + tid; i < e1; i += nthreads) y[i] = Elt<T>::from_f32(comm_reduce_elem(a.comm, (size_t)i));
 }
 
 // gate/up: t = silu(s*g) * (s*u); s is the router score of the slot (1 for dense / shared experts),
