@@ -33,42 +33,29 @@ struct mui_comm {
   size_t seg_bytes;
   unsigned char* seg[MUI_COMM_MAX_RANKS];  // seg[rank] is local, the others are IPC mappings
   bool opened[MUI_COMM_MAX_RANKS];
-  unsigned long long seq;
   bool ready;
 };
 
 namespace {
 
-constexpr size_t SEG_FLAGS_OFF = 0;       // world x u64, 128 bytes apart
-constexpr size_t SEG_COUNTER_OFF = 1024;  // u32 arrival counter (local use only)
-constexpr size_t SEG_DATA_OFF = 4096;
-constexpr size_t FLAG_STRIDE = MUI_COMM_FLAG_STRIDE;  // in u64 units (128 bytes)
+constexpr size_t SEG_SEQ_OFF = 0;       // u64 sequence counter (local use only)
+constexpr size_t SEG_COUNTER_OFF = 128;  // u32 arrival counter (local use only)
+constexpr size_t SEG_DATA_OFF = 4096;    // cells [2][world][capacity] of 8 bytes
 
-size_t seg_size(int world, size_t capacity) { return SEG_DATA_OFF + 2 * (size_t)world * capacity * sizeof(float); }
+size_t seg_size(int world, size_t capacity) { return SEG_DATA_OFF + 2 * (size_t)world * capacity * 8; }
 
-// Pointers of the next collective (advances the sequence number).
+// Device view of the communicator (the same for every collective: the sequence number lives on the device).
 void fill_dev(mui_comm* c, CommDev* d) {
-  c->seq += 1;
-  const int gen = static_cast<int>(c->seq & 1);
   memset(d, 0, sizeof(*d));
-  for (int p = 0; p < c->world; ++p) {
-    float* data = reinterpret_cast<float*>(c->seg[p] + SEG_DATA_OFF);
-    d->push_dst[p] = data + ((size_t)gen * c->world + c->rank) * c->capacity;
-    d->flag_dst[p] = reinterpret_cast<unsigned long long*>(c->seg[p] + SEG_FLAGS_OFF) + (size_t)c->rank * FLAG_STRIDE;
-  }
+  for (int p = 0; p < c->world; ++p)
+    d->peer_cells[p] = reinterpret_cast<unsigned long long*>(c->seg[p] + SEG_DATA_OFF);
   unsigned char* me = c->seg[c->rank];
-  d->local_slots = reinterpret_cast<const float*>(me + SEG_DATA_OFF) + (size_t)gen * c->world * c->capacity;
-  d->local_flags = reinterpret_cast<const unsigned long long*>(me + SEG_FLAGS_OFF);
+  d->local_seq = reinterpret_cast<unsigned long long*>(me + SEG_SEQ_OFF);
   d->arrive_counter = reinterpret_cast<unsigned int*>(me + SEG_COUNTER_OFF);
-  d->seq = c->seq;
   d->world = c->world;
   d->rank = c->rank;
   d->capacity = static_cast<int>(c->capacity);
 }
-
-}  // namespace
-
-namespace {
 
 constexpr int AR_THREADS = 256;
 
@@ -84,40 +71,47 @@ template <> struct ArIO<float> {
 // Stand-alone all-reduce: dst = sum over ranks of src (count elements), same protocol as the fused GEMV tail.
 template <typename T>
 __global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(const CommDev c, const T* src, T* dst, long long count) {
-  __shared__ int s_ok;
   pdl_wait_prior_grid();
   pdl_launch_dependents();
   const int tid = threadIdx.x;
+  const unsigned long long seq = comm_begin(c);
   const long long e0 = count * blockIdx.x / gridDim.x, e1 = count * (blockIdx.x + 1) / gridDim.x;
-  for (long long i = e0 + tid; i < e1; i += AR_THREADS) comm_push(c, (size_t)i, ArIO<T>::ld(src + i));
-  if (tid == 0) s_ok = 1;
+  for (long long i = e0 + tid; i < e1; i += AR_THREADS) comm_push(c, seq, (size_t)i, ArIO<T>::ld(src + i));
+  for (long long i = e0 + tid; i < e1; i += AR_THREADS) {
+    float v;
+    if (comm_reduce_elem(c, seq, (size_t)i, &v)) ArIO<T>::st(dst + i, v);
+  }
   __syncthreads();
-  if (tid == 0) comm_cta_arrive_and_publish(c, gridDim.x);
-  if (tid < c.world && !comm_wait_rank(c, tid)) s_ok = 0;
-  __syncthreads();
-  if (!s_ok) return;
-  for (long long i = e0 + tid; i < e1; i += AR_THREADS) ArIO<T>::st(dst + i, comm_reduce_elem(c, (size_t)i));
+  if (tid == 0) comm_cta_done(c, seq, gridDim.x);
 }
 
-// Broadcast of `words` 32-bit words from rank `root`: the root pushes, everybody publishes and waits for every
-// flag (keeps the generation-reuse argument the same as for the all-reduce), then copies the root's slot out.
+// Broadcast of `words` 32-bit words from rank `root`: the root pushes the words (as cell payloads), the others
+// push one arrival token; every rank polls the root's cells of its own segment and copies them out.
 __global__ void __launch_bounds__(AR_THREADS) broadcast_kernel(const CommDev c, int root, const unsigned int* src,
                                                                unsigned int* dst, long long words) {
-  __shared__ int s_ok;
   pdl_wait_prior_grid();
   pdl_launch_dependents();
   const int tid = threadIdx.x;
+  const unsigned long long seq = comm_begin(c);
   const long long e0 = words * blockIdx.x / gridDim.x, e1 = words * (blockIdx.x + 1) / gridDim.x;
-  if (c.rank == root)
-    for (long long i = e0 + tid; i < e1; i += AR_THREADS) comm_push(c, (size_t)i, __uint_as_float(__ldcg(src + i)));
-  if (tid == 0) s_ok = 1;
+  if (c.rank == root) {
+    for (long long i = e0 + tid; i < e1; i += AR_THREADS)
+      comm_push(c, seq, (size_t)i, __uint_as_float(__ldcg(src + i)));
+  } else if (blockIdx.x == 0 && tid == 0) {
+    comm_push(c, seq, 0, 0.f);  // arrival token in this rank's own slot
+  }
+  for (long long i = e0 + tid; i < e1; i += AR_THREADS) {
+    float v;
+    if (comm_take(c, seq, root, (size_t)i, &v)) dst[i] = __float_as_uint(v);
+  }
+  // every rank also waits for every other rank's token: a rank leaves the collective only when all peers have
+  // entered it, which is what lets the next-but-one collective reuse this generation's cells
+  if (blockIdx.x == 0 && tid < c.world) {
+    float v;
+    comm_take(c, seq, tid, 0, &v);
+  }
   __syncthreads();
-  if (tid == 0) comm_cta_arrive_and_publish(c, gridDim.x);
-  if (tid < c.world && !comm_wait_rank(c, tid)) s_ok = 0;
-  __syncthreads();
-  if (!s_ok) return;
-  const float* slot = c.local_slots + (size_t)root * c.capacity;
-  for (long long i = e0 + tid; i < e1; i += AR_THREADS) dst[i] = __float_as_uint(__ldcg(slot + i));
+  if (tid == 0) comm_cta_done(c, seq, gridDim.x);
 }
 
 mui_status_t check_ready(mui_comm* c) {

@@ -1,83 +1,94 @@
 // Device side of the one-shot "push" all-reduce over peer memory (NVLink / NVSwitch), shared by the
 // stand-alone collective kernels and the GEMV epilogue.
 //
-// Every rank owns a segment [2 generations][world][capacity] of fp32 partial sums plus one 64-bit flag per
-// source rank. A collective with sequence number s (generation s & 1) runs as:
-//   1. each rank stores its fp32 partial for element i into slot [gen][my_rank][i] of EVERY rank's segment
-//      (plain 4/16-byte stores to peer pointers; posted writes, nothing is read remotely);
-//   2. when all of a rank's stores are issued (all CTAs arrived on a local counter), one thread does
-//      __threadfence_system() and writes s into flag[my_rank] of every rank with st.release.sys;
-//   3. each rank waits until its local flags of all ranks are >= s (ld.acquire.sys, bounded spin), then sums the
-//      world slots of its own segment in rank order 0..P-1 in fp32 and rounds once — every rank gets the same
-//      bits. A wait that runs out records MUI_DEV_TIMEOUT_PEER with the late rank and skips the sum.
-// A rank may overwrite generation g for collective s+2 only after it left collective s+1, where it saw every
-// peer's flag s+1, which a peer publishes only after its own reads of collective s are done: no trailing barrier.
+// Every rank owns a segment of 8-byte cells [2 generations][world][capacity] and a device-resident sequence
+// counter. A cell carries one fp32 partial sum in its low half and the 32-bit sequence number of the collective
+// that wrote it in its high half; the two travel in ONE 64-bit store, so a reader that sees the expected
+// sequence number also sees the value — no fence, no separate flag, no remote read:
+//   1. the owner of output element i stores {partial, s} into cell [s & 1][my_rank][i] of EVERY rank's segment
+//      (plain 64-bit stores to peer pointers; posted writes);
+//   2. the same thread block then polls the world cells of element i in its own segment until each shows
+//      sequence s (relaxed system-scope loads of local memory, bounded spin) and adds them in rank order 0..P-1
+//      in fp32, rounding once — every rank gets the same bits. A wait that runs out records
+//      MUI_DEV_TIMEOUT_PEER with the late rank and leaves the output element untouched;
+//   3. the last CTA of the grid to finish advances the sequence counter (read from device memory at kernel
+//      start, so a launch captured in a CUDA graph replays correctly).
+// Generation g is overwritten for collective s+2 only after this rank's kernel of collective s+1 completed, in
+// which it received every peer's s+1 cells, and a peer writes those only from a kernel that started after its
+// own kernel of collective s (which read generation g) completed: no barrier is needed.
 #pragma once
 
 #include "common.cuh"
 
 #define MUI_COMM_MAX_RANKS 8
 #define MUI_COMM_WAIT_NS 2000000000ull
-#define MUI_COMM_FLAG_STRIDE 16  // u64 words between two ranks' flags (128 bytes)
 
 struct CommDev {
-  float* push_dst[MUI_COMM_MAX_RANKS];               // rank p's segment: &data[gen][my_rank][0]
-  unsigned long long* flag_dst[MUI_COMM_MAX_RANKS];  // rank p's segment: &flags[my_rank]
-  const float* local_slots;                          // my segment: &data[gen][0][0]
-  const unsigned long long* local_flags;             // my segment: &flags[0]
-  unsigned int* arrive_counter;                      // local, zero between collectives
-  unsigned long long seq;
+  unsigned long long* peer_cells[MUI_COMM_MAX_RANKS];  // rank p's cell array
+  unsigned long long* local_seq;                       // collectives completed on this rank
+  unsigned int* arrive_counter;                        // local, zero between collectives
   int world, rank;
-  int capacity;  // elements per slot
+  int capacity;  // cells per slot
 };
 
-__device__ __forceinline__ void comm_push(const CommDev& c, size_t idx, float v) {
+__device__ __forceinline__ unsigned long long comm_begin(const CommDev& c) { return __ldcg(c.local_seq) + 1ull; }
+
+__device__ __forceinline__ void comm_push(const CommDev& c, unsigned long long seq, size_t idx, float v) {
+  const size_t off = ((size_t)(seq & 1ull) * c.world + c.rank) * c.capacity + idx;
+  const unsigned long long cell = ((seq & 0xffffffffull) << 32) | (unsigned long long)__float_as_uint(v);
 #pragma unroll
   for (int p = 0; p < MUI_COMM_MAX_RANKS; ++p)
-    if (p < c.world) c.push_dst[p][idx] = v;
+    if (p < c.world) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(c.peer_cells[p] + off), "l"(cell) : "memory");
 }
 
-__device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
   unsigned long long v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
 
-// Called by one thread of each CTA after the CTA's pushes are complete (a CTA-wide barrier precedes it).
-// The last CTA of the grid publishes the flags.
-__device__ __forceinline__ void comm_cta_arrive_and_publish(const CommDev& c, unsigned num_ctas) {
-  __threadfence_system();
-  const unsigned prev = atomicAdd(c.arrive_counter, 1u);
-  if (prev == num_ctas - 1) {
-    *c.arrive_counter = 0u;
-    __threadfence_system();
-    for (int p = 0; p < c.world; ++p) st_release_sys_u64(c.flag_dst[p], c.seq);
-  }
-}
-
-// Thread r < world waits for rank r's flag. Returns false (and records the status) on timeout.
-__device__ __forceinline__ bool comm_wait_rank(const CommDev& c, int r) {
-  const unsigned long long* f = c.local_flags + (size_t)r * MUI_COMM_FLAG_STRIDE;
-  if (ld_acquire_sys_u64(f) >= c.seq) return true;
-  const uint64_t t0 = global_timer_ns();
-  unsigned spins = 0;
-  while (ld_acquire_sys_u64(f) < c.seq) {
-    if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > MUI_COMM_WAIT_NS) {
-      mui_dev_set_status(MUI_DEV_TIMEOUT_PEER, static_cast<unsigned>(r));
-      return false;
+// Polls rank r's cell of element idx until it carries `seq`; returns false (status recorded) on timeout.
+__device__ __forceinline__ bool comm_take(const CommDev& c, unsigned long long seq, int r, size_t idx, float* out) {
+  const unsigned long long* cell = c.peer_cells[c.rank] + ((size_t)(seq & 1ull) * c.world + r) * c.capacity + idx;
+  const unsigned want = static_cast<unsigned>(seq & 0xffffffffull);
+  unsigned long long v = ld_relaxed_sys_u64(cell);
+  if (static_cast<unsigned>(v >> 32) != want) {
+    const uint64_t t0 = global_timer_ns();
+    unsigned spins = 0;
+    while (true) {
+      v = ld_relaxed_sys_u64(cell);
+      if (static_cast<unsigned>(v >> 32) == want) break;
+      if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > MUI_COMM_WAIT_NS) {
+        mui_dev_set_status(MUI_DEV_TIMEOUT_PEER, static_cast<unsigned>(r));
+        return false;
+      }
     }
   }
+  *out = __uint_as_float(static_cast<unsigned>(v & 0xffffffffull));
   return true;
 }
 
-// Sum of the world slots for element idx, fixed rank order, fp32.
-__device__ __forceinline__ float comm_reduce_elem(const CommDev& c, size_t idx) {
+// Sum over ranks of element idx in fixed rank order; false if a rank's cell never arrived.
+__device__ __forceinline__ bool comm_reduce_elem(const CommDev& c, unsigned long long seq, size_t idx, float* out) {
   float s = 0.f;
+  bool ok = true;
 #pragma unroll
-  for (int r = 0; r < MUI_COMM_MAX_RANKS; ++r)
-    if (r < c.world) s += __ldcg(c.local_slots + (size_t)r * c.capacity + idx);
-  return s;
+  for (int r = 0; r < MUI_COMM_MAX_RANKS; ++r) {
+    if (r < c.world) {
+      float v = 0.f;
+      ok = comm_take(c, seq, r, idx, &v) && ok;
+      s += v;
+    }
+  }
+  *out = s;
+  return ok;
+}
+
+// One thread per CTA, when the CTA is done with the collective: the last CTA of the grid advances the counter.
+__device__ __forceinline__ void comm_cta_done(const CommDev& c, unsigned long long seq, unsigned num_ctas) {
+  const unsigned prev = atomicAdd(c.arrive_counter, 1u);
+  if (prev == num_ctas - 1) {
+    *c.arrive_counter = 0u;
+    *c.local_seq = seq;
+  }
 }

@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
 
   const int nseg = (a.moe_mode == GEMV_MOE_SEGMENTS) ? a.slots : 1;
   const int total_rows = (a.moe_mode == GEMV_MOE_ROWS) ? a.slots * a.N : a.N;
+  const unsigned long long comm_seq = (MODE == 0 && a.use_comm) ? comm_begin(a.comm) : 0ull;
   if (a.moe_mode == GEMV_MOE_SEGMENTS)
     gemv_stage_x_plain<T>(a, a.slots, x_s, a.Kp, tid);
   else
@@ -183,7 +184,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) s += red[(w * 2 + j) * NB + b];
-        if (b < a.B && (j == 0 || second_valid)) gemv_store_linear<T>(a, b, j == 0 ? ra : rb, s);
+        if (b < a.B && (j == 0 || second_valid)) gemv_store_linear<T>(a, b, j == 0 ? ra : rb, s, comm_seq);
       }
     } else {
       if (tid < NB) {
@@ -202,8 +203,13 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
     __syncthreads();
   }
   if (MODE == 0 && a.use_comm) {
-    __shared__ int s_comm_ok;
-    gemv_comm_tail<T>(a, tid, GEMV_CONSUMER_THREADS, 1, &s_comm_ok);
+    // rows of this CTA: items blockIdx.x, blockIdx.x + gridDim.x, ... hold rows 2*item and 2*item + 1
+    const int my_items = (num_items > (int)blockIdx.x) ? (num_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    int my_rows = 2 * my_items;
+    if (my_items > 0 && 2 * ((int)blockIdx.x + (my_items - 1) * (int)gridDim.x) + 1 >= total_rows) my_rows -= 1;
+    const int gx = gridDim.x, bx = blockIdx.x;
+    gemv_comm_tail<T>(a, comm_seq, tid, GEMV_CONSUMER_THREADS, 1, my_rows,
+                      [gx, bx](int i) { return 2 * (bx + (i >> 1) * gx) + (i & 1); });
   }
 }
 
@@ -370,6 +376,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
   } else {
     // ------------------------------ consumer warps ------------------------------
     pdl_wait_prior_grid();
+    const unsigned long long comm_seq = (MODE == 0 && a.use_comm) ? comm_begin(a.comm) : 0ull;
     if (a.moe_mode == GEMV_MOE_SEGMENTS)
       gemv_stage_x_plain<T>(a, a.slots, x_s, x_pitch, tid);
     else
@@ -478,7 +485,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
               float v = 0.f;
 #pragma unroll
               for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) v += rbuf[(w * PIPE_ROWS + r) * NB + b];
-              gemv_store_linear<T>(a, b, row, v);
+              gemv_store_linear<T>(a, b, row, v, comm_seq);
             } else {
               float g = 0.f, u = 0.f;
 #pragma unroll
@@ -495,7 +502,9 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
         ++blk;
       }
     }
-    if (MODE == 0 && a.use_comm) gemv_comm_tail<T>(a, tid, GEMV_CONSUMER_THREADS, 1, const_cast<int*>(abort_flag) + 1);
+    if (MODE == 0 && a.use_comm)
+      gemv_comm_tail<T>(a, comm_seq, tid, GEMV_CONSUMER_THREADS, 1, r_end - r_begin,
+                        [r_begin](int i) { return r_begin + i; });
   }
 }
 
@@ -581,7 +590,7 @@ mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flag
   const int num_items = (MODE == 0) ? (total_rows + 1) / 2 : total_rows;
   int per_sm = (int)std::min<size_t>(6, (size_t)(224 * 1024) / (x_bytes + 2048));
   per_sm = std::max(per_sm, 1);
-  const int grid = std::max(1, std::min(num_items, dev->sm_count * per_sm));
+  int grid = std::max(1, std::min(num_items, dev->sm_count * per_sm));
   MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(GEMV_CONSUMER_THREADS), x_bytes, stream, pdl, a));
   return MUI_OK;
 }

@@ -245,7 +245,8 @@ template <> struct W8Cvt<__nv_bfloat16> {
 // activation, * mul_bias, + add_bias, + residual; rounded once.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int n, float v) {
+__device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int n, float v,
+                                                  unsigned long long comm_seq = 0) {
   if (a.w8_fmt == MUI_W8_SYM_ROW) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[n]);
   if (a.activ == MUI_ACT_SILU) v = silu_f32(v);
   if (a.mul_bias) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.mul_bias)[n]);
@@ -253,7 +254,7 @@ __device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int 
   const size_t o = (size_t)b * a.N + n;
   if (a.residual) v += ld_act_f32<T>(reinterpret_cast<const T*>(a.residual) + o);
   if (a.use_comm) {
-    comm_push(a.comm, o, v);
+    comm_push(a.comm, comm_seq, o, v);
     return;
   }
   if (a.y_f32) a.y_f32[o] = v;
@@ -261,20 +262,22 @@ __device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int 
 }
 
 // Tail of a tensor-parallel GEMV: called by all `nthreads` threads that ran the epilogues (they synchronise on
-// named barrier `bar_id`), after the CTA's last push. Publishes this rank's flags once the whole grid has
-// pushed, waits for every rank, then this CTA reduces its slice of the B*N outputs into y.
-template <typename T>
-__device__ __forceinline__ void gemv_comm_tail(const GemvArgs& a, int tid, int nthreads, int bar_id, int* s_ok) {
-  if (tid == 0) *s_ok = 1;
-  named_bar_sync(bar_id, nthreads);
-  if (tid == 0) comm_cta_arrive_and_publish(a.comm, gridDim.x);
-  if (tid < a.comm.world && !comm_wait_rank(a.comm, tid)) *s_ok = 0;
-  named_bar_sync(bar_id, nthreads);
-  if (!*s_ok) return;
-  const long long total = (long long)a.B * a.N;
-  const long long e0 = total * blockIdx.x / gridDim.x, e1 = total * (blockIdx.x + 1) / gridDim.x;
+// named barrier `bar_id`), after the CTA's last push. The CTA reduces the rows it owns — the same rows the
+// same CTA of every other rank pushed — into y, polling its own segment until each rank's cells arrived.
+// `row_of(i)` enumerates the CTA's rows.
+template <typename T, typename RowFn>
+__device__ __forceinline__ void gemv_comm_tail(const GemvArgs& a, unsigned long long seq, int tid, int nthreads,
+                                               int bar_id, int num_rows, RowFn row_of) {
   T* y = reinterpret_cast<T*>(a.y);
-  for (long long i = e0 + tid; i < e1; i += nthreads) y[i] = Elt<T>::from_f32(comm_reduce_elem(a.comm, (size_t)i));
+  const int total = num_rows * a.B;
+  for (int i = tid; i < total; i += nthreads) {
+    const int b = i / num_rows, n = row_of(i - b * num_rows);
+    const size_t o = (size_t)b * a.N + n;
+    float v;
+    if (comm_reduce_elem(a.comm, seq, o, &v)) y[o] = Elt<T>::from_f32(v);
+  }
+  named_bar_sync(bar_id, nthreads);
+  if (tid == 0) comm_cta_done(a.comm, seq, gridDim.x);
 }
 
 // gate/up: t = silu(s*g) * (s*u); s is the router score of the slot (1 for dense / shared experts),
