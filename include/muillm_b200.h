@@ -294,6 +294,11 @@ typedef struct mui_llama_config {
   int batch;        /* 1..8 sequences decoded together */
   float rms_eps;
   float attn_scale; /* softmax scale, normally 1/sqrt(head_dim) */
+  /* Tensor parallelism (both 0 on one GPU): heads, kv_heads, intermediate and vocab above are then this rank's
+   * shard sizes; embed_vocab = rows of the (replicated) embedding table; vocab_offset = first token id of this
+   * rank's lm_head rows. */
+  int embed_vocab;
+  int vocab_offset;
 } mui_llama_config_t;
 
 typedef struct mui_llama_weights {
@@ -319,6 +324,13 @@ MUI_API size_t mui_llama_stack_scratch_bytes(const mui_llama_config_t* cfg);
 MUI_API mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_llama_weights_t* weights,
                                             void* scratch, size_t scratch_bytes, mui_llama_stack_t** out);
 MUI_API mui_status_t mui_llama_stack_destroy(mui_llama_stack_t* stack);
+/* Tensor-parallel decode: with a communicator of world > 1 attached, the weights are this rank's shards — QKV and
+ * gate/up by output rows (whole heads per rank), o_proj and down by input columns with the all-reduce fused into
+ * their GEMV (residual on rank 0), lm_head by rows with the arg-max finished by exchanging each rank's best
+ * (value, token) pair — the sharding of muillm/modules/parallelmultilinear.py:323-387,
+ * parallelgateupdownmlp.py:88-117, except the lm_head, which the reference shards by columns and all-reduces
+ * (muillm/modules/models/llama/model.py:655-664). All ranks must step together. */
+MUI_API mui_status_t mui_llama_stack_set_comm(mui_llama_stack_t* stack, mui_comm_t* comm);
 /* Sets the device-side state: `position` tokens are already in the cache (the next step writes row `position`),
  * per-sequence RoPE positions (host array of `batch` int64, NULL = position for all), and the device buffer
  * [out_capacity, batch] int64 that receives each step's arg-max token (may be NULL). Drops a captured graph. */

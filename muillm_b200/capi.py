@@ -59,6 +59,8 @@ class LlamaConfig(Structure):
         ("batch", c_int),
         ("rms_eps", c_float),
         ("attn_scale", c_float),
+        ("embed_vocab", c_int),
+        ("vocab_offset", c_int),
     ]
 
 
@@ -167,6 +169,7 @@ PROTOTYPES = {
     "mui_llama_stack_create": (
         c_int, [POINTER(LlamaConfig), POINTER(LlamaWeights), c_void_p, c_size_t, POINTER(c_void_p)]),
     "mui_llama_stack_destroy": (c_int, [c_void_p]),
+    "mui_llama_stack_set_comm": (c_int, [c_void_p, c_void_p]),
     "mui_llama_stack_reset": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), c_void_p, c_int]),
     "mui_llama_stack_set_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
     "mui_llama_stack_step": (c_int, [c_void_p, c_void_p, c_uint]),

@@ -114,6 +114,18 @@ __global__ void __launch_bounds__(AR_THREADS) broadcast_kernel(const CommDev c, 
   if (tid == 0) comm_cta_done(c, seq, gridDim.x);
 }
 
+}  // namespace
+
+// Device view for other translation units (decode stack).
+mui_status_t mui_comm_device_view(mui_comm* c, CommDev* out) {
+  MUI_REQUIRE(c != nullptr && out != nullptr, MUI_ERR_INVALID_ARG, "null pointer");
+  MUI_REQUIRE(c->ready, MUI_ERR_COMM, "communicator peers are not opened yet");
+  fill_dev(c, out);
+  return MUI_OK;
+}
+
+namespace {
+
 mui_status_t check_ready(mui_comm* c) {
   MUI_REQUIRE(c != nullptr, MUI_ERR_INVALID_ARG, "comm is null");
   MUI_REQUIRE(c->ready, MUI_ERR_COMM, "communicator peers are not opened yet");

@@ -1,7 +1,9 @@
 // Small kernels around the decode step: embedding row gather, greedy arg-max with the device-side
 // bookkeeping that lets a whole decode step replay from a CUDA graph (positions, sequence length and the
 // token fed to the next step all live in device memory).
-#include "common.cuh"
+#include "comm_dev.cuh"
+
+#include <cstring>
 
 MUI_STATUS_ACCESSOR(misc)
 
@@ -45,7 +47,8 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_advance_kernel(const T*
                                                                         long long* state, int32_t* seq_len32,
                                                                         long long* out_tokens, int out_capacity,
                                                                         float* partial_val, int* partial_idx,
-                                                                        unsigned int* counters) {
+                                                                        unsigned int* counters, int use_comm,
+                                                                        int index_offset, const CommDev comm) {
   __shared__ float s_val[ARGMAX_THREADS / 32];
   __shared__ int s_idx[ARGMAX_THREADS / 32];
   __shared__ int s_last;
@@ -121,6 +124,7 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_advance_kernel(const T*
   // the last CTA of the whole launch finishes every row (warp w takes row w; B <= 8 warps)
   __threadfence();
   const long long step = __ldcg(state);
+  const unsigned long long comm_seq = use_comm ? comm_begin(comm) : 0ull;
   if (warp < B) {
     const int r = warp;
     best = -INFINITY;
@@ -142,8 +146,36 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_advance_kernel(const T*
         best_i = oi;
       }
     }
+    if (best_i == 0x7fffffff) best_i = 0;  // all NaN / empty
+    best_i += index_offset;                // rows of a vocabulary shard -> global token id
+    if (use_comm) {
+      // tensor-parallel lm_head sharded by rows: exchange each rank's (value, token) pair and keep the best
+      // (lowest token id on ties) — every rank picks the same winner
+      if (lane == 0) {
+        comm_push(comm, comm_seq, 2 * r, best);
+        comm_push(comm, comm_seq, 2 * r + 1, __int_as_float(best_i));
+      }
+      float gv = -INFINITY;
+      int gi = 0x7fffffff;
+      if (lane < comm.world) {
+        float v = -INFINITY, fi = 0.f;
+        if (comm_take(comm, comm_seq, lane, 2 * r, &v) && comm_take(comm, comm_seq, lane, 2 * r + 1, &fi)) {
+          gv = v;
+          gi = __float_as_int(fi);
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(MUI_FULL_MASK, gv, o);
+        const int oi = __shfl_xor_sync(MUI_FULL_MASK, gi, o);
+        if (argmax_better(ov, oi, gv, gi)) {
+          gv = ov;
+          gi = oi;
+        }
+      }
+      best_i = (gi == 0x7fffffff) ? 0 : gi;
+    }
     if (lane == 0) {
-      if (best_i == 0x7fffffff) best_i = 0;  // all NaN / empty
       state[3 + B + r] = best_i;             // token fed to the next step
       if (out_tokens != nullptr && step < out_capacity) out_tokens[step * B + r] = best_i;
       state[3 + r] = __ldcg(state + 3 + r) + 1;  // position id of this sequence
@@ -152,6 +184,7 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_advance_kernel(const T*
   __syncthreads();  // every warp has read `step` before it moves
   if (tid == 0) {
     counters[0] = 0u;
+    if (use_comm) comm_cta_done(comm, comm_seq, 1);
     const long long in_cache = __ldcg(state + 1) + 1;
     state[0] = step + 1;
     state[1] = in_cache;
@@ -175,19 +208,23 @@ size_t mui_argmax_work_bytes(int B) { return 64 + (size_t)B * ARGMAX_CTAS * 8; }
 
 mui_status_t mui_launch_argmax_advance(cudaStream_t stream, mui_dtype_t dtype, const void* logits, int V, int B,
                                        long long* state, int32_t* seq_len32, long long* out_tokens, int out_capacity,
-                                       void* work, int pdl) {
+                                       void* work, int pdl, const CommDev* comm, int index_offset) {
   unsigned int* counters = reinterpret_cast<unsigned int*>(work);
   float* pval = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(work) + 64);
   int* pidx = reinterpret_cast<int*>(pval + (size_t)B * ARGMAX_CTAS);
   const dim3 grid(ARGMAX_CTAS, B);
+  CommDev cd;
+  memset(&cd, 0, sizeof(cd));
+  const int use_comm = (comm != nullptr && comm->world > 1) ? 1 : 0;
+  if (use_comm) cd = *comm;
   if (dtype == MUI_F16) {
     MUI_CUDA_CHECK(mui_launch(argmax_advance_kernel<__half>, grid, dim3(ARGMAX_THREADS), 0, stream, pdl,
                               (const __half*)logits, V, B, state, seq_len32, out_tokens, out_capacity, pval, pidx,
-                              counters));
+                              counters, use_comm, index_offset, cd));
   } else {
     MUI_CUDA_CHECK(mui_launch(argmax_advance_kernel<__nv_bfloat16>, grid, dim3(ARGMAX_THREADS), 0, stream, pdl,
                               (const __nv_bfloat16*)logits, V, B, state, seq_len32, out_tokens, out_capacity, pval,
-                              pidx, counters));
+                              pidx, counters, use_comm, index_offset, cd));
   }
   return MUI_OK;
 }

@@ -9,7 +9,7 @@
 // csrc/modules/parallel_decoder_stack.cpp:22-45, MuiLLMParallelDecoder::forward,
 // csrc/modules/parallel_decoder_module.cpp:22-62); single-GPU decode goes through Python per layer there
 // (muillm/modules/decoder/decoder.py:95-165).
-#include "common.cuh"
+#include "comm_dev.cuh"
 
 #include <cstring>
 #include <new>
@@ -19,7 +19,8 @@ mui_status_t mui_launch_embedding(cudaStream_t stream, const void* table, const 
                                   int H, int vocab, int pdl);
 mui_status_t mui_launch_argmax_advance(cudaStream_t stream, mui_dtype_t dtype, const void* logits, int V, int B,
                                        long long* state, int32_t* seq_len32, long long* out_tokens, int out_capacity,
-                                       void* work, int pdl);
+                                       void* work, int pdl, const CommDev* comm, int index_offset);
+mui_status_t mui_comm_device_view(mui_comm_t* c, CommDev* out);
 size_t mui_argmax_work_bytes(int B);
 
 struct mui_llama_stack {
@@ -39,6 +40,8 @@ struct mui_llama_stack {
   int out_capacity;
   cudaGraphExec_t graph_exec;
   unsigned graph_flags;
+  mui_comm_t* comm;  // tensor-parallel communicator (null on a single GPU)
+  CommDev comm_dev;
 };
 
 namespace {
@@ -95,7 +98,9 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   const long long* position_ids = s->state + 3;
   const long long* cache_position = s->state + 2;
   mui_status_t st;
-  st = mui_launch_embedding(stream, s->embed, (const int64_t*)tokens, s->h, B, H, c.vocab, pdl);
+  const bool tp = s->comm != nullptr;
+  const int embed_rows = c.embed_vocab > 0 ? c.embed_vocab : c.vocab;
+  st = mui_launch_embedding(stream, s->embed, (const int64_t*)tokens, s->h, B, H, embed_rows, pdl);
   if (st != MUI_OK) return st;
   // q,k,v are slices of the packed qkv row: [B, 1, (Hq+2Hkv)*D] viewed as [B, H*, 1, D]
   const mui_strides3_t qs = {(int64_t)qkv_n, (int64_t)D, (int64_t)qkv_n};
@@ -113,21 +118,30 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
     st = mui_flash_decode(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->seq_len32, c.attn_scale, s->q_rot,
                           s->k_cache[l], s->v_cache[l], kvs, nullptr, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
     if (st != MUI_OK) return st;
-    st = mui_linear_forward(stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr, nullptr,
-                            s->h, s->attn, s->h, flags);
+    if (tp)
+      st = mui_parallel_linear_forward(s->comm, stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], nullptr, nullptr,
+                                       s->h, s->attn, s->h, flags);
+    else
+      st = mui_linear_forward(stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr,
+                              nullptr, s->h, s->attn, s->h, flags);
     if (st != MUI_OK) return st;
     st = mui_gateup_silu_forward(stream, c.dtype, B, c.intermediate, H, s->ln2[l], c.rms_eps, s->gate[l], s->up[l],
                                  s->h, s->t, flags);
     if (st != MUI_OK) return st;
-    st = mui_linear_forward(stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l], MUI_ACT_IDENTITY,
-                            nullptr, nullptr, s->h, s->t, s->h, flags);
+    if (tp)
+      st = mui_parallel_linear_forward(s->comm, stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l],
+                                       nullptr, nullptr, s->h, s->t, s->h, flags);
+    else
+      st = mui_linear_forward(stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l], MUI_ACT_IDENTITY,
+                              nullptr, nullptr, s->h, s->t, s->h, flags);
     if (st != MUI_OK) return st;
   }
   st = mui_linear_forward(stream, c.dtype, B, c.vocab, H, s->final_norm, c.rms_eps, s->lm_head, MUI_ACT_IDENTITY,
                           nullptr, nullptr, nullptr, s->h, s->logits, flags);
   if (st != MUI_OK) return st;
   return mui_launch_argmax_advance(stream, c.dtype, s->logits, c.vocab, B, s->state, s->seq_len32, s->out_tokens,
-                                   s->out_capacity, s->argmax_work, pdl);
+                                   s->out_capacity, s->argmax_work, pdl, tp ? &s->comm_dev : nullptr,
+                                   c.vocab_offset);
 }
 
 }  // namespace
@@ -195,7 +209,32 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
   s->out_capacity = 0;
   s->graph_exec = nullptr;
   s->graph_flags = 0;
+  s->comm = nullptr;
   *out = s;
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_set_comm(mui_llama_stack_t* s, mui_comm_t* comm) {
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  if (comm == nullptr) {
+    s->comm = nullptr;
+    return MUI_OK;
+  }
+  int world = 1;
+  size_t cap = 0;
+  if (mui_status_t st = mui_comm_info(comm, nullptr, &world, &cap)) return st;
+  if (world <= 1) {
+    s->comm = nullptr;
+    return MUI_OK;
+  }
+  MUI_REQUIRE(cap >= (size_t)s->cfg.batch * s->cfg.hidden, MUI_ERR_UNSUPPORTED,
+              "communicator capacity %zu below batch*hidden = %zu", cap, (size_t)s->cfg.batch * s->cfg.hidden);
+  if (mui_status_t st = mui_comm_device_view(comm, &s->comm_dev)) return st;
+  s->comm = comm;
+  if (s->graph_exec) {
+    cudaGraphExecDestroy(s->graph_exec);
+    s->graph_exec = nullptr;
+  }
   return MUI_OK;
 }
 

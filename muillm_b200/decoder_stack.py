@@ -24,12 +24,40 @@ def rope_tables(max_pos, dim, theta, dtype, device):
     return emb.cos().to(dtype).to(device), emb.sin().to(dtype).to(device)
 
 
+def shard_llama_weights(weights, cfg, rank, world):
+    """This rank's tensor-parallel shard of un-sharded Llama weights, and the per-rank config.
+
+    QKV and gate/up are cut by output rows so that whole heads stay on a rank (q heads, then k heads, then v heads
+    of the rank, concatenated — muillm/modules/parallelmultilinear.py:340-387), o_proj and down by input columns
+    (muillm/modules/parallellinear.py:422-467), lm_head by rows; embedding and norms are replicated."""
+    Hq, Hkv, D, I, V = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["intermediate"], cfg["vocab"]
+    if Hq % world or Hkv % world or I % world or V % world:
+        raise RuntimeError("heads, kv_heads, intermediate and vocab must be divisible by the tensor-parallel degree")
+    hq, hkv, il, vl = Hq // world, Hkv // world, I // world, V // world
+    out = {"embed": weights["embed"], "norm": weights["norm"],
+           "lm_head": weights["lm_head"][rank * vl:(rank + 1) * vl].contiguous(),
+           "qkv": [], "o": [], "gate": [], "up": [], "down": [], "ln1": weights["ln1"], "ln2": weights["ln2"]}
+    for l in range(cfg["layers"]):
+        w = weights["qkv"][l]
+        q = w[rank * hq * D:(rank + 1) * hq * D]
+        k = w[Hq * D + rank * hkv * D: Hq * D + (rank + 1) * hkv * D]
+        v = w[(Hq + Hkv) * D + rank * hkv * D: (Hq + Hkv) * D + (rank + 1) * hkv * D]
+        out["qkv"].append(torch.cat([q, k, v], dim=0).contiguous())
+        out["o"].append(weights["o"][l][:, rank * hq * D:(rank + 1) * hq * D].contiguous())
+        out["gate"].append(weights["gate"][l][rank * il:(rank + 1) * il].contiguous())
+        out["up"].append(weights["up"][l][rank * il:(rank + 1) * il].contiguous())
+        out["down"].append(weights["down"][l][:, rank * il:(rank + 1) * il].contiguous())
+    local = dict(cfg)
+    local.update(heads=hq, kv_heads=hkv, intermediate=il, vocab=vl, embed_vocab=V, vocab_offset=rank * vl)
+    return out, local
+
+
 class LlamaDecodeStack:
     """weights: dict with 'embed', 'lm_head', 'norm' tensors and per-layer lists 'qkv', 'o', 'gate', 'up',
     'down', 'ln1', 'ln2' (CUDA, contiguous, fp16 or bf16). cfg: dict with layers, hidden, intermediate, heads,
     kv_heads, head_dim, vocab, eps, rope_theta."""
 
-    def __init__(self, weights, cfg, max_seq, batch=1, max_new_tokens=4096, flags=0):
+    def __init__(self, weights, cfg, max_seq, batch=1, max_new_tokens=4096, flags=0, comm=None):
         self.lib = capi.lib()
         self.cfg = dict(cfg)
         self.w = weights
@@ -46,7 +74,8 @@ class LlamaDecodeStack:
         self.cos, self.sin = rope_tables(max_seq, D, cfg["rope_theta"], dt, dev)
         c = capi.LlamaConfig(
             capi.MUI_F16 if dt == torch.float16 else capi.MUI_BF16, L, cfg["hidden"], cfg["intermediate"],
-            cfg["heads"], Hkv, D, cfg["vocab"], max_seq, batch, float(cfg["eps"]), 1.0 / math.sqrt(D))
+            cfg["heads"], Hkv, D, cfg["vocab"], max_seq, batch, float(cfg["eps"]), 1.0 / math.sqrt(D),
+            int(cfg.get("embed_vocab", 0)), int(cfg.get("vocab_offset", 0)))
         self._c = c
         nbytes = self.lib.mui_llama_stack_scratch_bytes(ctypes.byref(c))
         if nbytes == 0:
@@ -72,6 +101,9 @@ class LlamaDecodeStack:
                                                    self.scratch.numel(), ctypes.byref(h)))
         self._h = h
         self._captured = False
+        self.comm = comm  # keeps the communicator alive as long as the stack uses it
+        if comm is not None:
+            capi.check(self.lib.mui_llama_stack_set_comm(h, comm.handle))
         self.reset(0)
 
     def __del__(self):

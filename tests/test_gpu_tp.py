@@ -107,6 +107,29 @@ def _case_parallel_mlp(rank, world, comm):
     torch.testing.assert_close(got.float().cpu(), want.float(), rtol=1e-2, atol=2e-3)
 
 
+def _case_tp_decode_stack(rank, world, comm):
+    from muillm_b200 import capi
+    from muillm_b200.decoder_stack import LlamaDecodeStack, shard_llama_weights
+
+    cfg = dict(layers=3, hidden=512, intermediate=1024, heads=8, kv_heads=8, head_dim=64, vocab=1024, eps=1e-5,
+               rope_theta=500000.0)
+    dtype = torch.float16
+    w = oracle.make_llama_weights(cfg, dtype, seed=0, std=0.08)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg["vocab"], (1, 16), generator=g)
+    want = oracle.LlamaOracle(w, cfg, max_T=64).greedy(prompt, 32)
+    wl, cl = shard_llama_weights(w, cfg, rank, world)
+    wl = {k: ([t.cuda() for t in v] if isinstance(v, list) else v.cuda()) for k, v in wl.items()}
+    for flags, graph in ((0, False), (capi.MUI_FLAG_PDL, True)):
+        stack = LlamaDecodeStack(wl, cl, max_seq=64, batch=1, flags=flags, comm=comm)
+        got = stack.greedy(prompt, 32, use_graph=graph).cpu()
+        same = (got[0] == want[0]).long().cumprod(0).sum().item()
+        # the sharded sums round differently from the single-device order: identical tokens are expected for
+        # this seeded model, a late divergence would point at logit ties, an early one at a bug
+        assert same == 32, f"flags={flags} graph={graph}: tensor-parallel tokens diverge after {same}: {got.tolist()}"
+        del stack
+
+
 def test_all_reduce_and_broadcast():
     _run("_case_all_reduce_and_broadcast")
 
@@ -117,3 +140,7 @@ def test_parallel_linear_fused_all_reduce():
 
 def test_parallel_mlp_fused_all_reduce():
     _run("_case_parallel_mlp")
+
+
+def test_tp_decode_stack_greedy_tokens():
+    _run("_case_tp_decode_stack")
