@@ -49,6 +49,8 @@ typedef enum { MUI_W8_SYM_ROW = 0, MUI_W8_GROUP_MIN = 1 } mui_w8_format_t;
 #define MUI_FLAG_PDL 1u          /* launch with programmatic stream serialization (overlaps the weight prefetch
                                     of this kernel with the tail of the previous kernel on the stream) */
 #define MUI_FLAG_FORCE_GENERIC 2u /* use the plain-load kernel even where the bulk-copy pipeline applies */
+#define MUI_FLAG_MEGAKERNEL 8u    /* decode stack only: run the whole step as ONE persistent kernel (one CTA per SM,
+                                    continuous weight stream, grid barriers between operations); batch 1 only */
 #define MUI_FLAG_FORCE_PIPELINE 4u /* fail with MUI_ERR_UNSUPPORTED instead of falling back to the plain-load kernel */
 
 MUI_API const char* mui_status_string(mui_status_t s);
@@ -69,6 +71,17 @@ MUI_API mui_status_t mui_device_props(int device, mui_device_props_t* out);
 /* Reads (and clears when `clear` != 0) the device status word that kernels set when a bounded wait
  * ran out. Synchronises the device. *code == 0 means no kernel reported anything. */
 MUI_API mui_status_t mui_device_status(unsigned* code, int clear);
+
+/* ---- launch tracing (the reference has none built in; its examples wrap generate() in torch.profiler,
+ * examples/llama3_8b.py:61-67) ------------------------------------------------------------------------------
+ * After mui_trace_enable(stream, buf, n) the calling thread's next n launches of the GEMV, gate/up, flash-decoding
+ * and RoPE kernels each fill one record {first CTA start, ~last CTA end} (two uint64 %globaltimer values, ns) in
+ * the device buffer `buf` (n * 16 bytes, filled with 0xFF by this call on `stream`). Records are bound at launch
+ * (or capture) time, so a captured graph keeps writing its records on every replay. mui_trace_enable(…, NULL, 0)
+ * switches tracing off. mui_trace_count returns how many records were handed out and their kernel tags
+ * (1 linear GEMV, 2 gate/up GEMV, 3 flash decoding, 4 RoPE). */
+MUI_API mui_status_t mui_trace_enable(void* stream, void* device_buffer, int max_records);
+MUI_API int mui_trace_count(int* tags_out, int max_tags);
 
 /* ---- (a1) linear / GEMV --------------------------------------------------------------------------
  * y[b, n] = act( sum_k W[n,k] * xn[b,k] ) * mul_bias[n] + add_bias[n] + residual[b, n]
@@ -340,6 +353,11 @@ MUI_API mui_status_t mui_llama_stack_reset(mui_llama_stack_t* stack, void* strea
 /* Token ids (int64, `batch` of them) fed to the next step; host or device pointer. */
 MUI_API mui_status_t mui_llama_stack_set_tokens(mui_llama_stack_t* stack, void* stream, const int64_t* tokens,
                                                 int on_device);
+/* Phase timeline of the whole-step kernel (MUI_FLAG_MEGAKERNEL): CTA 0 writes {tag, %globaltimer ns} pairs of
+ * uint64 at every phase boundary of every layer (0 layer start, 1/4/6/9/12 after a grid barrier, 2/7/10/13 after
+ * staging the activations, 3/8/11/14 after a projection, 5 after attention) into device_buffer (16 bytes per
+ * record) on the steps launched afterwards. NULL switches it off. */
+MUI_API mui_status_t mui_llama_stack_op_trace(mui_llama_stack_t* stack, void* device_buffer, int max_records);
 MUI_API mui_status_t mui_llama_stack_step(mui_llama_stack_t* stack, void* stream, unsigned flags);
 /* Captures one step on `stream` (must not be the default stream) into a graph; replay launches it `steps` times. */
 MUI_API mui_status_t mui_llama_stack_capture(mui_llama_stack_t* stack, void* stream, unsigned flags);

@@ -32,6 +32,7 @@ MUI_W8_GROUP_MIN = 1
 MUI_FLAG_PDL = 1
 MUI_FLAG_FORCE_GENERIC = 2
 MUI_FLAG_FORCE_PIPELINE = 4
+MUI_FLAG_MEGAKERNEL = 8
 
 
 class Strides3(Structure):
@@ -81,6 +82,8 @@ PROTOTYPES = {
     "mui_version": (c_int, []),
     "mui_device_props": (c_int, [c_int, POINTER(DeviceProps)]),
     "mui_device_status": (c_int, [POINTER(c_uint), c_int]),
+    "mui_trace_enable": (c_int, [c_void_p, c_void_p, c_int]),
+    "mui_trace_count": (c_int, [POINTER(c_int), c_int]),
     "mui_linear_forward": (
         c_int,
         [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -172,6 +175,7 @@ PROTOTYPES = {
     "mui_llama_stack_set_comm": (c_int, [c_void_p, c_void_p]),
     "mui_llama_stack_reset": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), c_void_p, c_int]),
     "mui_llama_stack_set_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "mui_llama_stack_op_trace": (c_int, [c_void_p, c_void_p, c_int]),
     "mui_llama_stack_step": (c_int, [c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_capture": (c_int, [c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_replay": (c_int, [c_void_p, c_void_p, c_int]),

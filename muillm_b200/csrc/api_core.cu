@@ -25,6 +25,17 @@ void mui_set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+// ---- launch tracing state (per host thread) ----
+static thread_local unsigned long long* tls_trace_buf = nullptr;
+static thread_local int tls_trace_cap = 0, tls_trace_next = 0;
+static thread_local int tls_trace_tags[4096];
+
+unsigned long long* mui_trace_next_record(int kernel_tag) {
+  if (tls_trace_buf == nullptr || tls_trace_next >= tls_trace_cap) return nullptr;
+  tls_trace_tags[tls_trace_next] = kernel_tag;
+  return tls_trace_buf + 2 * (size_t)(tls_trace_next++);
+}
+
 const MuiDeviceInfo* mui_current_device_info() {
   static MuiDeviceInfo infos[64];
   static bool valid[64] = {false};
@@ -103,6 +114,26 @@ mui_status_t mui_device_status(unsigned* code, int clear) {
     if (v != 0 && *code == 0) *code = v;
   }
   return MUI_OK;
+}
+
+mui_status_t mui_trace_enable(void* stream, void* device_buffer, int max_records) {
+  if (device_buffer == nullptr || max_records <= 0) {
+    tls_trace_buf = nullptr;  // the count and tags of the finished trace stay readable
+    tls_trace_cap = 0;
+    return MUI_OK;
+  }
+  MUI_REQUIRE(max_records <= 4096, MUI_ERR_INVALID_ARG, "at most 4096 trace records");
+  MUI_CUDA_CHECK(cudaMemsetAsync(device_buffer, 0xFF, (size_t)max_records * 16, (cudaStream_t)stream));
+  tls_trace_buf = reinterpret_cast<unsigned long long*>(device_buffer);
+  tls_trace_cap = max_records;
+  tls_trace_next = 0;
+  return MUI_OK;
+}
+
+int mui_trace_count(int* tags_out, int max_tags) {
+  const int n = tls_trace_next;
+  for (int i = 0; i < n && i < max_tags; ++i) tags_out[i] = tls_trace_tags[i];
+  return n;
 }
 
 static mui_status_t check_dtype(mui_dtype_t d) {

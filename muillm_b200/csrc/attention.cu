@@ -37,6 +37,7 @@ struct FdArgs {
   mui_strides3_t kvs;
   float scale_log2;  // softmax scale * log2(e)
   int B, Hq, Hkv, D, S, G, max_splits;
+  unsigned long long* trace;
 };
 
 __device__ __forceinline__ void fd_merge(float& m, float& l, float (&acc)[8], float mo, float lo,
@@ -59,6 +60,7 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
   __shared__ float sm_acc[FD_WARPS][GP][D];
   __shared__ int sm_is_last;
 
+  trace_start(a.trace);
   pdl_wait_prior_grid();
   pdl_launch_dependents();
 
@@ -224,7 +226,10 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
       p[2 + d] = aa;
     }
   }
-  if (n_active == 1) return;
+  if (n_active == 1) {
+    if (tid == 0) trace_end(a.trace);
+    return;
+  }
 
   // last CTA of this (batch, kv head) merges the splits
   __threadfence();
@@ -234,7 +239,10 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
     sm_is_last = (prev == static_cast<unsigned>(n_active - 1)) ? 1 : 0;
   }
   __syncthreads();
-  if (!sm_is_last) return;
+  if (!sm_is_last) {
+    if (tid == 0) trace_end(a.trace);
+    return;
+  }
   __threadfence();
   for (int idx = tid; idx < G * D; idx += FD_THREADS) {
     const int g = idx / D, d = idx - g * D;
@@ -273,7 +281,10 @@ __global__ void __launch_bounds__(FD_THREADS) flash_decode_kernel(const FdArgs a
     }
     out[head * D + d] = Elt<T>::from_f32(ll > 0.f ? aa / ll : 0.f);
   }
-  if (tid == 0) a.counters[b * a.Hkv + kvh] = 0u;  // ready for the next call
+  if (tid == 0) {
+    a.counters[b * a.Hkv + kvh] = 0u;  // ready for the next call
+    trace_end(a.trace);
+  }
 }
 
 template <typename T, int D>
@@ -342,6 +353,7 @@ mui_status_t mui_flash_decode(void* stream, mui_dtype_t dtype, int B, int Hq, in
   a.kvs = kv_strides;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.S = S; a.G = G; a.max_splits = FD_MAX_SPLITS;
+  a.trace = mui_trace_next_record(3);
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == MUI_F16)

@@ -59,6 +59,29 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Launch tracing: when the host has switched tracing on (mui_trace_enable), every traced launch gets a
+// record of two 64-bit words in a device buffer pre-filled with 0xFF: the earliest %globaltimer at which any of
+// its CTAs started and (stored complemented, so that atomicMin serves both) the latest at which any finished.
+// The timeline of a captured, dependently launched step can be read back without a profiler.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void trace_start(unsigned long long* rec) {
+  if (rec != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    atomicMin(rec, t);
+  }
+}
+__device__ __forceinline__ void trace_end(unsigned long long* rec) {
+  if (rec != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    atomicMin(rec + 1, ~t);
+  }
+}
+// next record of the calling thread's trace (nullptr when tracing is off or the buffer is full)
+unsigned long long* mui_trace_next_record(int kernel_tag);
+
+// ---------------------------------------------------------------------------------------------
 // 16-bit element traits
 // ---------------------------------------------------------------------------------------------
 template <typename T> struct Elt;

@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+  trace_start(a.trace);
   pdl_wait_prior_grid();
   pdl_launch_dependents();
 
@@ -211,6 +212,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
     gemv_comm_tail<T>(a, comm_seq, tid, GEMV_CONSUMER_THREADS, 1, my_rows,
                       [gx, bx](int i) { return 2 * (bx + (i >> 1) * gx) + (i & 1); });
   }
+  if (tid == 0) trace_end(a.trace);
 }
 
 // =============================================================================================
@@ -252,32 +254,6 @@ __host__ __device__ inline PipeLayout pipe_layout(int stage_bytes, int stages, i
   return l;
 }
 
-template <typename T> struct MmaOp;
-template <> struct MmaOp<__half> {
-  static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-};
-template <> struct MmaOp<__nv_bfloat16> {
-  static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-};
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(smem_addr));
-}
-__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t smem_addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_addr));
-}
-
 template <typename T, int NB, int MODE, int KC, int WB>
 __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs a, const int num_stages) {
   using G = PipeGeom<KC, WB>;
@@ -302,6 +278,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
     *abort_flag = 0;
     mbar_fence_init();
   }
+  trace_start(a.trace);
   __syncthreads();
   pdl_launch_dependents();
 
@@ -505,6 +482,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
     if (MODE == 0 && a.use_comm)
       gemv_comm_tail<T>(a, comm_seq, tid, GEMV_CONSUMER_THREADS, 1, r_end - r_begin,
                         [r_begin](int i) { return r_begin + i; });
+    if (tid == 0) trace_end(a.trace);
   }
 }
 
@@ -618,15 +596,18 @@ mui_status_t launch_gemv_dt(cudaStream_t stream, int mode, const GemvArgs& a, in
 }  // namespace
 
 // Launches MODE 0 (linear) or MODE 1 (gate/up) on validated arguments; a.w8_fmt < 0 means 16-bit weights.
-mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode, const GemvArgs& a, unsigned flags) {
+mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode, const GemvArgs& a_in, unsigned flags) {
   const MuiDeviceInfo* dev = mui_current_device_info();
   if (!dev) return MUI_ERR_CUDA;
+  GemvArgs a = a_in;
+  if (a.trace == nullptr) a.trace = mui_trace_next_record(mode == 0 ? 1 : 2);
   const int nb = a.B <= 1 ? 1 : (a.B <= 2 ? 2 : (a.B <= 4 ? 4 : 8));
   // Activations of all batch rows are staged in shared memory; when they cannot fit (large K with B > 1), run
   // the batch in two halves (the weights are then streamed twice).
   if (a.B > 1 && a.moe_mode == GEMV_MOE_NONE && (size_t)nb * (a.Kp + 8) * 2 > 150 * 1024) {
     const int h = a.B / 2;
     GemvArgs lo = a, hi = a;
+    lo.trace = hi.trace = nullptr;
     lo.B = h;
     hi.B = a.B - h;
     hi.x = reinterpret_cast<const unsigned char*>(a.x) + (size_t)h * a.K * 2;

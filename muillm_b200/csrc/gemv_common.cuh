@@ -37,6 +37,7 @@ struct GemvArgs {
   int num_shared;  // shared experts among the slots
   int group_shift; // 8-bit GROUP_MIN: log2(group size)
   int w8_fmt;      // -1: 16-bit weights; else mui_w8_format_t of the 8-bit weights
+  unsigned long long* trace;  // launch-trace record or null
   int use_comm;    // tensor-parallel: push the fp32 results to every rank, then all-reduce into y
   CommDev comm;
 };
@@ -188,6 +189,35 @@ __device__ __forceinline__ size_t gemv_weight_row(const GemvArgs& a, int r, int 
     return (size_t)gemv_slot_expert(a, slot) * a.N + (r - slot * a.N);
   }
   return (size_t)gemv_slot_expert(a, seg) * a.N + r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// tensor-core helpers of the pipeline kernels (mma.sync m16n8k16, fp32 accumulate) and ldmatrix
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct MmaOp;
+template <> struct MmaOp<__half> {
+  static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+template <> struct MmaOp<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_addr));
 }
 
 // ---------------------------------------------------------------------------------------------

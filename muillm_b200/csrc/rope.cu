@@ -19,10 +19,12 @@ struct RopeArgs {
   const int64_t* cache_position;
   mui_strides3_t qs, ks, vs;
   int B, T, max_T, Hq, Hkv, D, table_layout, apply_rope;
+  unsigned long long* trace;
 };
 
 template <typename T>
 __global__ void __launch_bounds__(ROPE_WARPS * 32) rope_kernel(const RopeArgs a) {
+  trace_start(a.trace);
   pdl_wait_prior_grid();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,9 +93,11 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) rope_kernel(const RopeArgs a)
       out_cache[i + half] = o2;
     }
   }
+  if (lane == 0) trace_end(a.trace);
 }
 
-mui_status_t launch_rope(cudaStream_t stream, mui_dtype_t dtype, const RopeArgs& a, unsigned flags) {
+mui_status_t launch_rope(cudaStream_t stream, mui_dtype_t dtype, RopeArgs a, unsigned flags) {
+  a.trace = mui_trace_next_record(4);
   const long long rows = (long long)(a.Hq + 2 * a.Hkv) * a.T * a.B;
   if (rows == 0) return MUI_OK;
   const int grid = static_cast<int>((rows + ROPE_WARPS - 1) / ROPE_WARPS);

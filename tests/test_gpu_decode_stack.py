@@ -82,3 +82,50 @@ def test_batch4_matches_per_sequence_runs():
         alone = LlamaDecodeStack(w, cfg, max_seq=64, batch=1).greedy(prompt[b:b + 1], 16, use_graph=False).cpu()
         same = (alone[0] == together[b]).long().cumprod(0).sum().item()
         assert same >= 8, f"sequence {b}: batched decode diverges from the single run after {same} tokens"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_whole_step_kernel_logits_match_oracle(dtype):
+    """The single persistent kernel per step: teacher-forced logits against the oracle, like the per-kernel path."""
+    cfg = SMALL128
+    w = oracle.make_llama_weights(cfg, dtype, seed=0, std=0.05)
+    ref = oracle.LlamaOracle(w, cfg, max_T=64)
+    stack = LlamaDecodeStack(_to_cuda(w), cfg, max_seq=64, batch=1, flags=capi.MUI_FLAG_MEGAKERNEL)
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg["vocab"], (1, 12), generator=g)
+    for t in range(toks.shape[1]):
+        want = ref.forward(toks[:, t:t + 1])
+        stack.set_tokens(toks[:, t].contiguous())
+        stack.step()
+        got = stack.logits().float().cpu()
+        tol = 2e-2 if dtype == torch.float16 else 1e-1
+        torch.testing.assert_close(got, want.to(dtype).float(), rtol=tol, atol=tol)
+    assert capi.device_status() == 0
+
+
+def test_whole_step_kernel_tokens_equal_per_kernel_path():
+    """Greedy tokens of the whole-step kernel (eager, graph replay, dependent launch) equal the per-kernel stack's
+    and the oracle's, including a prompt long enough for several KV splits."""
+    cfg, dtype = SMALL128, torch.float16
+    w_cpu = oracle.make_llama_weights(cfg, dtype, seed=3, std=0.08)
+    w = _to_cuda(w_cpu)
+    g = torch.Generator().manual_seed(2)
+    for plen, new in ((8, 40), (300, 24)):
+        prompt = torch.randint(0, cfg["vocab"], (1, plen), generator=g)
+        base = LlamaDecodeStack(w, cfg, max_seq=512, batch=1).greedy(prompt, new, use_graph=False).cpu()
+        for flags, graph in ((capi.MUI_FLAG_MEGAKERNEL, False), (capi.MUI_FLAG_MEGAKERNEL, True),
+                             (capi.MUI_FLAG_MEGAKERNEL | capi.MUI_FLAG_PDL, True)):
+            got = LlamaDecodeStack(w, cfg, max_seq=512, batch=1, flags=flags).greedy(prompt, new, use_graph=graph).cpu()
+            assert torch.equal(got, base), f"prompt {plen}, flags {flags}, graph {graph}: {got.tolist()} vs {base.tolist()}"
+        if plen == 8:
+            want = oracle.LlamaOracle(w_cpu, cfg, max_T=512).greedy(prompt, 32)
+            assert torch.equal(base[:, :32], want)
+    assert capi.device_status() == 0
+
+
+def test_whole_step_kernel_rejects_unsupported_shapes():
+    w = _to_cuda(oracle.make_llama_weights(TINY, torch.float16, seed=0))  # head_dim 64
+    stack = LlamaDecodeStack(w, TINY, max_seq=32, batch=1, flags=capi.MUI_FLAG_MEGAKERNEL)
+    stack.set_tokens(torch.tensor([1], dtype=torch.int64))
+    with pytest.raises(RuntimeError, match="whole-step kernel"):
+        stack.step()
