@@ -75,13 +75,22 @@ MUI_API mui_status_t mui_device_status(unsigned* code, int clear);
 /* ---- launch tracing (the reference has none built in; its examples wrap generate() in torch.profiler,
  * examples/llama3_8b.py:61-67) ------------------------------------------------------------------------------
  * After mui_trace_enable(stream, buf, n) the calling thread's next n launches of the GEMV, gate/up, flash-decoding
- * and RoPE kernels each fill one record {first CTA start, ~last CTA end} (two uint64 %globaltimer values, ns) in
- * the device buffer `buf` (n * 16 bytes, filled with 0xFF by this call on `stream`). Records are bound at launch
+ * and RoPE kernels each fill one record of four uint64 %globaltimer values (ns) {first CTA start, ~last CTA end, first CTA
+ * past its wait for the previous kernel, ~last CTA with its activations staged; the last two only for the
+ * pipeline GEMV} in the device buffer `buf` (n * 32 bytes, filled with 0xFF by this call on `stream`). Records are bound at launch
  * (or capture) time, so a captured graph keeps writing its records on every replay. mui_trace_enable(…, NULL, 0)
  * switches tracing off. mui_trace_count returns how many records were handed out and their kernel tags
  * (1 linear GEMV, 2 gate/up GEMV, 3 flash decoding, 4 RoPE). */
 MUI_API mui_status_t mui_trace_enable(void* stream, void* device_buffer, int max_records);
 MUI_API int mui_trace_count(int* tags_out, int max_tags);
+
+/* L2 prefetch hint: up to 3 weight matrices ([rows][row_bytes], 16-byte aligned) of the kernels that FOLLOW the
+ * next GEMV / gate-up launch of this host thread on its stream. Once their own copies are issued, that launch's
+ * producer warps pull into L2 the first frac1024/1024 of the row range each CTA index will own in the consuming
+ * kernel, so HBM keeps streaming through the kernel tail, the launch gap and short latency-bound kernels in
+ * between. Consumed (and cleared) by the next pipeline GEMV launch; harmless otherwise. */
+MUI_API mui_status_t mui_prefetch_hint(const void* const* ptrs, const int* rows, const int* row_bytes,
+                                       const int* frac1024, int n);
 
 /* ---- (a1) linear / GEMV --------------------------------------------------------------------------
  * y[b, n] = act( sum_k W[n,k] * xn[b,k] ) * mul_bias[n] + add_bias[n] + residual[b, n]
@@ -179,6 +188,21 @@ MUI_API mui_status_t mui_flash_decode(void* stream, mui_dtype_t dtype, int B, in
                                       const int32_t* seq_len_dev, float scale, const void* q, const void* k,
                                       const void* v, mui_strides3_t kv_strides, const void* mask, void* out,
                                       void* workspace, size_t workspace_bytes, unsigned flags);
+
+/* Fused decode attention: RoPE on q and on the new k, write of rope(k) and v into the static caches at
+ * cache_position, and attention of the one new token over the S = *seq_len_dev cached-plus-new tokens, in ONE launch
+ * (thread-block cluster of 8 CTAs per (KV head, sequence), partials merged through distributed shared memory: no
+ * global scratch). qkv is the packed output of the QKV projection [B, (Hq + 2*Hkv) * D] (q rows, then k, then v);
+ * position_ids [B] (int64, RoPE position per sequence), cache_position [1] (int64, row written) and seq_len_dev
+ * (int32) live on the device; out is [B, Hq * D]. D == 128, Hq / Hkv <= 8. Replaces the pair
+ * muillm_rope_forward_static_cache + flash_decode_no_mask on the decode path (csrc/rope/rotary.cu:603-756,
+ * csrc/attention/flash_decoding.cu:288-305; MuiLLMParallelAttention::forward chains them,
+ * csrc/modules/parallel_attention_module.cpp:45-90). */
+MUI_API mui_status_t mui_rope_flash_decode(void* stream, mui_dtype_t dtype, int B, int Hq, int Hkv, int D, int max_seq,
+                                           const void* qkv, const void* cos_table, const void* sin_table,
+                                           const int64_t* position_ids, const int64_t* cache_position,
+                                           const int32_t* seq_len_dev, float scale, void* k_cache, void* v_cache,
+                                           void* out, unsigned flags);
 
 /* Flash decoding for callers that may not allocate device memory. No counterpart in the reference (there,
  * torch allocates the partial buffers on every call, csrc/attention/flash_decoding.cu:154-158). Meant for hosts

@@ -2,6 +2,7 @@
 // status word, and the argument validation + dispatch of the linear and gate/up entry points.
 #include "gemv_common.cuh"
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -33,7 +34,22 @@ static thread_local int tls_trace_tags[4096];
 unsigned long long* mui_trace_next_record(int kernel_tag) {
   if (tls_trace_buf == nullptr || tls_trace_next >= tls_trace_cap) return nullptr;
   tls_trace_tags[tls_trace_next] = kernel_tag;
-  return tls_trace_buf + 2 * (size_t)(tls_trace_next++);
+  return tls_trace_buf + 4 * (size_t)(tls_trace_next++);
+}
+
+// ---- L2 prefetch hint (per host thread) ----
+static thread_local const void* tls_pf_ptr[3] = {nullptr, nullptr, nullptr};
+static thread_local int tls_pf_rows[3] = {0, 0, 0}, tls_pf_row_bytes[3] = {0, 0, 0}, tls_pf_frac[3] = {0, 0, 0};
+
+void mui_take_prefetch_hint(const void** ptrs, int* rows, int* row_bytes, int* frac1024) {
+  for (int i = 0; i < 3; ++i) {
+    ptrs[i] = tls_pf_ptr[i];
+    rows[i] = tls_pf_rows[i];
+    row_bytes[i] = tls_pf_row_bytes[i];
+    frac1024[i] = tls_pf_frac[i];
+    tls_pf_ptr[i] = nullptr;
+    tls_pf_frac[i] = 0;
+  }
 }
 
 const MuiDeviceInfo* mui_current_device_info() {
@@ -123,10 +139,24 @@ mui_status_t mui_trace_enable(void* stream, void* device_buffer, int max_records
     return MUI_OK;
   }
   MUI_REQUIRE(max_records <= 4096, MUI_ERR_INVALID_ARG, "at most 4096 trace records");
-  MUI_CUDA_CHECK(cudaMemsetAsync(device_buffer, 0xFF, (size_t)max_records * 16, (cudaStream_t)stream));
+  MUI_CUDA_CHECK(cudaMemsetAsync(device_buffer, 0xFF, (size_t)max_records * 32, (cudaStream_t)stream));
   tls_trace_buf = reinterpret_cast<unsigned long long*>(device_buffer);
   tls_trace_cap = max_records;
   tls_trace_next = 0;
+  return MUI_OK;
+}
+
+mui_status_t mui_prefetch_hint(const void* const* ptrs, const int* rows, const int* row_bytes, const int* frac1024,
+                               int n) {
+  MUI_REQUIRE(n >= 0 && n <= 3, MUI_ERR_INVALID_ARG, "at most 3 prefetch ranges");
+  for (int i = 0; i < 3; ++i) {
+    const bool on = i < n && ptrs[i] != nullptr && (reinterpret_cast<uintptr_t>(ptrs[i]) & 15) == 0 && rows[i] > 0 &&
+                    row_bytes[i] > 0 && (row_bytes[i] & 15) == 0 && frac1024[i] > 0;
+    tls_pf_ptr[i] = on ? ptrs[i] : nullptr;
+    tls_pf_rows[i] = on ? rows[i] : 0;
+    tls_pf_row_bytes[i] = on ? row_bytes[i] : 0;
+    tls_pf_frac[i] = on ? std::min(frac1024[i], 1024) : 0;
+  }
   return MUI_OK;
 }
 

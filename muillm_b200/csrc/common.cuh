@@ -78,6 +78,18 @@ __device__ __forceinline__ void trace_end(unsigned long long* rec) {
     atomicMin(rec + 1, ~t);
   }
 }
+// Prefetch hint of the calling host thread: up to 3 matrices the NEXT GEMV launch should start pulling into L2
+// after issuing its own copies; taking the hint clears it.
+void mui_take_prefetch_hint(const void** ptrs, int* rows, int* row_bytes, int* frac1024);
+// optional extra stamps of a record (words 2 and 3): earliest moment a CTA got past its wait for the previous
+// kernel, and (complemented) latest moment a CTA had its activations staged
+__device__ __forceinline__ void trace_mark(unsigned long long* rec, int word, bool complement) {
+  if (rec != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    atomicMin(rec + word, complement ? ~t : t);
+  }
+}
 // next record of the calling thread's trace (nullptr when tracing is off or the buffer is full)
 unsigned long long* mui_trace_next_record(int kernel_tag);
 
@@ -281,6 +293,11 @@ __device__ __forceinline__ void bulk_load_1d(void* dst_smem, const void* src_gme
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
       ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
+}
+
+// Bulk prefetch of a global range into L2 (no shared memory involved): src 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
 // stage costs each consumer warp a few dozen instructions; at the end of a row block the warps' partial
 // tiles are summed through shared memory in a fixed order.
 constexpr int PIPE_ROWS = 16;
-constexpr int PIPE_THREADS = GEMV_CONSUMER_THREADS + 32;
+constexpr int PIPE_MAX_PRODUCERS = 2;
 constexpr int PIPE_MAX_STAGES = 8;
 constexpr int PIPE_XPAD = 8;  // elements of padding per staged activation row (bank spread for ldmatrix)
 
@@ -254,8 +254,9 @@ __host__ __device__ inline PipeLayout pipe_layout(int stage_bytes, int stages, i
   return l;
 }
 
-template <typename T, int NB, int MODE, int KC, int WB>
-__global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs a, const int num_stages) {
+template <typename T, int NB, int MODE, int KC, int WB, int NPROD>
+__global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_kernel(const GemvArgs a,
+                                                                                      const int num_stages) {
   using G = PipeGeom<KC, WB>;
   constexpr int EB = WB / 8;  // bytes per weight
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -272,7 +273,7 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
 
   if (tid == 0) {
     for (int s = 0; s < num_stages; ++s) {
-      mbar_init(full_bar + s, 1);
+      mbar_init(full_bar + s, NPROD);
       mbar_init(empty_bar + s, GEMV_CONSUMER_WARPS);
     }
     *abort_flag = 0;
@@ -294,8 +295,12 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
   const int cpb = nseg * nchunks;  // stage items per row block
   const int total_items = nblk * cpb;
 
-  if (warp == GEMV_CONSUMER_WARPS) {
-    // ------------------------------ producer warp ------------------------------
+  if (warp >= GEMV_CONSUMER_WARPS) {
+    // ------------------------------ producer warps ------------------------------
+    // each of the NPROD warps issues the copies of its share of the 16 tile rows (the copy engine takes one
+    // warp's copies one after the other; two issuing warps double the ingest rate of 4 KiB copies)
+    constexpr int ROWS_PER_PROD = PIPE_ROWS / NPROD;
+    const int prod = warp - GEMV_CONSUMER_WARPS;
     if (a.moe_mode != GEMV_MOE_NONE) pdl_wait_prior_grid();  // expert ids come from the previous kernel
     const uint64_t policy = l2_policy_evict_first();
     const unsigned char* __restrict__ W = reinterpret_cast<const unsigned char*>(a.W);
@@ -322,18 +327,18 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
       const int kc_len = min(KC, K - kc * KC);
       const uint32_t bytes = static_cast<uint32_t>(kc_len) * EB;
       const int rows_valid = min(ROWS_PER_STAGE, r_end - rb);
-      const int ncopies = (MODE == 0) ? rows_valid : 2 * rows_valid;
+      // tile row tr: MODE 0 -> output row rb + tr; MODE 1 -> gate (tr < 8) / up (tr >= 8) row rb + tr%8
+      const int tr = prod * ROWS_PER_PROD + lane;
+      const int orow = (MODE == 0) ? tr : (tr & 7);
+      const bool mine = (lane < ROWS_PER_PROD) && (orow < rows_valid);
+      const int ncopies = __popc(__ballot_sync(MUI_FULL_MASK, mine));
       if (lane == 0) mbar_arrive_expect_tx(full_bar + s, static_cast<uint32_t>(ncopies) * bytes);
       __syncwarp();
-      if (lane < PIPE_ROWS) {
-        // tile row `lane`: MODE 0 -> output row rb + lane; MODE 1 -> gate (lane < 8) / up (lane >= 8) row rb + lane%8
-        const int orow = (MODE == 0) ? lane : (lane & 7);
-        if (orow < rows_valid) {
-          const unsigned char* src = ((MODE == 1 && lane >= 8) ? W2 : W) +
-                                     (gemv_weight_row(a, rb + orow, seg) * (size_t)K + (size_t)kc * KC) * EB;
-          bulk_load_1d(stage_mem + (size_t)s * G::STAGE_BYTES + (size_t)lane * G::ROW_PITCH, src, bytes,
-                       full_bar + s, policy);
-        }
+      if (mine) {
+        const unsigned char* src = ((MODE == 1 && tr >= 8) ? W2 : W) +
+                                   (gemv_weight_row(a, rb + orow, seg) * (size_t)K + (size_t)kc * KC) * EB;
+        bulk_load_1d(stage_mem + (size_t)s * G::STAGE_BYTES + (size_t)tr * G::ROW_PITCH, src, bytes, full_bar + s,
+                     policy);
       }
       issued = it + 1;
       if (++c == cpb) {
@@ -341,7 +346,22 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
         ++blk;
       }
     }
-    if (!ok && lane == 0) {
+    if (ok && prod == 0) {
+      // L2 prefetch of what comes next on the stream: for each hinted matrix the head of the row range this CTA
+      // index owns in the kernel that will consume it (same even row split), 8 KiB per request
+#pragma unroll
+      for (int sgm = 0; sgm < 3; ++sgm) {
+        if (a.pf_ptr[sgm] == nullptr || a.pf_frac[sgm] <= 0) continue;
+        const long long rows = a.pf_rows[sgm], rbytes = a.pf_row_bytes[sgm];
+        const long long pr0 = rows * blockIdx.x / gridDim.x, pr1 = rows * (blockIdx.x + 1) / gridDim.x;
+        const long long b0 = pr0 * rbytes;
+        const long long nb = ((pr1 - pr0) * rbytes * a.pf_frac[sgm] / 1024) & ~15ll;
+        const unsigned char* base = reinterpret_cast<const unsigned char*>(a.pf_ptr[sgm]) + b0;
+        for (long long off = (long long)lane * 8192; off < nb; off += 32 * 8192)
+          bulk_prefetch_l2(base + off, static_cast<uint32_t>(min(8192ll, nb - off)));
+      }
+    }
+    if (!ok && lane == 0 && prod == 0) {
       // leave no copy in flight behind: wait (bounded) for every stage that was armed
       const int first = max(0, issued - num_stages);
       for (int it = first; it < issued; ++it) {
@@ -353,11 +373,13 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
   } else {
     // ------------------------------ consumer warps ------------------------------
     pdl_wait_prior_grid();
+    if (tid == 0) trace_mark(a.trace, 2, false);
     const unsigned long long comm_seq = (MODE == 0 && a.use_comm) ? comm_begin(a.comm) : 0ull;
     if (a.moe_mode == GEMV_MOE_SEGMENTS)
       gemv_stage_x_plain<T>(a, a.slots, x_s, x_pitch, tid);
     else
       gemv_stage_x<T, NB>(a, a.B, x_s, x_pitch, red, tid);
+    if (tid == 0) trace_mark(a.trace, 3, true);
 
     float d[4] = {0.f, 0.f, 0.f, 0.f};
     // ldmatrix sources. A (weight tile, 16 rows x 16 k): lane gives tile row (lane%8) + 8*((lane/8)%2), k offset
@@ -489,6 +511,11 @@ __global__ void __launch_bounds__(PIPE_THREADS) gemv_pipe_kernel(const GemvArgs 
 // =============================================================================================
 // host dispatch
 // =============================================================================================
+static int mui_pipe_producers() {
+  static int v = env_int("MUI_PIPE_PRODUCERS", 1);
+  return v;
+}
+
 template <typename T, int NB, int MODE, int KC, int WB>
 mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int total_rows, int x_rows,
                          const MuiDeviceInfo* dev, bool* applicable) {
@@ -509,19 +536,23 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
     return MUI_OK;
   }
   *applicable = true;
-  auto kern = gemv_pipe_kernel<T, NB, MODE, KC, WB>;
   const PipeLayout lay = pipe_layout(G::STAGE_BYTES, stages, x_rows, a.Kp, NB);
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
-    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                        cudaSharedmemCarveoutMaxShared));
-    configured = true;
-  }
   const int units = (total_rows + 7) / 8;  // at least one row block per CTA
   const int grid = std::max(1, std::min(units, dev->sm_count * ctas_per_sm));
-  MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(PIPE_THREADS), (size_t)lay.total, stream, pdl, a, stages));
-  return MUI_OK;
+  auto launch = [&](auto kern, int threads, bool* configured) -> mui_status_t {
+    if (!*configured) {
+      MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+      MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          cudaSharedmemCarveoutMaxShared));
+      *configured = true;
+    }
+    MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(threads), (size_t)lay.total, stream, pdl, a, stages));
+    return MUI_OK;
+  };
+  static bool configured1 = false, configured2 = false;  // per instantiation
+  if (mui_pipe_producers() >= 2)
+    return launch(gemv_pipe_kernel<T, NB, MODE, KC, WB, 2>, GEMV_CONSUMER_THREADS + 64, &configured2);
+  return launch(gemv_pipe_kernel<T, NB, MODE, KC, WB, 1>, GEMV_CONSUMER_THREADS + 32, &configured1);
 }
 
 template <typename T, int NB, int MODE, int WB>
@@ -601,6 +632,7 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
   if (!dev) return MUI_ERR_CUDA;
   GemvArgs a = a_in;
   if (a.trace == nullptr) a.trace = mui_trace_next_record(mode == 0 ? 1 : 2);
+  mui_take_prefetch_hint(a.pf_ptr, a.pf_rows, a.pf_row_bytes, a.pf_frac);
   const int nb = a.B <= 1 ? 1 : (a.B <= 2 ? 2 : (a.B <= 4 ? 4 : 8));
   // Activations of all batch rows are staged in shared memory; when they cannot fit (large K with B > 1), run
   // the batch in two halves (the weights are then streamed twice).
@@ -608,6 +640,7 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
     const int h = a.B / 2;
     GemvArgs lo = a, hi = a;
     lo.trace = hi.trace = nullptr;
+    for (int i = 0; i < 3; ++i) lo.pf_frac[i] = 0;
     lo.B = h;
     hi.B = a.B - h;
     hi.x = reinterpret_cast<const unsigned char*>(a.x) + (size_t)h * a.K * 2;

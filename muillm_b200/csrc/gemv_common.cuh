@@ -38,6 +38,13 @@ struct GemvArgs {
   int group_shift; // 8-bit GROUP_MIN: log2(group size)
   int w8_fmt;      // -1: 16-bit weights; else mui_w8_format_t of the 8-bit weights
   unsigned long long* trace;  // launch-trace record or null
+  // weights of the kernels that follow on the stream: once its own copies are issued, the producer warp pulls
+  // this CTA's slice of them into L2, so that HBM keeps streaming through this kernel's tail, the launch gap and
+  // the latency-bound kernels in between
+  const void* pf_ptr[3];  // matrices [pf_rows][pf_row_bytes]; CTA c pulls the first pf_frac/1024 of ITS row range
+  int pf_rows[3];
+  int pf_row_bytes[3];
+  int pf_frac[3];
   int use_comm;    // tensor-parallel: push the fp32 results to every rank, then all-reduce into y
   CommDev comm;
 };
@@ -73,6 +80,47 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
   float rstd[NBX];
 #pragma unroll
   for (int b = 0; b < NBX; ++b) rstd[b] = 1.f;
+
+  // Fast path (one activation row, K up to 8192, 16-byte aligned): every thread keeps its slices of x in
+  // registers between the sum of squares and the scaling, so x is read from L2 once — one dependent round trip
+  // less on the critical path between two kernels.
+  if (NBX == 1 && vec_ok && nw != nullptr && K <= GEMV_CONSUMER_THREADS * 8 * 4 && rows_present >= 1) {
+    uint4 keep[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = (j * GEMV_CONSUMER_THREADS + tid) * 8;
+      keep[j] = (k < K) ? ld_act16(x + k) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float f[8];
+      unpack8<T>(keep[j], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    named_bar_sync(1, GEMV_CONSUMER_THREADS);
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) tot += red[w];
+    const float r = rsqrtf(tot / static_cast<float>(K) + a.eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = (j * GEMV_CONSUMER_THREADS + tid) * 8;
+      if (k < K) {
+        float f[8], wv[8];
+        unpack8<T>(keep[j], f);
+        unpack8<T>(ld_cached16(nw + k), wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = Elt<T>::to_f32(Elt<T>::from_f32(f[i] * r)) * wv[i];
+        *reinterpret_cast<uint4*>(x_s + k) = pack8<T>(f);
+      }
+    }
+    named_bar_sync(1, GEMV_CONSUMER_THREADS);
+    return;
+  }
 
   if (nw != nullptr) {
     float ss[NBX];

@@ -12,6 +12,7 @@
 #include "mega.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -23,6 +24,11 @@ mui_status_t mui_launch_argmax_advance(cudaStream_t stream, mui_dtype_t dtype, c
                                        void* work, int pdl, const CommDev* comm, int index_offset);
 mui_status_t mui_comm_device_view(mui_comm_t* c, CommDev* out);
 size_t mui_argmax_work_bytes(int B);
+
+struct WeightRef {
+  const void* ptr;
+  int rows, row_bytes;
+};
 
 struct mui_llama_stack {
   mui_llama_config_t cfg;
@@ -53,6 +59,8 @@ struct mui_llama_stack {
   int mega_x_elems;
   unsigned long long* op_trace;
   int op_trace_cap;
+  std::vector<WeightRef> order;  // weight matrices in execution order: per layer qkv, o, gate, up, down; then lm_head
+  size_t prefetch_window;
 };
 
 namespace {
@@ -146,6 +154,40 @@ mui_status_t launch_mega(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   return mui_launch_mega_step(stream, c.dtype, a, c.heads / c.kv_heads, grid, (flags & MUI_FLAG_PDL) ? 1 : 0);
 }
 
+// Hint for the GEMV about to be launched: the weight matrices that follow it in execution order, up to `window`
+// bytes in total (a gate/up pair shares its part of the window evenly, since the kernel consumes both in step).
+void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t window) {
+  const void* ptrs[3] = {nullptr, nullptr, nullptr};
+  int rows[3] = {0, 0, 0}, rbytes[3] = {0, 0, 0}, frac[3] = {0, 0, 0};
+  int n = 0;
+  for (size_t i = first; i < order.size() && n < 3 && window > 0; ++i) {
+    const size_t full = (size_t)order[i].rows * order[i].row_bytes;
+    const bool pair = (i % 5 == 2) && i + 1 < order.size() && n < 2;  // gate followed by up
+    if (pair) {
+      const size_t take = std::min(2 * full, window);
+      const int f = (int)std::min<size_t>(1024, take * 1024 / (2 * full));
+      for (int j = 0; j < 2; ++j) {
+        ptrs[n] = order[i + j].ptr;
+        rows[n] = order[i + j].rows;
+        rbytes[n] = order[i + j].row_bytes;
+        frac[n] = f;
+        ++n;
+      }
+      window -= take;
+      ++i;
+    } else {
+      const size_t take = std::min(full, window);
+      ptrs[n] = order[i].ptr;
+      rows[n] = order[i].rows;
+      rbytes[n] = order[i].row_bytes;
+      frac[n] = (int)std::min<size_t>(1024, take * 1024 / full);
+      window -= take;
+      ++n;
+    }
+  }
+  mui_prefetch_hint(ptrs, rows, rbytes, frac, n);
+}
+
 mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags) {
   const mui_llama_config_t& c = s->cfg;
   if (flags & MUI_FLAG_MEGAKERNEL) {
@@ -162,6 +204,7 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   const long long* cache_position = s->state + 2;
   mui_status_t st;
   const bool tp = s->comm != nullptr;
+  const bool pf = s->prefetch_window > 0;
   const int embed_rows = c.embed_vocab > 0 ? c.embed_vocab : c.vocab;
   st = mui_launch_embedding(stream, s->embed, (const int64_t*)tokens, s->h, B, H, embed_rows, pdl);
   if (st != MUI_OK) return st;
@@ -170,17 +213,27 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   const mui_strides3_t kvs = {(int64_t)Hkv * c.max_seq * D, (int64_t)c.max_seq * D, (int64_t)D};
   const size_t e = 2;
   for (int l = 0; l < c.layers; ++l) {
+    if (pf) hint_prefetch(s->order, 5 * (size_t)l + 1, s->prefetch_window);
     st = mui_linear_forward(stream, c.dtype, B, qkv_n, H, s->ln1[l], c.rms_eps, s->qkv[l], MUI_ACT_IDENTITY, nullptr,
                             nullptr, nullptr, s->h, s->qkv_out, flags);
     if (st != MUI_OK) return st;
-    const unsigned char* qp = (const unsigned char*)s->qkv_out;
-    st = mui_rope_forward(stream, c.dtype, B, 1, c.max_seq, Hq, Hkv, D, 0, (const int64_t*)position_ids, s->cos_t,
-                          s->sin_t, qp, qs, qp + (size_t)Hq * D * e, qs, qp + (size_t)(Hq + Hkv) * D * e, qs,
-                          s->q_rot, nullptr, s->k_cache[l], s->v_cache[l], (const int64_t*)cache_position, flags);
-    if (st != MUI_OK) return st;
-    st = mui_flash_decode(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->seq_len32, c.attn_scale, s->q_rot,
-                          s->k_cache[l], s->v_cache[l], kvs, nullptr, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
-    if (st != MUI_OK) return st;
+    if (D == 128 && Hq / Hkv <= 8 && !(flags & MUI_FLAG_FORCE_GENERIC)) {
+      // one launch: RoPE + cache write + attention (cluster kernel)
+      st = mui_rope_flash_decode(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->qkv_out, s->cos_t, s->sin_t,
+                                 (const int64_t*)position_ids, (const int64_t*)cache_position, s->seq_len32,
+                                 c.attn_scale, s->k_cache[l], s->v_cache[l], s->attn, flags);
+      if (st != MUI_OK) return st;
+    } else {
+      const unsigned char* qp = (const unsigned char*)s->qkv_out;
+      st = mui_rope_forward(stream, c.dtype, B, 1, c.max_seq, Hq, Hkv, D, 0, (const int64_t*)position_ids, s->cos_t,
+                            s->sin_t, qp, qs, qp + (size_t)Hq * D * e, qs, qp + (size_t)(Hq + Hkv) * D * e, qs,
+                            s->q_rot, nullptr, s->k_cache[l], s->v_cache[l], (const int64_t*)cache_position, flags);
+      if (st != MUI_OK) return st;
+      st = mui_flash_decode(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->seq_len32, c.attn_scale, s->q_rot,
+                            s->k_cache[l], s->v_cache[l], kvs, nullptr, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
+      if (st != MUI_OK) return st;
+    }
+    if (pf) hint_prefetch(s->order, 5 * (size_t)l + 2, s->prefetch_window);
     if (tp)
       st = mui_parallel_linear_forward(s->comm, stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], nullptr, nullptr,
                                        s->h, s->attn, s->h, flags);
@@ -188,9 +241,11 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
       st = mui_linear_forward(stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr,
                               nullptr, s->h, s->attn, s->h, flags);
     if (st != MUI_OK) return st;
+    if (pf) hint_prefetch(s->order, 5 * (size_t)l + 4, s->prefetch_window);
     st = mui_gateup_silu_forward(stream, c.dtype, B, c.intermediate, H, s->ln2[l], c.rms_eps, s->gate[l], s->up[l],
                                  s->h, s->t, flags);
     if (st != MUI_OK) return st;
+    if (pf) hint_prefetch(s->order, 5 * (size_t)l + 5, s->prefetch_window);
     if (tp)
       st = mui_parallel_linear_forward(s->comm, stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l],
                                        nullptr, nullptr, s->h, s->t, s->h, flags);
@@ -275,6 +330,21 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
   s->comm = nullptr;
   s->op_trace = nullptr;
   s->op_trace_cap = 0;
+  {
+    const int qkv_rows = (cfg->heads + 2 * cfg->kv_heads) * cfg->head_dim;
+    const int od = cfg->heads * cfg->head_dim;
+    for (int l = 0; l < cfg->layers; ++l) {
+      s->order.push_back(WeightRef{w->qkv[l], qkv_rows, cfg->hidden * 2});
+      s->order.push_back(WeightRef{w->o[l], cfg->hidden, od * 2});
+      s->order.push_back(WeightRef{w->gate[l], cfg->intermediate, cfg->hidden * 2});
+      s->order.push_back(WeightRef{w->up[l], cfg->intermediate, cfg->hidden * 2});
+      s->order.push_back(WeightRef{w->down[l], cfg->hidden, cfg->intermediate * 2});
+    }
+    s->order.push_back(WeightRef{w->lm_head, cfg->vocab, cfg->hidden * 2});
+    const char* e = getenv("MUI_PREFETCH_MB");
+    const long mb = (e && *e) ? atol(e) : 48;
+    s->prefetch_window = mb > 0 ? (size_t)mb << 20 : 0;
+  }
   // whole-step kernel: per-layer pointer table on the device, scratch, eligibility
   s->mega_layers = reinterpret_cast<MegaLayer*>(base + lay.mega_layers);
   s->attn_part = reinterpret_cast<float*>(base + lay.attn_part);

@@ -162,8 +162,13 @@ class LlamaDecodeStack:
 
     @property
     def launches_per_step(self):
-        """Kernels one decode step launches: embedding + 6 per layer + lm_head + arg-max."""
-        return 3 + 6 * self.cfg["layers"]
+        """Kernels one decode step launches: embedding, per layer {QKV, attention (one fused launch at head dim 128,
+        else RoPE + flash decoding), o_proj, gate/up, down}, lm_head, arg-max; a single launch for the whole-step
+        kernel."""
+        if self.flags & capi.MUI_FLAG_MEGAKERNEL:
+            return 1
+        fused = self.cfg["head_dim"] == 128 and not (self.flags & capi.MUI_FLAG_FORCE_GENERIC)
+        return 3 + (5 if fused else 6) * self.cfg["layers"]
 
     def prefill(self, prompt):
         """Feeds prompt [batch, T] token by token through the decode step; the arg-max after the last prompt

@@ -294,3 +294,22 @@ def muillm_int8_dequantize_forward(weights, scales_min_vals, group_size_shift, d
                                             int(group_size_shift), N, K, _ptr(weights), _ptr(scales_min_vals),
                                             _ptr(out)))
     return out
+
+
+def rope_flash_decode(qkv, cos_table, sin_table, position_ids, cache_position, seq_len, k_cache, v_cache, num_q_heads,
+                      flags=0):
+    """Fused decode attention for one new token per sequence: RoPE on q and the new k, K/V cache write at
+    cache_position, attention over the first `seq_len` cache rows (the new one included). qkv is the packed QKV
+    projection output [B, (Hq + 2*Hkv) * D]; position_ids [B] int64, cache_position [1] int64 and seq_len [1] int32
+    are device tensors. Returns [B, 1, Hq * D]. One launch in place of muillm_rope_forward_static_cache +
+    muillm_causal_transformer_decoding_no_mask."""
+    for t, n in ((qkv, "qkv"), (cos_table, "cos_table"), (sin_table, "sin_table"), (position_ids, "position_ids"),
+                 (cache_position, "cache_position"), (seq_len, "seq_len"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        _check_input(t, n)
+    B, Hkv, max_seq, D = k_cache.shape
+    out = torch.empty((B, 1, num_q_heads * D), dtype=qkv.dtype, device=qkv.device)
+    capi.check(capi.lib().mui_rope_flash_decode(
+        _stream(), _dtype_code(qkv), B, num_q_heads, Hkv, D, max_seq, _ptr(qkv), _ptr(cos_table), _ptr(sin_table),
+        _ptr(position_ids), _ptr(cache_position), _ptr(seq_len), 1.0 / math.sqrt(D), _ptr(k_cache), _ptr(v_cache),
+        _ptr(out), flags))
+    return out

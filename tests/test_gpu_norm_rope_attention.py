@@ -148,3 +148,37 @@ def test_flash_decode_softmax_shift_invariance():
     a = ops.muillm_causal_transformer_decoding_no_mask(q, k, v)
     b = ops.muillm_causal_transformer_decoding_no_mask(q, torch.cat([k, k], 2), torch.cat([v, v], 2))
     _close(a, b.cpu(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,Hq,Hkv,S", [(1, 32, 8, 1), (1, 32, 8, 17), (1, 32, 8, 280), (1, 32, 8, 513),
+                                        (2, 8, 1, 2000), (3, 4, 4, 65), (1, 8, 8, 4096)])
+def test_fused_rope_cache_write_attention(dtype, B, Hq, Hkv, S):
+    """One launch = RoPE(q, k_new) + cache write + attention over S tokens (the new one last)."""
+    D, max_T = 128, 4096
+    g = _gen(S + B + Hq)
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
+    kc = torch.randn(B, Hkv, max_T, D, generator=g).to(dtype)
+    vc = torch.randn(B, Hkv, max_T, D, generator=g).to(dtype)
+    cos, sin = oracle.rope_tables(max_T, D, 500000.0, dtype)
+    pos = S - 1
+    position_ids = torch.full((B, 1), pos, dtype=torch.int64)
+    if B > 1:
+        position_ids[1, 0] = max(0, pos - 3)  # per-sequence RoPE positions may differ from the cache row
+    cache_position = torch.tensor([pos], dtype=torch.int64)
+    q = qkv[:, : Hq * D].view(B, Hq, 1, D)
+    k = qkv[:, Hq * D: (Hq + Hkv) * D].view(B, Hkv, 1, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(B, Hkv, 1, D)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    q_rot, ks, vs = oracle.rope_write_static_cache(q, k, v, cos, sin, position_ids, kc_ref, vc_ref, cache_position, S)
+    want = oracle.decode_attention(q_rot, ks, vs)
+    kc_g, vc_g = kc.cuda(), vc.cuda()
+    got = ops.rope_flash_decode(qkv.cuda(), cos.cuda(), sin.cuda(), position_ids.view(-1).cuda(), cache_position.cuda(),
+                                torch.tensor([S], dtype=torch.int32, device="cuda"), kc_g, vc_g, Hq)
+    _close(got, want)
+    # the cache got exactly the rows the stand-alone RoPE kernel writes, and nothing else moved
+    _close(kc_g[:, :, pos], kc_ref[:, :, pos])
+    assert torch.equal(vc_g.cpu(), vc_ref)
+    keep = torch.ones(max_T, dtype=torch.bool)
+    keep[pos] = False
+    assert torch.equal(kc_g.cpu()[:, :, keep], kc[:, :, keep])
