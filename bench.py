@@ -352,8 +352,8 @@ def run_gpu(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at this shape, from the ncu capture
-# summarised in profiles/gemv_gateup_llama8b.md (None until a capture exists)
-GATEUP_DRAM_TRAFFIC_BYTES = None
+# summarised in profiles/gemv_gateup_llama8b.md (mean of the two captured launches)
+GATEUP_DRAM_TRAFFIC_BYTES = 238540416
 
 
 def main():

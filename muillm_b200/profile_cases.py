@@ -1,0 +1,83 @@
+"""Small fixed workloads for profiling one kernel at a time (e.g. under `ncu -k regex:<kernel> -c 2`).
+
+  python -m muillm_b200.profile_cases gateup     # fused gate/up+SiLU GEMV, Llama-3-8B MLP shape, 4 distinct layers
+  python -m muillm_b200.profile_cases linear     # QKV-shaped fused-norm GEMV (6144 x 4096), 8 distinct matrices
+  python -m muillm_b200.profile_cases attention  # fused RoPE + cache write + attention, 32 q / 8 kv heads, S = 2048
+  python -m muillm_b200.profile_cases w8         # int8 (per-row scale) gate/up GEMV, same MLP shape
+
+Each case keeps well under 2 GB on the device, uses inputs larger than L2 in total so that weights come from
+HBM, launches the kernel a handful of times and synchronises.
+"""
+import sys
+
+import torch
+
+from . import capi, ops
+
+
+def _gateup(dtype=torch.float16, w8=False):
+    H, I, L = 4096, 14336, 4
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(1, H, device=dev, generator=g).to(dtype)
+    nw = torch.ones(H, device=dev, dtype=dtype)
+    ws = []
+    for _ in range(L):
+        G = (torch.randn(I, H, device=dev, generator=g) * 0.02).to(dtype)
+        U = (torch.randn(I, H, device=dev, generator=g) * 0.02).to(dtype)
+        if w8:
+            def q(w):
+                s = (w.float().abs().amax(dim=1) / 127.0).clamp(min=1e-8).to(dtype)
+                return torch.round(w.float() / s.float()[:, None]).clamp(-127, 127).to(torch.int8), s
+            ws.append(q(G) + q(U))
+        else:
+            ws.append((G, U))
+    for rep in range(2):
+        for w in ws:
+            if w8:
+                ops.int8_gateup_silu(x, w[0], w[1], w[2], w[3], norm_weights=nw, epsilon=1e-5)
+            else:
+                ops.gateup_silu(x, w[0], w[1], norm_weights=nw, epsilon=1e-5)
+    torch.cuda.synchronize()
+
+
+def _linear(dtype=torch.float16):
+    N, K, L = 6144, 4096, 8
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(1, K, device=dev, generator=g).to(dtype)
+    nw = torch.ones(K, device=dev, dtype=dtype)
+    ws = [(torch.randn(N, K, device=dev, generator=g) * 0.02).to(dtype) for _ in range(L)]
+    for rep in range(2):
+        for w in ws:
+            ops.muillm_linear_forward(None, x, w, norm_weights=nw, epsilon=1e-5)
+    torch.cuda.synchronize()
+
+
+def _attention(dtype=torch.float16):
+    B, Hq, Hkv, D, S, max_T = 1, 32, 8, 128, 2048, 4096
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device=dev, generator=g).to(dtype)
+    caches = [(torch.randn(B, Hkv, max_T, D, device=dev, generator=g).to(dtype),
+               torch.randn(B, Hkv, max_T, D, device=dev, generator=g).to(dtype)) for _ in range(16)]
+    cos = torch.ones(max_T, D, device=dev, dtype=dtype)
+    sin = torch.zeros(max_T, D, device=dev, dtype=dtype)
+    pos = torch.full((B,), S - 1, dtype=torch.int64, device=dev)
+    cpos = torch.tensor([S - 1], dtype=torch.int64, device=dev)
+    sl = torch.tensor([S], dtype=torch.int32, device=dev)
+    for kc, vc in caches:
+        ops.rope_flash_decode(qkv, cos, sin, pos, cpos, sl, kc, vc, Hq)
+    torch.cuda.synchronize()
+
+
+def main():
+    case = sys.argv[1] if len(sys.argv) > 1 else "gateup"
+    torch.cuda.set_device(0)
+    {"gateup": _gateup, "linear": _linear, "attention": _attention, "w8": lambda: _gateup(w8=True)}[case]()
+    assert capi.device_status() == 0
+    print("ok", case)
+
+
+if __name__ == "__main__":
+    main()
