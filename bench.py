@@ -337,7 +337,7 @@ def run_gpu(args):
         "roofline": {"bound": "hbm", "kernel": f"gemv_pipe_kernel<half, NB=1, gate/up+SiLU> "
                                                f"(I={local_cfg['intermediate']}, H=4096)",
                      "achieved": achieved, "peak": peak, "peak_source": peak_kind, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": GATEUP_DRAM_TRAFFIC_BYTES,
+                     "frac": achieved / peak, "traffic": GATEUP_DRAM_TRAFFIC_BYTES if world == 1 else None,
                      "algorithmic_bytes": k_bytes, "avg_launch_us": k_seconds * 1e6},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
         "gpu_launches": K * stack.launches_per_step,

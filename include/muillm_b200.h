@@ -223,6 +223,70 @@ MUI_API mui_status_t mui_flash_decode_static_scratch(void* stream, mui_dtype_t d
                                                      const void* k, const void* v, mui_strides3_t kv_strides,
                                                      const void* mask, void* out, unsigned flags);
 
+/* ---- (a15) Llama-4 attention prologue, windowed cache, small bookkeeping ops ------------------------
+ * q/k are [B,H,T,D] views given by element strides (innermost stride 1, D even, D <= 256); outputs are contiguous
+ * [B,H,T,D]. Every stage computes in fp32 and rounds once to dtype.
+ *
+ * mui_complex_rope_forward: (x[2i] + j·x[2i+1]) · (cos_i + j·sin_i) with position_embeds fp32 [B,T,D/2,2].
+ *   Replaces muillm_complex_rope_forward_no_cache (csrc/rope/rotary.cu:798-915).
+ * mui_qkl2norm_forward: x · rsqrt(mean(x²) + eps) on rows_q rows of q and rows_k rows of k (contiguous rows of D).
+ *   Replaces muillm_qkl2norm_forward (csrc/norm/qkl2norm.cu:38-100); with rows_k = 0 also muillm_l2norm_forward
+ *   for rows of at most 256 elements. eps is added to the mean (HF Llama4TextL2Norm), not to the sum as the
+ *   reference kernel does (csrc/norm/qkl2norm_fp16_kernels.cu:66,117).
+ * mui_temperature_tuning_forward: q · (log1p(floor((cache_position[t] + 1) / floor_scale)) · attn_scale + 1).
+ *   Replaces muillm_apply_temperature_tuning (csrc/temperaturetuning/temperature_tuning.cu).
+ * mui_llama4_qk_prologue: the three above in one launch, in that order; a stage is skipped when its input is
+ *   absent (position_embeds NULL: no rope; use_qk_norm 0: no norm; cache_position NULL: no temperature scale, which
+ *   applies to q only). Bit-identical to the three separate calls. */
+MUI_API mui_status_t mui_complex_rope_forward(void* stream, mui_dtype_t dtype, int B, int T, int Hq, int Hk, int D,
+                                              const float* position_embeds, const void* q_in,
+                                              mui_strides3_t q_strides, const void* k_in, mui_strides3_t k_strides,
+                                              void* q_out, void* k_out, unsigned flags);
+MUI_API mui_status_t mui_qkl2norm_forward(void* stream, mui_dtype_t dtype, long long rows_q, long long rows_k, int D,
+                                          const void* q, const void* k, void* q_out, void* k_out, float eps,
+                                          unsigned flags);
+MUI_API mui_status_t mui_temperature_tuning_forward(void* stream, mui_dtype_t dtype, int B, int T, int H, int D,
+                                                    const void* q_in, mui_strides3_t q_strides,
+                                                    const int64_t* cache_position, void* q_out, float attn_scale,
+                                                    float floor_scale, unsigned flags);
+MUI_API mui_status_t mui_llama4_qk_prologue(void* stream, mui_dtype_t dtype, int B, int T, int Hq, int Hk, int D,
+                                            const float* position_embeds, int use_qk_norm, float norm_eps,
+                                            const int64_t* cache_position, float attn_scale, float floor_scale,
+                                            const void* q_in, mui_strides3_t q_strides, const void* k_in,
+                                            mui_strides3_t k_strides, void* q_out, void* k_out, unsigned flags);
+
+/* Sliding-window cache update, rows kept in chronological order (csrc/kvcaches/sliding_kvcache.cpp:87-246).
+ * seen_tokens counts the T new tokens. *mode_out (host int, may be NULL) tells what happened:
+ *   0  seen_tokens == T: first fill; the last min(T, max_T) new rows go to cache rows 0..; attend k_in / v_in.
+ *   1  seen_tokens > max_T: the window is full; k_cache_out / v_cache_out (second buffers, required) receive the
+ *      old rows shifted down by min(T, max_T) followed by the new rows; attend all max_T rows of the new buffers.
+ *   2  otherwise: new rows are scattered in place at cache_position[t]; attend the first seen_tokens rows. */
+MUI_API mui_status_t mui_sliding_kvcache_update(void* stream, mui_dtype_t dtype, int B, int T, int max_T, int Hk,
+                                                int Hv, int D, const void* k_in, mui_strides3_t k_strides,
+                                                const void* v_in, mui_strides3_t v_strides, void* k_cache,
+                                                void* v_cache, void* k_cache_out, void* v_cache_out,
+                                                const int64_t* cache_position, long long seen_tokens, int* mode_out,
+                                                unsigned flags);
+
+/* y[b, n] = sum_m x[b, m, n], fp32 accumulation (N == 1 sums the last dimension of [B, M]).
+ * Replaces muillm_reduce_sum_forward (csrc/reduce/reduce.cu:33-108). */
+MUI_API mui_status_t mui_reduce_sum_forward(void* stream, mui_dtype_t dtype, long long B, int M, long long N,
+                                            const void* x, void* y, unsigned flags);
+
+/* One step of a generation loop's bookkeeping: next_input_ids [B,T+1] = input_ids [B,T] with the next token
+ * appended (pad_token_id for sequences already finished when the eos criterion is on); next_unfinished[b] =
+ * unfinished[b] and not (token is one of eos_token_ids) and not (T + 1 >= max_length), each criterion only if
+ * enabled. next_tokens is int32, the rest int64. Follows the generation loop of HF `GenerationMixin._sample`
+ * that the reference's muillm_add_tokens_check_finished fuses (csrc/generation/generation.cu:30-213); the
+ * reference kernel's extra store to next_input_ids[b] and its `T <= max_length` test are not reproduced. */
+MUI_API mui_status_t mui_add_tokens_check_finished(void* stream, int B, int T, const int64_t* input_ids,
+                                                   const int32_t* next_tokens, const int64_t* unfinished_sequences,
+                                                   int has_eos_stopping_criteria, long long pad_token_id,
+                                                   const int64_t* eos_token_ids, int num_eos_tokens,
+                                                   int has_max_length_stopping_criteria, long long max_length,
+                                                   int64_t* next_input_ids, int64_t* next_unfinished_sequences,
+                                                   unsigned flags);
+
 /* ---- (a6) router top-k + sigmoid -------------------------------------------------------------------
  * For each of `rows` rows of logits [rows, M] (M <= 4096): the k largest values (ties -> lowest index, as a
  * stable descending sort orders them), sigmoid in fp32, rounded to dtype; indices int64.

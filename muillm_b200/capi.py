@@ -7,7 +7,8 @@ csrc/linear/linear.cu:72-74).
 """
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint, c_void_p
+from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_longlong, c_size_t, c_uint,
+                    c_void_p)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libmuillm_b200.so")
@@ -136,6 +137,36 @@ PROTOTYPES = {
         c_int,
         [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
          Strides3, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_complex_rope_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, Strides3, c_void_p, Strides3,
+         c_void_p, c_void_p, c_uint],
+    ),
+    "mui_qkl2norm_forward": (
+        c_int,
+        [c_void_p, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_uint],
+    ),
+    "mui_temperature_tuning_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, Strides3, c_void_p, c_void_p, c_float, c_float,
+         c_uint],
+    ),
+    "mui_llama4_qk_prologue": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_float, c_float,
+         c_void_p, Strides3, c_void_p, Strides3, c_void_p, c_void_p, c_uint],
+    ),
+    "mui_sliding_kvcache_update": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, Strides3, c_void_p, Strides3,
+         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, POINTER(c_int), c_uint],
+    ),
+    "mui_reduce_sum_forward": (c_int, [c_void_p, c_int, c_longlong, c_int, c_longlong, c_void_p, c_void_p, c_uint]),
+    "mui_add_tokens_check_finished": (
+        c_int,
+        [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int,
+         c_longlong, c_void_p, c_void_p, c_uint],
     ),
     "mui_topk_sigmoid_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint]),
     "mui_moe_gateup_silu_forward": (

@@ -77,12 +77,14 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(const CommDev c, 
   const unsigned long long seq = comm_begin(c);
   const long long e0 = count * blockIdx.x / gridDim.x, e1 = count * (blockIdx.x + 1) / gridDim.x;
   for (long long i = e0 + tid; i < e1; i += AR_THREADS) comm_push(c, seq, (size_t)i, ArIO<T>::ld(src + i));
+  __syncthreads();  // every thread has read the counter before this CTA announces itself
+  unsigned ticket = 0;
+  if (tid == 0) ticket = comm_cta_arrive(c);
   for (long long i = e0 + tid; i < e1; i += AR_THREADS) {
     float v;
     if (comm_reduce_elem(c, seq, (size_t)i, &v)) ArIO<T>::st(dst + i, v);
   }
-  __syncthreads();
-  if (tid == 0) comm_cta_done(c, seq, gridDim.x);
+  if (tid == 0) comm_cta_finish(c, seq, ticket, gridDim.x);
 }
 
 // Broadcast of `words` 32-bit words from rank `root`: the root pushes the words (as cell payloads), the others
@@ -132,7 +134,10 @@ mui_status_t check_ready(mui_comm* c) {
   return MUI_OK;
 }
 
-int ar_grid(long long count) { return (int)std::max<long long>(1, std::min<long long>(32, (count + 1023) / 1024)); }
+// one element per thread up to two CTAs per SM: the collective is a latency chain, not a bandwidth problem
+int ar_grid(long long count) {
+  return (int)std::max<long long>(1, std::min<long long>(296, (count + AR_THREADS - 1) / AR_THREADS));
+}
 
 // ---------------------------------------------------------------------------------------------
 // local-socket bootstrap: all-gather of fixed-size blobs between the ranks of one node

@@ -68,27 +68,47 @@ __device__ __forceinline__ bool comm_take(const CommDev& c, unsigned long long s
   return true;
 }
 
-// Sum over ranks of element idx in fixed rank order; false if a rank's cell never arrived.
+// Sum over ranks of element idx in fixed rank order; false if a rank's cell never arrived. The loads of all ranks'
+// cells are issued back to back (one L2 round trip for the common case that everything has landed); only cells
+// that still carry an older sequence number are polled.
 __device__ __forceinline__ bool comm_reduce_elem(const CommDev& c, unsigned long long seq, size_t idx, float* out) {
+  const unsigned long long* base = c.peer_cells[c.rank] + (size_t)(seq & 1ull) * c.world * c.capacity + idx;
+  const unsigned want = static_cast<unsigned>(seq & 0xffffffffull);
+  unsigned long long v[MUI_COMM_MAX_RANKS];
+#pragma unroll
+  for (int r = 0; r < MUI_COMM_MAX_RANKS; ++r)
+    if (r < c.world) v[r] = ld_relaxed_sys_u64(base + (size_t)r * c.capacity);
   float s = 0.f;
   bool ok = true;
 #pragma unroll
   for (int r = 0; r < MUI_COMM_MAX_RANKS; ++r) {
     if (r < c.world) {
-      float v = 0.f;
-      ok = comm_take(c, seq, r, idx, &v) && ok;
-      s += v;
+      float f = __uint_as_float(static_cast<unsigned>(v[r] & 0xffffffffull));
+      if (static_cast<unsigned>(v[r] >> 32) != want) {
+        f = 0.f;
+        ok = comm_take(c, seq, r, idx, &f) && ok;
+      }
+      s += f;
     }
   }
   *out = s;
   return ok;
 }
 
-// One thread per CTA, when the CTA is done with the collective: the last CTA of the grid advances the counter.
-__device__ __forceinline__ void comm_cta_done(const CommDev& c, unsigned long long seq, unsigned num_ctas) {
-  const unsigned prev = atomicAdd(c.arrive_counter, 1u);
-  if (prev == num_ctas - 1) {
+// Advancing the sequence counter: every CTA of a collective announces itself once (after it has read the counter
+// through comm_begin), and the CTA that finds itself last stores the new value. Split in two so that the round trip
+// of the atomic overlaps the wait for the peers' cells: thread 0 calls comm_cta_arrive before it polls and
+// comm_cta_finish with the returned ticket afterwards.
+__device__ __forceinline__ unsigned comm_cta_arrive(const CommDev& c) { return atomicAdd(c.arrive_counter, 1u); }
+
+__device__ __forceinline__ void comm_cta_finish(const CommDev& c, unsigned long long seq, unsigned ticket,
+                                                unsigned num_ctas) {
+  if (ticket == num_ctas - 1) {
     *c.arrive_counter = 0u;
     *c.local_seq = seq;
   }
+}
+
+__device__ __forceinline__ void comm_cta_done(const CommDev& c, unsigned long long seq, unsigned num_ctas) {
+  comm_cta_finish(c, seq, comm_cta_arrive(c), num_ctas);
 }

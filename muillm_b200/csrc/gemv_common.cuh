@@ -339,8 +339,8 @@ __device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int 
   if (a.y) reinterpret_cast<T*>(a.y)[o] = Elt<T>::from_f32(v);
 }
 
-// Tail of a tensor-parallel GEMV: called by all `nthreads` threads that ran the epilogues (they synchronise on
-// named barrier `bar_id`), after the CTA's last push. The CTA reduces the rows it owns — the same rows the
+// Tail of a tensor-parallel GEMV: called by all `nthreads` threads that ran the epilogues, after the CTA's last
+// push (no CTA-wide barrier is needed: a cell is taken only once it carries this collective's sequence number). The CTA reduces the rows it owns — the same rows the
 // same CTA of every other rank pushed — into y, polling its own segment until each rank's cells arrived.
 // `row_of(i)` enumerates the CTA's rows.
 template <typename T, typename RowFn>
@@ -348,14 +348,15 @@ __device__ __forceinline__ void gemv_comm_tail(const GemvArgs& a, unsigned long 
                                                int bar_id, int num_rows, RowFn row_of) {
   T* y = reinterpret_cast<T*>(a.y);
   const int total = num_rows * a.B;
+  unsigned ticket = 0;
+  if (tid == 0) ticket = comm_cta_arrive(a.comm);  // result is looked at after the polls below
   for (int i = tid; i < total; i += nthreads) {
     const int b = i / num_rows, n = row_of(i - b * num_rows);
     const size_t o = (size_t)b * a.N + n;
     float v;
     if (comm_reduce_elem(a.comm, seq, o, &v)) y[o] = Elt<T>::from_f32(v);
   }
-  named_bar_sync(bar_id, nthreads);
-  if (tid == 0) comm_cta_done(a.comm, seq, gridDim.x);
+  if (tid == 0) comm_cta_finish(a.comm, seq, ticket, gridDim.x);
 }
 
 // gate/up: t = silu(s*g) * (s*u); s is the router score of the slot (1 for dense / shared experts),

@@ -5,6 +5,7 @@ output with torch (device memory and streams are torch's job here) and launch on
 Every function fails loudly when the CUDA library is missing or a tensor is not a contiguous CUDA
 tensor of a supported dtype — there is no eager/PyTorch fallback inside.
 """
+import ctypes
 import math
 
 import torch
@@ -313,3 +314,152 @@ def rope_flash_decode(qkv, cos_table, sin_table, position_ids, cache_position, s
         _ptr(position_ids), _ptr(cache_position), _ptr(seq_len), 1.0 / math.sqrt(D), _ptr(k_cache), _ptr(v_cache),
         _ptr(out), flags))
     return out
+
+
+# ---- Llama-4 attention prologue, windowed cache, bookkeeping ------------------------------------------------
+
+
+def muillm_complex_rope_forward_no_cache(q_in, k_in, position_embeds, flags=0):
+    """Interleaved-pair rotary embedding with fp32 (cos, sin) pairs [B, T, D/2, 2] (a complex tensor viewed as
+    real works too); returns contiguous (q_out, k_out) (csrc/rope/rotary.cu:798-915)."""
+    if position_embeds.is_complex():
+        position_embeds = torch.view_as_real(position_embeds)
+    _check_input(position_embeds, "position_embeds")
+    if position_embeds.dim() != 4 or position_embeds.dtype != torch.float32:
+        raise RuntimeError("Complex ROPE only supported with BTE layout")
+    B, Hq, T, D = q_in.shape
+    Hk = k_in.shape[1]
+    q_out = torch.empty((B, Hq, T, D), dtype=q_in.dtype, device=q_in.device)
+    k_out = torch.empty((B, Hk, T, D), dtype=k_in.dtype, device=k_in.device)
+    capi.check(capi.lib().mui_complex_rope_forward(
+        _stream(), _dtype_code(q_in), B, T, Hq, Hk, D, _ptr(position_embeds), _ptr(q_in), _strides3(q_in),
+        _ptr(k_in), _strides3(k_in), _ptr(q_out), _ptr(k_out), flags))
+    return q_out, k_out
+
+
+def muillm_qkl2norm_forward(q, k, epsilon, flags=0):
+    """L2 norm over the last dimension of q and of k in one launch (csrc/norm/qkl2norm.cu:38-100)."""
+    _check_input(q, "q")
+    _check_input(k, "k")
+    D = q.shape[-1]
+    if k.shape[-1] != D:
+        raise RuntimeError("The last dimension of q and k must be the same")
+    q_out, k_out = torch.empty_like(q), torch.empty_like(k)
+    capi.check(capi.lib().mui_qkl2norm_forward(_stream(), _dtype_code(q), q.numel() // D, k.numel() // D, D, _ptr(q),
+                                               _ptr(k), _ptr(q_out), _ptr(k_out), float(epsilon), flags))
+    return q_out, k_out
+
+
+def muillm_l2norm_forward(x, epsilon, flags=0):
+    """x * rsqrt(mean(x^2) + eps) over the last dimension (csrc/norm/l2norm.cu:28-76): the RMSNorm kernel
+    without weights."""
+    _check_input(x, "x")
+    K = x.shape[-1]
+    y = torch.empty_like(x)
+    capi.check(capi.lib().mui_rmsnorm_forward(_stream(), _dtype_code(x), _rows(x), K, None, float(epsilon), _ptr(x),
+                                              _ptr(y), flags))
+    return y
+
+
+def muillm_apply_temperature_tuning(query_states, cache_position, attn_scale, floor_scale, flags=0):
+    """q * (log1p(floor((cache_position + 1) / floor_scale)) * attn_scale + 1) for q [B, H, T, D]
+    (csrc/temperaturetuning/temperature_tuning.cu)."""
+    _check_input(cache_position, "cache_position")
+    B, H, T, D = query_states.shape
+    out = torch.empty((B, H, T, D), dtype=query_states.dtype, device=query_states.device)
+    capi.check(capi.lib().mui_temperature_tuning_forward(
+        _stream(), _dtype_code(query_states), B, T, H, D, _ptr(query_states), _strides3(query_states),
+        _ptr(cache_position), _ptr(out), float(attn_scale), float(floor_scale), flags))
+    return out
+
+
+def llama4_qk_prologue(q_in, k_in, position_embeds=None, qk_norm_eps=None, cache_position=None, attn_scale=0.0,
+                       floor_scale=1.0, flags=0):
+    """Complex rope -> QK L2 norm -> temperature scale (q only) in one launch; any stage may be absent."""
+    if position_embeds is not None and position_embeds.is_complex():
+        position_embeds = torch.view_as_real(position_embeds)
+    B, Hq, T, D = q_in.shape
+    Hk = k_in.shape[1]
+    q_out = torch.empty((B, Hq, T, D), dtype=q_in.dtype, device=q_in.device)
+    k_out = torch.empty((B, Hk, T, D), dtype=k_in.dtype, device=k_in.device)
+    capi.check(capi.lib().mui_llama4_qk_prologue(
+        _stream(), _dtype_code(q_in), B, T, Hq, Hk, D, _ptr(position_embeds), 0 if qk_norm_eps is None else 1,
+        float(qk_norm_eps or 0.0), _ptr(cache_position), float(attn_scale), float(floor_scale), _ptr(q_in),
+        _strides3(q_in), _ptr(k_in), _strides3(k_in), _ptr(q_out), _ptr(k_out), flags))
+    return q_out, k_out
+
+
+def muillm_sliding_kvcache_update(k_in, v_in, k_cache, v_cache, cache_position, seen_tokens, flags=0):
+    """Sliding-window cache update with rows in chronological order (csrc/kvcaches/sliding_kvcache.cpp:87-246).
+    Returns the (key, value) states to attend: the inputs on the first fill, the first seen_tokens cache rows
+    while the window is not full, else a fresh pair of full-window buffers the caller keeps as the cache."""
+    _check_input(k_cache, "k_cache")
+    _check_input(v_cache, "v_cache")
+    _check_input(cache_position, "cache_position")
+    B, Hk, T, D = k_in.shape
+    Hv = v_in.shape[1]
+    max_T = k_cache.shape[2]
+    full = seen_tokens > max_T and seen_tokens != T
+    k_new = torch.empty_like(k_cache) if full else None
+    v_new = torch.empty_like(v_cache) if full else None
+    mode = ctypes.c_int(-1)
+    capi.check(capi.lib().mui_sliding_kvcache_update(
+        _stream(), _dtype_code(k_in), B, T, max_T, Hk, Hv, D, _ptr(k_in), _strides3(k_in), _ptr(v_in),
+        _strides3(v_in), _ptr(k_cache), _ptr(v_cache), _ptr(k_new), _ptr(v_new), _ptr(cache_position),
+        int(seen_tokens), ctypes.byref(mode), flags))
+    if mode.value == 0:
+        return k_in, v_in
+    if mode.value == 1:
+        return k_new, v_new
+    return k_cache.narrow(2, 0, seen_tokens), v_cache.narrow(2, 0, seen_tokens)
+
+
+def muillm_reduce_sum_forward(x, dim, keep_dim, flags=0):
+    """Sum over one dimension with fp32 accumulation (csrc/reduce/reduce.cu:33-153)."""
+    _check_input(x, "x")
+    if x.dim() < 1:
+        raise RuntimeError("Input tensor must have at least one dimension")
+    if dim < 0:
+        dim += x.dim()
+    if not 0 <= dim < x.dim():
+        raise RuntimeError("Invalid dimension for reduction")
+    sizes = list(x.shape)
+    Bo = 1
+    for s in sizes[:dim]:
+        Bo *= s
+    N = 1
+    for s in sizes[dim + 1:]:
+        N *= s
+    M = sizes[dim]
+    out_sizes = sizes[:dim] + ([1] if keep_dim else []) + sizes[dim + 1:]
+    y = torch.empty(out_sizes, dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_reduce_sum_forward(_stream(), _dtype_code(x), Bo, M, N, _ptr(x), _ptr(y), flags))
+    return y
+
+
+def muillm_add_tokens_check_finished(input_ids, next_tokens, unfinished_sequences, has_eos_stopping_criteria,
+                                     pad_token_id, eos_token_ids, has_max_length_stopping_criteria, max_length,
+                                     flags=0):
+    """Append the next token to input_ids [B, T] and update the unfinished mask
+    (csrc/generation/generation.cu:119-213). next_tokens int32, the other tensors int64."""
+    for t, n in ((input_ids, "input_ids"), (next_tokens, "next_tokens"), (unfinished_sequences,
+                                                                         "unfinished_sequences")):
+        _check_input(t, n)
+    if input_ids.dtype != torch.int64:
+        raise RuntimeError("input_ids must be of type int64")
+    if unfinished_sequences.dtype != torch.int64:
+        raise RuntimeError("unfinished_sequences must be of type int64")
+    if next_tokens.dtype != torch.int32:
+        raise RuntimeError("next_tokens must be of type int")
+    B, T = input_ids.shape
+    if unfinished_sequences.shape[0] != B:
+        raise RuntimeError("unfinished_sequences doesn't have the shape [B]")
+    n_eos = 0 if eos_token_ids is None else int(eos_token_ids.numel())
+    out = torch.empty((B, T + 1), dtype=torch.int64, device=input_ids.device)
+    unf = torch.empty_like(unfinished_sequences)
+    capi.check(capi.lib().mui_add_tokens_check_finished(
+        _stream(), B, T, _ptr(input_ids), _ptr(next_tokens), _ptr(unfinished_sequences),
+        1 if has_eos_stopping_criteria else 0, int(pad_token_id or 0), _ptr(eos_token_ids), n_eos,
+        1 if has_max_length_stopping_criteria else 0, int(max_length if max_length is not None else -1), _ptr(out),
+        _ptr(unf), flags))
+    return out, unf

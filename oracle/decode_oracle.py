@@ -219,6 +219,72 @@ def moe_mlp(x, gate_w, up_w, down_w, num_shared, num_experts_total, router_score
 # All-reduce of per-rank fp32 partial sums in fixed rank order 0..P-1, one rounding. (The reference sums
 # 16-bit partials pairwise in half precision, csrc/comms/comm_p2p.cu:889-895 — a documented deviation.)
 # ---------------------------------------------------------------------------------------------------
+# ---- Llama-4 attention prologue, windowed cache, bookkeeping -------------------------------------------------
+
+
+def complex_rope(x: torch.Tensor, position_embeds: torch.Tensor) -> torch.Tensor:
+    """x [B, H, T, D] times (cos + j sin) on interleaved (even, odd) pairs; position_embeds fp32 [B, T, D/2, 2].
+    Follows the reference's CPU branch and HF `apply_rotary_emb` (muillm/modules/attention/llama4attention.py:58-73,
+    kernel csrc/rope/rotary_fp16_kernels.cu:842-942): complex product in fp32, one rounding."""
+    xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2).contiguous())
+    fc = torch.view_as_complex(position_embeds.float().contiguous())
+    return torch.view_as_real(xc * fc[:, None, :, :]).flatten(3).to(x.dtype)
+
+
+def l2norm(x: torch.Tensor, eps: float) -> torch.Tensor:
+    """x * rsqrt(mean(x^2) + eps) in fp32, one rounding (HF Llama4TextL2Norm; kernel csrc/norm/qkl2norm_fp16_kernels.cu:35-140
+    places eps inside the sum instead)."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def temperature_tuning(q: torch.Tensor, cache_position: torch.Tensor, attn_scale: float, floor_scale: float):
+    """q [B, H, T, D] scaled per token (muillm/modules/attention/llama4attention.py:76-108,
+    csrc/temperaturetuning/temperature_tuning_fp16_kernels.cu:10-46)."""
+    s = torch.log1p(torch.floor((cache_position.float() + 1.0) / floor_scale)) * attn_scale + 1.0
+    return (q.float() * s.view(1, 1, -1, 1)).to(q.dtype)
+
+
+def sliding_cache_update(k_in, v_in, k_cache, v_cache, cache_position, seen_tokens):
+    """The three modes of csrc/kvcaches/sliding_kvcache.cpp:87-246 (seen_tokens counts the new tokens); returns
+    (k_states, v_states, k_cache, v_cache) with the caches the caller keeps afterwards."""
+    T, W = k_in.shape[2], k_cache.shape[2]
+    if seen_tokens == T:
+        n = min(T, W)
+        k_cache[:, :, :n] = k_in[:, :, T - n:]
+        v_cache[:, :, :n] = v_in[:, :, T - n:]
+        return k_in, v_in, k_cache, v_cache
+    if seen_tokens > W:
+        n = min(T, W)
+        k_new = torch.cat((k_cache[:, :, n:], k_in[:, :, T - n:]), dim=2)
+        v_new = torch.cat((v_cache[:, :, n:], v_in[:, :, T - n:]), dim=2)
+        return k_new, v_new, k_new, v_new
+    k_cache[:, :, cache_position] = k_in
+    v_cache[:, :, cache_position] = v_in
+    return k_cache[:, :, :seen_tokens], v_cache[:, :, :seen_tokens], k_cache, v_cache
+
+
+def reduce_sum(x: torch.Tensor, dim: int, keep_dim: bool) -> torch.Tensor:
+    """fp32 sum over one dimension, one rounding (csrc/reduce/reduce.cu:33-153)."""
+    return x.float().sum(dim=dim, keepdim=keep_dim).to(x.dtype)
+
+
+def add_tokens_check_finished(input_ids, next_tokens, unfinished, has_eos, pad_token_id, eos_ids, has_max_length,
+                              max_length):
+    """The bookkeeping of HF `GenerationMixin._sample` that csrc/generation/generation.cu:30-213 fuses: finished
+    sequences receive the pad token, the token is appended, then the eos / max-length criteria update the mask."""
+    tok = next_tokens.to(torch.int64)
+    if has_eos:
+        tok = tok * unfinished + pad_token_id * (1 - unfinished)
+    out = torch.cat((input_ids, tok[:, None]), dim=1)
+    done = torch.zeros_like(unfinished, dtype=torch.bool)
+    if has_max_length:
+        done |= out.shape[1] >= max_length
+    if has_eos:
+        done |= torch.isin(tok, eos_ids)
+    return out, unfinished & (~done).to(torch.int64)
+
+
 def all_reduce_fixed_order(partials, out_dtype):
     acc = torch.zeros_like(partials[0], dtype=torch.float32)
     for p in partials:

@@ -157,7 +157,56 @@ def hf_fixtures(out):
         out["hf_model_sd/" + name] = t.half().numpy()
 
 
+def llama4_fixtures(out):
+    """HF Llama-4 building blocks: interleaved rotary embedding, QK L2 norm, temperature scale, sliding window."""
+    from transformers.cache_utils import StaticSlidingWindowLayer
+    from transformers.models.llama4.modeling_llama4 import Llama4TextL2Norm, apply_rotary_emb
+
+    g = torch.Generator().manual_seed(4)
+    B, Hq, Hk, T, D = 2, 5, 2, 3, 128
+    # HF layout is [B, T, H, D] here (rope runs before the transpose); fixtures are stored as [B, H, T, D]
+    q = torch.randn(B, T, Hq, D, generator=g)
+    k = torch.randn(B, T, Hk, D, generator=g)
+    ang = torch.rand(B, T, D // 2, generator=g) * 6.28
+    freqs_cis = torch.polar(torch.ones_like(ang), ang)
+    for dt, tag in ((torch.float16, "f16"), (torch.bfloat16, "bf16")):
+        qr, kr = apply_rotary_emb(q.to(dt), k.to(dt), freqs_cis)
+        out[f"l4_rope_{tag}_q"] = qr.float().transpose(1, 2).contiguous().numpy()
+        out[f"l4_rope_{tag}_k"] = kr.float().transpose(1, 2).contiguous().numpy()
+        nrm = Llama4TextL2Norm(1e-5)
+        out[f"l4_norm_{tag}_q"] = nrm(qr).float().transpose(1, 2).contiguous().numpy()
+        out[f"l4_norm_{tag}_k"] = nrm(kr).float().transpose(1, 2).contiguous().numpy()
+    out["l4_q"] = q.transpose(1, 2).contiguous().numpy()
+    out["l4_k"] = k.transpose(1, 2).contiguous().numpy()
+    out["l4_pos_embeds"] = torch.view_as_real(freqs_cis).contiguous().numpy()
+    # temperature tuning as in Llama4TextAttention.forward (floor_scale 8192, attn_scale 0.1)
+    cache_position = torch.tensor([8190, 8191, 40000])
+    scales = torch.log1p(torch.floor((cache_position.float() + 1.0) / 8192.0)) * 0.1 + 1.0
+    qt = (q.to(torch.bfloat16) * scales.view(1, T, 1, 1)).to(torch.bfloat16)
+    out["l4_temp_pos"] = cache_position.numpy()
+    out["l4_temp_bf16_q"] = qt.float().transpose(1, 2).contiguous().numpy()
+    # sliding window of 6 rows: 4-token prefill, then single-token steps past the window
+    W, Hs, Ds = 6, 2, 8
+    layer = StaticSlidingWindowLayer(max_cache_len=W, sliding_window=W)
+    ks = torch.randn(1, Hs, 12, Ds, generator=g).half()
+    vs = torch.randn(1, Hs, 12, Ds, generator=g).half()
+    out["l4_slide_k"], out["l4_slide_v"] = ks.float().numpy(), vs.float().numpy()
+    kk, vv = layer.update(ks[:, :, :4], vs[:, :, :4], {"cache_position": torch.arange(4)})
+    for step in range(4, 12):
+        kk, vv = layer.update(ks[:, :, step:step + 1], vs[:, :, step:step + 1],
+                              {"cache_position": torch.tensor([step])})
+        n = min(step + 1, W)
+        out[f"l4_slide_states_k_{step}"] = kk[:, :, :n].float().numpy().copy()
+        out[f"l4_slide_states_v_{step}"] = vv[:, :, :n].float().numpy().copy()
+
+
 def main():
+    if sys.argv[1:] == ["llama4"]:
+        l4 = {}
+        llama4_fixtures(l4)
+        np.savez_compressed(os.path.join(HERE, "hf_llama4_ops.npz"), **l4)
+        print("hf_llama4_ops.npz", os.path.getsize(os.path.join(HERE, "hf_llama4_ops.npz")) // 1024, "KiB")
+        return
     ref, hf = {}, {}
     # HF first: in this container, running the reference's bf16/fp16 CPU branches first left the later fp32
     # batched matmul inside LlamaRotaryEmbedding at reduced precision (cos/sin off by 2e-4); in a fresh

@@ -124,9 +124,14 @@ def _case_tp_decode_stack(rank, world, comm):
         stack = LlamaDecodeStack(wl, cl, max_seq=64, batch=1, flags=flags, comm=comm)
         got = stack.greedy(prompt, 32, use_graph=graph).cpu()
         same = (got[0] == want[0]).long().cumprod(0).sum().item()
-        # the sharded sums round differently from the single-device order: identical tokens are expected for
-        # this seeded model, a late divergence would point at logit ties, an early one at a bug
-        assert same == 32, f"flags={flags} graph={graph}: tensor-parallel tokens diverge after {same}: {got.tolist()}"
+        if same < 32:
+            # the sharded fp32 sums round differently from the single-device order; tokens may part ways only at a
+            # near-tie of the oracle's two best logits (teacher-forced on the common prefix), anything else is a bug
+            o = oracle.LlamaOracle(w, cfg, max_T=64)
+            logits = o.forward(torch.cat((prompt, want[:, :same]), dim=1))[0]
+            margin = (logits[want[0, same]] - logits[got[0, same]]).item()
+            assert 0 <= margin < 1e-2, (f"flags={flags} graph={graph}: tensor-parallel tokens diverge after {same} "
+                                        f"with logit margin {margin}: {got.tolist()}")
         del stack
 
 

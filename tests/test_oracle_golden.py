@@ -129,3 +129,53 @@ def test_all_reduce_fixed_order_is_deterministic():
     b = oracle.all_reduce_fixed_order(parts, torch.float16)
     assert torch.equal(a, b)
     torch.testing.assert_close(a.float(), torch.stack(parts).sum(0), rtol=2e-3, atol=2e-3)
+
+
+# ---- Llama-4 attention prologue and sliding window (HF Llama-4 building blocks) ----------------------------------
+
+
+@pytest.fixture(scope="module")
+def l4():
+    return np.load(os.path.join(GOLD, "hf_llama4_ops.npz"))
+
+
+@pytest.mark.parametrize("tag,dtype", [("f16", torch.float16), ("bf16", torch.bfloat16)])
+def test_llama4_complex_rope_and_l2norm_bit_exact(l4, tag, dtype):
+    pe = T(l4["l4_pos_embeds"])
+    for name in ("q", "k"):
+        x = T(l4[f"l4_{name}"], dtype)
+        rot = oracle.complex_rope(x, pe)
+        assert torch.equal(rot.float(), T(l4[f"l4_rope_{tag}_{name}"]))
+        assert torch.equal(oracle.l2norm(rot, 1e-5).float(), T(l4[f"l4_norm_{tag}_{name}"]))
+
+
+def test_llama4_temperature_tuning_bit_exact(l4):
+    q = T(l4["l4_q"], torch.bfloat16)
+    got = oracle.temperature_tuning(q, T(l4["l4_temp_pos"]), 0.1, 8192.0)
+    assert torch.equal(got.float(), T(l4["l4_temp_bf16_q"]))
+
+
+def test_sliding_window_states_match_hf_layer(l4):
+    ks, vs = T(l4["l4_slide_k"], torch.float16), T(l4["l4_slide_v"], torch.float16)
+    W = 6
+    kc = torch.zeros(1, ks.shape[1], W, ks.shape[3], dtype=torch.float16)
+    vc = torch.zeros_like(kc)
+    _, _, kc, vc = oracle.sliding_cache_update(ks[:, :, :4], vs[:, :, :4], kc, vc, torch.arange(4), 4)
+    for step in range(4, 12):
+        k_st, v_st, kc, vc = oracle.sliding_cache_update(ks[:, :, step:step + 1], vs[:, :, step:step + 1], kc, vc,
+                                                         torch.tensor([step]), step + 1)
+        assert torch.equal(k_st.float(), T(l4[f"l4_slide_states_k_{step}"])), step
+        assert torch.equal(v_st.float(), T(l4[f"l4_slide_states_v_{step}"])), step
+
+
+def test_add_tokens_check_finished_matches_generation_loop_semantics():
+    ids = torch.tensor([[5, 6, 7], [8, 9, 10], [1, 2, 3]])
+    nxt = torch.tensor([11, 2, 99], dtype=torch.int32)
+    unf = torch.tensor([1, 1, 0])
+    out, u = oracle.add_tokens_check_finished(ids, nxt, unf, True, 0, torch.tensor([2, 77]), True, 5)
+    assert out.tolist() == [[5, 6, 7, 11], [8, 9, 10, 2], [1, 2, 3, 0]]
+    assert u.tolist() == [1, 0, 0]
+    out, u = oracle.add_tokens_check_finished(ids, nxt, unf, True, 0, torch.tensor([2]), True, 4)
+    assert u.tolist() == [0, 0, 0]
+    out, u = oracle.add_tokens_check_finished(ids, nxt, unf, False, 0, torch.tensor([2]), False, -1)
+    assert out[:, -1].tolist() == [11, 2, 99] and u.tolist() == [1, 1, 0]
