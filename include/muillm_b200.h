@@ -370,6 +370,19 @@ MUI_API mui_status_t mui_parallel_gateupdown_forward(mui_comm_t* comm, void* str
                                                      const void* down_weights, const void* residual, const void* x,
                                                      void* scratch_t, void* y, unsigned flags);
 
+/* Sharded MoE MLP: every expert's gate/up rows and down columns are split across ranks ([(shared + routed)·I_local, H]
+ * and [(shared + routed)·H, I_local]); the router outputs are replicated. Gate/up is local; the down kernel sums the
+ * computed experts and all-reduces across ranks in the same launch; the residual enters on rank 0. scratch_t holds
+ * [num_shared + top_k, I_local] elements. Replaces muillm_parallel_gateupsilumoe_forward
+ * (csrc/parallel_gateupmoe_kernels.cu:6-125). */
+MUI_API mui_status_t mui_parallel_moe_mlp_forward(mui_comm_t* comm, void* stream, mui_dtype_t dtype, int num_shared,
+                                                  int num_routed, int top_k, int I_local, int H,
+                                                  const void* norm_weights, float epsilon, const void* gate_weights,
+                                                  const void* up_weights, const void* down_weights,
+                                                  const void* residual, const void* x, const void* router_scores,
+                                                  const int64_t* router_indices, void* scratch_t, void* y,
+                                                  unsigned flags);
+
 /* ---- embedding row gather (csrc/embedding/embedding_xx16_kernels.cu:26,74) ------------------------
  * out[i, :] = table[token_ids[i], :] for 16-bit tables [vocab, H]; token ids are int64 on the device and
  * are clamped to [0, vocab). */

@@ -204,6 +204,11 @@ PROTOTYPES = {
         [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_void_p, c_uint],
     ),
+    "mui_parallel_moe_mlp_forward": (
+        c_int,
+        [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint],
+    ),
     "mui_embedding_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_scratch_bytes": (c_size_t, [POINTER(LlamaConfig)]),
     "mui_llama_stack_create": (

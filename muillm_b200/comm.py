@@ -89,3 +89,24 @@ class MuiCommunicator:
             self._h, _stream(), _dtype_code(x), B, I, H, _ptr(norm_weights), float(epsilon), _ptr(gate_weights),
             _ptr(up_weights), _ptr(down_weights), _ptr(residual), _ptr(x), _ptr(t), _ptr(y), flags))
         return y
+
+    def parallel_moe_mlp(self, num_shared_experts, num_dynamic_experts, norm_weights, epsilon, gate_weights,
+                         up_weights, down_weights, residual, x, router_scores, router_indices, flags=0):
+        """Sharded MoE MLP for one token: packed expert shards [(shared + routed) * I_local, H] /
+        [(shared + routed) * H, I_local], replicated router outputs, all-reduce fused into the down kernel
+        (muillm_parallel_gateupsilumoe_forward, csrc/parallel_gateupmoe_kernels.cu:6-125)."""
+        for t, n in ((x, "x"), (gate_weights, "gate_weights"), (up_weights, "up_weights"),
+                     (down_weights, "down_weights"), (norm_weights, "norm_weights"), (residual, "residual"),
+                     (router_scores, "router_scores"), (router_indices, "router_indices")):
+            _check_input(t, n)
+        total = num_shared_experts + num_dynamic_experts
+        H = x.shape[-1]
+        I = gate_weights.shape[0] // total
+        top_k = 0 if router_indices is None else router_indices.shape[-1]
+        t = torch.empty((num_shared_experts + top_k, I), dtype=x.dtype, device=x.device)
+        y = torch.empty_like(x)
+        capi.check(self.lib.mui_parallel_moe_mlp_forward(
+            self._h, _stream(), _dtype_code(x), num_shared_experts, num_dynamic_experts, top_k, I, H,
+            _ptr(norm_weights), float(epsilon), _ptr(gate_weights), _ptr(up_weights), _ptr(down_weights),
+            _ptr(residual), _ptr(x), _ptr(router_scores), _ptr(router_indices), _ptr(t), _ptr(y), flags))
+        return y

@@ -449,4 +449,40 @@ mui_status_t mui_parallel_gateupdown_forward(mui_comm_t* c, void* stream, mui_dt
                                      residual, scratch_t, y, flags);
 }
 
+mui_status_t mui_parallel_moe_mlp_forward(mui_comm_t* c, void* stream, mui_dtype_t dtype, int num_shared,
+                                          int num_routed, int top_k, int I_local, int H, const void* norm_weights,
+                                          float epsilon, const void* gate_weights, const void* up_weights,
+                                          const void* down_weights, const void* residual, const void* x,
+                                          const void* router_scores, const int64_t* router_indices, void* scratch_t,
+                                          void* y, unsigned flags) {
+  if (mui_status_t s = check_ready(c)) return s;
+  MUI_REQUIRE(scratch_t != nullptr, MUI_ERR_INVALID_ARG,
+              "scratch_t must be non-null ([num_shared + top_k, I_local] elements)");
+  MUI_REQUIRE(down_weights && y, MUI_ERR_INVALID_ARG, "down_weights and y must be non-null");
+  MUI_REQUIRE((size_t)H <= c->capacity, MUI_ERR_UNSUPPORTED, "H=%d exceeds the communicator capacity %zu", H,
+              c->capacity);
+  mui_status_t s = mui_moe_gateup_silu_forward(stream, dtype, num_shared, num_routed, top_k, I_local, H, norm_weights,
+                                               epsilon, gate_weights, up_weights, x, router_scores, router_indices,
+                                               scratch_t, flags);
+  if (s != MUI_OK) return s;
+  GemvArgs a;
+  memset(&a, 0, sizeof(a));
+  a.W = down_weights;
+  a.x = scratch_t;
+  a.residual = (c->rank == 0) ? residual : nullptr;
+  a.y = y;
+  a.N = H;
+  a.K = I_local;
+  a.B = 1;
+  a.Kp = (I_local + 7) & ~7;
+  a.moe_mode = GEMV_MOE_SEGMENTS;
+  a.slots = num_shared + top_k;
+  a.num_shared = num_shared;
+  a.router_indices = router_indices;
+  a.w8_fmt = -1;
+  a.use_comm = 1;
+  fill_dev(c, &a.comm);
+  return mui_launch_gemv16((cudaStream_t)stream, dtype, 0, a, flags);
+}
+
 }  // extern "C"

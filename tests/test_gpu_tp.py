@@ -107,6 +107,36 @@ def _case_parallel_mlp(rank, world, comm):
     torch.testing.assert_close(got.float().cpu(), want.float(), rtol=1e-2, atol=2e-3)
 
 
+def _case_parallel_moe(rank, world, comm):
+    from muillm_b200 import capi
+
+    for dtype in (torch.float16, torch.bfloat16):
+        for (H, I, shared, routed, top_k) in ((512, 64 * world, 1, 4, 1), (5120, 256 * world, 1, 16, 1),
+                                              (256, 24 * world, 0, 8, 2)):
+            g = torch.Generator().manual_seed(H + I + top_k)
+            E = shared + routed
+            x = torch.randn(1, 1, H, generator=g).to(dtype)
+            nw = (1 + 0.01 * torch.randn(H, generator=g)).to(dtype)
+            G = (torch.randn(E, I, H, generator=g) * 0.03).to(dtype)
+            U = (torch.randn(E, I, H, generator=g) * 0.03).to(dtype)
+            Dw = (torch.randn(E, H, I, generator=g) * 0.03).to(dtype)
+            scores, idx = oracle.topk_sigmoid(torch.randn(1, 1, routed, generator=g).to(dtype), top_k)
+            want = oracle.moe_mlp(x, G.reshape(E * I, H), U.reshape(E * I, H), Dw.reshape(E * H, I), shared, E, scores,
+                                  idx, norm_weights=nw, eps=1e-5, residual=x)
+            # every expert's intermediate dimension is split across the ranks
+            s = I // world
+            sl = slice(rank * s, (rank + 1) * s)
+            Gl = G[:, sl].reshape(E * s, H).contiguous().cuda()
+            Ul = U[:, sl].reshape(E * s, H).contiguous().cuda()
+            Dl = Dw[:, :, sl].reshape(E * H, s).contiguous().cuda()
+            xc = x.cuda()
+            for flags in (0, capi.MUI_FLAG_PDL):
+                got = comm.parallel_moe_mlp(shared, routed, nw.cuda(), 1e-5, Gl, Ul, Dl, xc, xc,
+                                            scores.reshape(-1).cuda(), idx.reshape(-1).cuda(), flags=flags)
+                tol = dict(rtol=1e-2, atol=2e-3) if dtype == torch.float16 else dict(rtol=2e-2, atol=8e-3)
+                torch.testing.assert_close(got.float().cpu(), want.float(), **tol)
+
+
 def _case_tp_decode_stack(rank, world, comm):
     from muillm_b200 import capi
     from muillm_b200.decoder_stack import LlamaDecodeStack, shard_llama_weights
@@ -149,3 +179,7 @@ def test_parallel_mlp_fused_all_reduce():
 
 def test_tp_decode_stack_greedy_tokens():
     _run("_case_tp_decode_stack")
+
+
+def test_parallel_moe_mlp_fused_all_reduce():
+    _run("_case_parallel_moe")
