@@ -382,6 +382,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
     if (tid == 0) trace_mark(a.trace, 3, true);
 
     float d[4] = {0.f, 0.f, 0.f, 0.f};
+    float d2[4] = {0.f, 0.f, 0.f, 0.f};  // 8-bit path only
     // ldmatrix sources. A (weight tile, 16 rows x 16 k): lane gives tile row (lane%8) + 8*((lane/8)%2), k offset
     // 8*(lane/16). B (activations, 16 k x 8 batch): lanes 0-15 give staged row min(lane%8, NB-1) (columns past
     // the batch repeat the last row; their results are never read), k offset 8*((lane/8)%2).
@@ -425,35 +426,22 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
         const int n_row = ((lane >> 2) < NB) ? (lane >> 2) : (NB - 1);
         const T* xrow = x_s + (size_t)(n_row + seg) * x_pitch + (size_t)kc * KC + (lane & 3) * 4;
         const bool sgn = (a.w8_fmt == MUI_W8_SYM_ROW);
-#pragma unroll 2
+        const uint32_t xmask = sgn ? 0x80808080u : 0u, cbias = W8Cvt<T>::bias_for(sgn);
+        const uint32_t x_addr = smem_u32(xrow);
+#pragma unroll 4
         for (int j = warp; j < nsteps; j += GEMV_CONSUMER_WARPS) {
           uint32_t r[4];
           ldmatrix_x4(r, a_addr + j * 32);
-          const uint2 xa = *reinterpret_cast<const uint2*>(xrow + j * 32);
-          const uint2 xb = *reinterpret_cast<const uint2*>(xrow + j * 32 + 16);
-          uint32_t lo0, hi0, lo1, hi1;
-          if (sgn) {
-            W8Cvt<T>::template cvt4<true>(r[0], lo0, hi0);
-            W8Cvt<T>::template cvt4<true>(r[1], lo1, hi1);
-          } else {
-            W8Cvt<T>::template cvt4<false>(r[0], lo0, hi0);
-            W8Cvt<T>::template cvt4<false>(r[1], lo1, hi1);
-          }
-          {
-            const uint32_t af[4] = {lo0, lo1, hi0, hi1};
-            MmaOp<T>::run(d, af, xa.x, xa.y);
-          }
-          if (sgn) {
-            W8Cvt<T>::template cvt4<true>(r[2], lo0, hi0);
-            W8Cvt<T>::template cvt4<true>(r[3], lo1, hi1);
-          } else {
-            W8Cvt<T>::template cvt4<false>(r[2], lo0, hi0);
-            W8Cvt<T>::template cvt4<false>(r[3], lo1, hi1);
-          }
-          {
-            const uint32_t af[4] = {lo0, lo1, hi0, hi1};
-            MmaOp<T>::run(d, af, xb.x, xb.y);
-          }
+          uint32_t xa0, xa1, xb0, xb1;
+          lds_v2(x_addr + j * 64, xa0, xa1);
+          lds_v2(x_addr + j * 64 + 32, xb0, xb1);
+          uint32_t af[4], bf[4];
+          W8Cvt<T>::cvt4(r[0], xmask, cbias, af[0], af[2]);
+          W8Cvt<T>::cvt4(r[1], xmask, cbias, af[1], af[3]);
+          W8Cvt<T>::cvt4(r[2], xmask, cbias, bf[0], bf[2]);
+          W8Cvt<T>::cvt4(r[3], xmask, cbias, bf[1], bf[3]);
+          MmaOp<T>::run(d, af, xa0, xa1);
+          MmaOp<T>::run(d2, bf, xb0, xb1);  // second accumulator: halves the dependent mma chain
         }
       }
       __syncwarp();
@@ -466,6 +454,13 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
         float* rbuf = red + (blk & 1) * (GEMV_CONSUMER_WARPS * PIPE_ROWS * NB);
         // this thread holds D[tile row lane/4 (+8)][batch (lane%4)*2 + {0,1}]
         const int trow = lane >> 2, n0 = (lane & 3) * 2;
+        if (WB == 8) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            d[q] += d2[q];
+            d2[q] = 0.f;
+          }
+        }
         if (n0 < NB) {
           rbuf[(warp * PIPE_ROWS + trow) * NB + n0] = d[0];
           rbuf[(warp * PIPE_ROWS + trow + 8) * NB + n0] = d[2];

@@ -290,31 +290,47 @@ __device__ __forceinline__ float dot16_w8(const uint4& w, const float (&x)[16]) 
 // Four 8-bit integers (one 32-bit register) -> two packed 16-bit pairs {q0,q1}, {q2,q3}, exactly, without
 // integer-to-float conversion instructions: the byte is planted in the mantissa of a constant and the
 // constant subtracted (fp16: 1024 + u; bf16: through fp32 8388608 + u, then one packing conversion).
+// `xmask` flips the sign bits of signed bytes (0x80808080, else 0) and `bias` is the matching constant
+// (fp16 pair 1152 / 1024; fp32 8388736 / 8388608 for bf16), both loop-invariant registers, so that one code path
+// serves both 8-bit formats without a branch.
 template <typename T> struct W8Cvt;
 template <> struct W8Cvt<__half> {
-  template <bool SIGNED>
-  static __device__ __forceinline__ void cvt4(uint32_t r, uint32_t& lo, uint32_t& hi) {
-    const uint32_t v = SIGNED ? (r ^ 0x80808080u) : r;
+  static __device__ __forceinline__ uint32_t bias_for(bool is_signed) {
+    const __half2 b = is_signed ? __floats2half2_rn(1152.f, 1152.f) : __floats2half2_rn(1024.f, 1024.f);
+    return *reinterpret_cast<const uint32_t*>(&b);
+  }
+  static __device__ __forceinline__ void cvt4(uint32_t r, uint32_t xmask, uint32_t bias, uint32_t& lo, uint32_t& hi) {
+    const uint32_t v = r ^ xmask;
     const uint32_t plo = __byte_perm(v, 0x64646464u, 0x5140);
     const uint32_t phi = __byte_perm(v, 0x64646464u, 0x5342);
-    const __half2 bias = SIGNED ? __floats2half2_rn(1152.f, 1152.f) : __floats2half2_rn(1024.f, 1024.f);
-    __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&plo), bias);
-    __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&phi), bias);
-    lo = *reinterpret_cast<uint32_t*>(&a);
-    hi = *reinterpret_cast<uint32_t*>(&b);
+    const __half2 b = *reinterpret_cast<const __half2*>(&bias);
+    __half2 x = __hsub2(*reinterpret_cast<const __half2*>(&plo), b);
+    __half2 y = __hsub2(*reinterpret_cast<const __half2*>(&phi), b);
+    lo = *reinterpret_cast<uint32_t*>(&x);
+    hi = *reinterpret_cast<uint32_t*>(&y);
+  }
+  template <bool SIGNED>
+  static __device__ __forceinline__ void cvt4(uint32_t r, uint32_t& lo, uint32_t& hi) {
+    cvt4(r, SIGNED ? 0x80808080u : 0u, bias_for(SIGNED), lo, hi);
   }
 };
 template <> struct W8Cvt<__nv_bfloat16> {
-  template <bool SIGNED>
-  static __device__ __forceinline__ void cvt4(uint32_t r, uint32_t& lo, uint32_t& hi) {
-    const uint32_t v = SIGNED ? (r ^ 0x80808080u) : r;
-    const float bias = SIGNED ? 8388736.f : 8388608.f;
-    const float f0 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650)) - bias;
-    const float f1 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7651)) - bias;
-    const float f2 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7652)) - bias;
-    const float f3 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7653)) - bias;
+  static __device__ __forceinline__ uint32_t bias_for(bool is_signed) {
+    return __float_as_uint(is_signed ? 8388736.f : 8388608.f);
+  }
+  static __device__ __forceinline__ void cvt4(uint32_t r, uint32_t xmask, uint32_t bias, uint32_t& lo, uint32_t& hi) {
+    const uint32_t v = r ^ xmask;
+    const float b = __uint_as_float(bias);
+    const float f0 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650)) - b;
+    const float f1 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7651)) - b;
+    const float f2 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7652)) - b;
+    const float f3 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7653)) - b;
     lo = Elt<__nv_bfloat16>::pack2(f0, f1);
     hi = Elt<__nv_bfloat16>::pack2(f2, f3);
+  }
+  template <bool SIGNED>
+  static __device__ __forceinline__ void cvt4(uint32_t r, uint32_t& lo, uint32_t& hi) {
+    cvt4(r, SIGNED ? 0x80808080u : 0u, bias_for(SIGNED), lo, hi);
   }
 };
 
