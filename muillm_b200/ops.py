@@ -243,6 +243,19 @@ def muillm_gateupsilumoe_forward(engine, num_shared_experts, num_dynamic_experts
     return y
 
 
+def muillm_embedding_forward(weights, inputs, flags=0):
+    """Row gather out[..., :] = weights[inputs[...], :] for int64 token ids (csrc/embedding/embedding_xx16_kernels.cu:26)."""
+    _check_input(weights, "weights")
+    _check_input(inputs, "inputs")
+    if inputs.dtype != torch.int64:
+        raise RuntimeError("token ids must be int64")
+    vocab, H = weights.shape
+    out = torch.empty(tuple(inputs.shape) + (H,), dtype=weights.dtype, device=weights.device)
+    capi.check(capi.lib().mui_embedding_forward(_stream(), _dtype_code(weights), inputs.numel(), H, vocab,
+                                                _ptr(weights), _ptr(inputs), _ptr(out), flags))
+    return out
+
+
 def _w8_fmt(qweights):
     if qweights.dtype == torch.int8:
         return capi.MUI_W8_SYM_ROW
