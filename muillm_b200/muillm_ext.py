@@ -189,7 +189,7 @@ class muillm_synchronizer_ptr:
     pass
 
 
-def muillm_sync_init(engine):
+def muillm_sync_init():
     return muillm_synchronizer_ptr()
 
 

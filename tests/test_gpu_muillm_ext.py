@@ -197,7 +197,7 @@ def test_synchronizer_and_embedding():
     emb = ext.muillm_embedding_module_init(None, torch.arange(40, dtype=torch.float16).reshape(10, 4).cuda())
     out = ext.muillm_embedding_module_forward(emb, torch.tensor([[3, 9]], device="cuda"))
     assert out.shape == (1, 2, 4) and out[0, 1].tolist() == [36.0, 37.0, 38.0, 39.0]
-    sync = ext.muillm_sync_init(None)
+    sync = ext.muillm_sync_init()
     assert ext.muillm_item_bool(sync, torch.tensor(True, device="cuda")) is True
     assert math.isclose(ext.muillm_item_f32(sync, torch.tensor(1.5, device="cuda")), 1.5)
     assert ext.muillm_to_cpu(sync, torch.ones(2, device="cuda")).device.type == "cpu"
