@@ -52,6 +52,9 @@ typedef enum { MUI_W8_SYM_ROW = 0, MUI_W8_GROUP_MIN = 1 } mui_w8_format_t;
 #define MUI_FLAG_MEGAKERNEL 8u    /* decode stack only: run the whole step as ONE persistent kernel (one CTA per SM,
                                     continuous weight stream, grid barriers between operations); batch 1 only */
 #define MUI_FLAG_FORCE_PIPELINE 4u /* fail with MUI_ERR_UNSUPPORTED instead of falling back to the plain-load kernel */
+#define MUI_FLAG_SHORT_CONTEXT 16u  /* mui_rope_flash_decode / decode stack: at most a few hundred tokens are attended;
+                                      one CTA per KV head stages the whole K/V history in shared memory (up to 384 rows
+                                      per round) before the QKV projection has finished. Correct for any length. */
 
 MUI_API const char* mui_status_string(mui_status_t s);
 MUI_API const char* mui_last_error(void);

@@ -34,6 +34,7 @@ MUI_FLAG_PDL = 1
 MUI_FLAG_FORCE_GENERIC = 2
 MUI_FLAG_FORCE_PIPELINE = 4
 MUI_FLAG_MEGAKERNEL = 8
+MUI_FLAG_SHORT_CONTEXT = 16
 
 
 class Strides3(Structure):

@@ -41,6 +41,16 @@ unsigned long long* mui_trace_next_record(int kernel_tag) {
 static thread_local const void* tls_pf_ptr[3] = {nullptr, nullptr, nullptr};
 static thread_local int tls_pf_rows[3] = {0, 0, 0}, tls_pf_row_bytes[3] = {0, 0, 0}, tls_pf_frac[3] = {0, 0, 0};
 
+// Number of SMs the next GEMV launch of this thread leaves free (for a small kernel that should become resident
+// beside it); consumed by that launch.
+static thread_local int tls_reserve_sms = 0;
+void mui_set_gemv_reserve_sms(int n) { tls_reserve_sms = n > 0 ? n : 0; }
+int mui_take_gemv_reserve_sms() {
+  const int n = tls_reserve_sms;
+  tls_reserve_sms = 0;
+  return n;
+}
+
 void mui_take_prefetch_hint(const void** ptrs, int* rows, int* row_bytes, int* frac1024) {
   for (int i = 0; i < 3; ++i) {
     ptrs[i] = tls_pf_ptr[i];

@@ -15,6 +15,7 @@
 // csrc/attention/flash_decoding.cu:288-305) on the decode path; the stand-alone kernels stay for the other uses
 // (prefill RoPE, masks, strided views).
 #include "common.cuh"
+#include "gemv_common.cuh"
 
 #include <algorithm>
 
@@ -306,6 +307,252 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_cluster_kernel(c
   if (tid == 0) trace_end(a.trace);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Short-context variant: ONE CTA per (KV head, sequence), no cluster, so the launch can become resident while the
+// QKV projection is still running (that GEMV leaves Hkv*B SMs free for it, see GemvArgs::reserve_sms). Before it
+// waits for the projection it reads the decode state (final since the previous step's arg-max, which finished
+// before the projection was allowed to start) and pulls the whole K/V history of its head into shared memory with
+// 16-byte asynchronous copies into rows padded to 272 bytes (conflict-free ldmatrix); after the wait only the new
+// token's q/k/v (one L2 round trip) and the arithmetic are left, and the arithmetic runs on the tensor cores with
+// the query heads of the group as the m dimension (padded to 16):
+//   pass 1   S^T[head, token] = Q[head, :] . K[token, :]      mma m16n8k16, A = q fragments, B = K rows (ldmatrix)
+//   pass 2   O[head, :] = P[head, tokens] . V[tokens, :]       A = exp2(s - max) as a 16-bit value + 16-bit correction,
+//                                                              B = V rows through ldmatrix.trans; warps split the
+//                                                              tokens and add their partials; denominators in fp32
+// At most RA_ROWS tokens (the new one included); a longer history records MUI_DEV_BAD_LENGTH and writes nothing —
+// the caller picks this variant (MUI_FLAG_SHORT_CONTEXT) only when it can bound the length.
+constexpr int RA_ROWS = 384;
+constexpr int RA_PITCH = FA_D + 8;  // elements
+
+template <int GP> constexpr size_t ra_smem_bytes() {
+  return (size_t)2 * RA_ROWS * RA_PITCH * 2 + (size_t)GP * FA_D * 2 + (size_t)GP * RA_ROWS * 4 +
+         (size_t)2 * FA_WARPS * GP * 4 + 32;
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+
+template <typename T, int GP>
+__global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(const FaArgs a) {
+  extern __shared__ __align__(128) unsigned char ra_smem[];
+  T* Ks = reinterpret_cast<T*>(ra_smem);
+  T* Vs = Ks + (size_t)RA_ROWS * RA_PITCH;
+  T* Qs = Vs + (size_t)RA_ROWS * RA_PITCH;                         // [GP][D] rotated queries
+  float* Sc = reinterpret_cast<float*>(Qs + GP * FA_D);            // [GP][RA_ROWS] scores * scale * log2(e)
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int G = a.G;
+  trace_start(a.trace);
+
+  // ---- before the dependency wait: decode state + K/V history (nothing the previous kernel writes) ----
+  const long long pos_id = __ldcg(a.position_ids + b);
+  const long long cache_pos = __ldcg(a.cache_position);
+  const int S = min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
+  if (S > RA_ROWS) {
+    if (tid == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(S));
+    return;
+  }
+  const int cached = S - 1;
+  T* kc = reinterpret_cast<T*>(a.k_cache) + ((size_t)b * a.Hkv + kvh) * a.max_seq * FA_D;
+  T* vc = reinterpret_cast<T*>(a.v_cache) + ((size_t)b * a.Hkv + kvh) * a.max_seq * FA_D;
+  // 16-byte asynchronous copies (cp.async): each lands at its padded position; a bulk copy could not pad, and one
+  // bulk copy per row costs the copy engine ~15 ns each
+  {
+    const uint32_t ks_u = smem_u32(Ks), vs_u = smem_u32(Vs);
+    const int pieces = cached * (FA_D / 8);
+    for (int i = tid; i < pieces; i += FA_THREADS) {
+      const int r = i >> 4, c = (i & 15) * 8;
+      const uint32_t so = static_cast<uint32_t>((r * RA_PITCH + c) * 2);
+      const size_t go = (size_t)r * FA_D + c;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks_u + so), "l"(kc + go) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs_u + so), "l"(vc + go) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  // rows of the last 16-token slab past the sequence multiply probabilities that are zero: they must be finite
+  {
+    const int r = S + (tid >> 4);
+    if (r < ((S + 15) & ~15)) *reinterpret_cast<uint4*>(Vs + (size_t)r * RA_PITCH + (tid & 15) * 8) = make_uint4(0, 0, 0, 0);
+  }
+  constexpr int LPT = FA_D / 8;  // 16 lanes hold one 128-element row
+  const int sub = lane / LPT, dlane = lane % LPT, d0 = dlane * 8;
+  float cs[8], sn[8];
+  unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.cos_t) + (size_t)pos_id * FA_D + d0), cs);
+  unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.sin_t) + (size_t)pos_id * FA_D + d0), sn);
+  pdl_launch_dependents();
+  pdl_wait_prior_grid();
+  if (tid == 0) trace_mark(a.trace, 2, false);
+
+  // ---- the new token: half-warp `slot` rotates query head `slot` (< G), the key (== G) or copies the value (== G+1) ----
+  {
+    const int slot = warp * 2 + sub;
+    const T* row = reinterpret_cast<const T*>(a.qkv) + (size_t)b * (a.Hq + 2 * a.Hkv) * FA_D;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (slot < G) raw = ld_act16(row + ((size_t)kvh * G + slot) * FA_D + d0);
+    else if (slot == G) raw = ld_act16(row + ((size_t)a.Hq + kvh) * FA_D + d0);
+    else if (slot == G + 1) raw = ld_act16(row + ((size_t)a.Hq + a.Hkv + kvh) * FA_D + d0);
+    float x[8];
+    unpack8<T>(raw, x);
+    fa_rope8<T>(x, cs, sn, dlane < (LPT / 2));  // every lane takes part in the shuffles
+    const uint4 rot = pack8<T>(x);
+    if (slot < G) {
+      *reinterpret_cast<uint4*>(Qs + (size_t)slot * FA_D + d0) = rot;
+    } else if (slot == G) {
+      *reinterpret_cast<uint4*>(Ks + (size_t)cached * RA_PITCH + d0) = rot;
+      *reinterpret_cast<uint4*>(kc + (size_t)cache_pos * FA_D + d0) = rot;
+    } else if (slot == G + 1) {
+      *reinterpret_cast<uint4*>(Vs + (size_t)cached * RA_PITCH + d0) = raw;
+      *reinterpret_cast<uint4*>(vc + (size_t)cache_pos * FA_D + d0) = raw;
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's pieces of the history have landed
+  __syncthreads();
+
+  const int hrow = lane >> 2, cpair = (lane & 3) * 2;  // fragment coordinates of this lane
+  const bool real_head = hrow < G;
+
+  // ---- pass 1: scores; warp w takes token tiles w, w + 8, ... and keeps the running maximum of its tiles ----
+  float* wmax = Sc + GP * RA_ROWS;         // [WARPS][GP]
+  float* wsum = wmax + FA_WARPS * GP;      // [WARPS][GP]
+  {
+    uint32_t qa[8][2];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      qa[kk][0] = real_head ? *reinterpret_cast<const uint32_t*>(Qs + (size_t)hrow * FA_D + kk * 16 + cpair) : 0u;
+      qa[kk][1] = real_head ? *reinterpret_cast<const uint32_t*>(Qs + (size_t)hrow * FA_D + kk * 16 + 8 + cpair) : 0u;
+    }
+    const int ntile = (S + 7) >> 3;
+    // ldmatrix: lane gives row (lane % 8) of matrix (lane / 8); matrices = d offsets 0, 8, 16, 24 of a 32-wide k pair
+    const uint32_t k_base = smem_u32(Ks) + static_cast<uint32_t>(((lane & 7) * RA_PITCH + (lane >> 3) * 8) * 2);
+    float mx = -INFINITY;
+    for (int j = warp; j < ntile; j += FA_WARPS) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};  // two chains of four dependent mma
+      const uint32_t tile_addr = k_base + static_cast<uint32_t>(j * 8 * RA_PITCH * 2);
+#pragma unroll
+      for (int k2 = 0; k2 < 4; ++k2) {
+        uint32_t r[4];
+        ldmatrix_x4(r, tile_addr + k2 * 64);
+        const uint32_t a0[4] = {qa[2 * k2][0], 0u, qa[2 * k2][1], 0u};
+        const uint32_t a1[4] = {qa[2 * k2 + 1][0], 0u, qa[2 * k2 + 1][1], 0u};
+        MmaOp<T>::run(acc, a0, r[0], r[1]);
+        MmaOp<T>::run(acc2, a1, r[2], r[3]);
+      }
+      if (real_head) {
+        const int t0 = j * 8 + cpair;
+        const float s0 = (acc[0] + acc2[0]) * a.scale_log2, s1 = (acc[1] + acc2[1]) * a.scale_log2;
+        if (t0 < S) {
+          Sc[hrow * RA_ROWS + t0] = s0;
+          mx = fmaxf(mx, s0);
+        }
+        if (t0 + 1 < S) {
+          Sc[hrow * RA_ROWS + t0 + 1] = s1;
+          mx = fmaxf(mx, s1);
+        }
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(MUI_FULL_MASK, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(MUI_FULL_MASK, mx, 2));
+    if (real_head && (lane & 3) == 0) wmax[warp * GP + hrow] = mx;
+  }
+  __syncthreads();
+
+  // ---- pass 2: O = P V; warp w takes 16-token slabs w, w + 8, ... for all 128 columns (16 independent accumulator
+  // tiles), then the warps' partial outputs and denominators are summed through shared memory (the K rows are no
+  // longer needed, their space holds the partials). The probabilities enter the tensor cores as a 16-bit value plus
+  // a 16-bit correction (two mma per tile), which keeps them at fp32-like accuracy. ----
+  float* red = reinterpret_cast<float*>(Ks);  // [WARPS][GP][D]
+  {
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const float* sc = Sc + (real_head ? hrow : 0) * RA_ROWS;
+    float mh = -INFINITY;
+    if (real_head) {
+#pragma unroll
+      for (int w = 0; w < FA_WARPS; ++w) mh = fmaxf(mh, wmax[w * GP + hrow]);
+    }
+    // ldmatrix.trans: matrix (lane / 8): bit 0 = token half (+8 rows), bit 1 = column tile (+8 columns)
+    const uint32_t v_base = smem_u32(Vs) +
+        static_cast<uint32_t>((((lane & 7) + ((lane >> 3) & 1) * 8) * RA_PITCH + (lane >> 4) * 8) * 2);
+    const int nslab = (S + 15) >> 4;
+    float lsum = 0.f;
+    for (int t = warp; t < nslab; t += FA_WARPS) {
+      uint32_t ph[4] = {0u, 0u, 0u, 0u}, pl[4] = {0u, 0u, 0u, 0u};
+      if (real_head) {
+        const int t0 = t * 16 + cpair;
+        const float p0 = (t0 < S) ? exp2f(sc[t0] - mh) : 0.f;
+        const float p1 = (t0 + 1 < S) ? exp2f(sc[t0 + 1] - mh) : 0.f;
+        const float p2 = (t0 + 8 < S) ? exp2f(sc[t0 + 8] - mh) : 0.f;
+        const float p3 = (t0 + 9 < S) ? exp2f(sc[t0 + 9] - mh) : 0.f;
+        lsum += (p0 + p1) + (p2 + p3);
+        ph[0] = Elt<T>::pack2(p0, p1);
+        ph[2] = Elt<T>::pack2(p2, p3);
+        const float2 h01 = Elt<T>::unpack2(ph[0]), h23 = Elt<T>::unpack2(ph[2]);
+        pl[0] = Elt<T>::pack2(p0 - h01.x, p1 - h01.y);
+        pl[2] = Elt<T>::pack2(p2 - h23.x, p3 - h23.y);
+      }
+      const uint32_t slab_addr = v_base + static_cast<uint32_t>(t * 16 * RA_PITCH * 2);
+#pragma unroll
+      for (int n2 = 0; n2 < 8; ++n2) {
+        uint32_t r[4];
+        ldmatrix_x4_trans(r, slab_addr + n2 * 32);
+        MmaOp<T>::run(o[2 * n2], ph, r[0], r[1]);
+        MmaOp<T>::run(o[2 * n2 + 1], ph, r[2], r[3]);
+        MmaOp<T>::run(o[2 * n2], pl, r[0], r[1]);
+        MmaOp<T>::run(o[2 * n2 + 1], pl, r[2], r[3]);
+      }
+    }
+    lsum += __shfl_xor_sync(MUI_FULL_MASK, lsum, 1);
+    lsum += __shfl_xor_sync(MUI_FULL_MASK, lsum, 2);
+    if (real_head) {
+      if ((lane & 3) == 0) wsum[warp * GP + hrow] = lsum;
+      float* dst = red + ((size_t)warp * GP + hrow) * FA_D + cpair;
+#pragma unroll
+      for (int n = 0; n < 16; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][0], o[n][1]);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) trace_mark(a.trace, 3, true);
+  {
+    T* out = reinterpret_cast<T*>(a.out) + ((size_t)b * a.Hq + (size_t)kvh * G) * FA_D;
+    for (int idx = tid; idx < G * FA_D; idx += FA_THREADS) {
+      const int g = idx / FA_D, d = idx - g * FA_D;
+      float v = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < FA_WARPS; ++w) {
+        v += red[((size_t)w * GP + g) * FA_D + d];
+        l += wsum[w * GP + g];
+      }
+      out[idx] = Elt<T>::from_f32(l > 0.f ? v / l : 0.f);
+    }
+  }
+  if (tid == 0) trace_end(a.trace);
+}
+
+template <typename T, int GP>
+mui_status_t launch_ra(cudaStream_t stream, const FaArgs& a, int pdl) {
+  static bool configured = false;  // per instantiation
+  auto kern = rope_flash_decode_resident_kernel<T, GP>;
+  if (!configured) {
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ra_smem_bytes<GP>()));
+    configured = true;
+  }
+  MUI_CUDA_CHECK(mui_launch(kern, dim3(a.Hkv, a.B), dim3(FA_THREADS), ra_smem_bytes<GP>(), stream, pdl, a));
+  return MUI_OK;
+}
+
+template <typename T>
+mui_status_t launch_ra_g(cudaStream_t stream, const FaArgs& a, int pdl) {
+  if (a.G <= 1) return launch_ra<T, 1>(stream, a, pdl);
+  if (a.G <= 2) return launch_ra<T, 2>(stream, a, pdl);
+  if (a.G <= 4) return launch_ra<T, 4>(stream, a, pdl);
+  return launch_ra<T, 8>(stream, a, pdl);
+}
+
 template <typename T, int GP, int U>
 mui_status_t launch_fa(cudaStream_t stream, const FaArgs& a, int pdl) {
   cudaLaunchConfig_t cfg = {};
@@ -370,6 +617,10 @@ extern "C" mui_status_t mui_rope_flash_decode(void* stream, mui_dtype_t dtype, i
   a.G = Hq / Hkv;
   a.trace = mui_trace_next_record(3);
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
+  if (flags & MUI_FLAG_SHORT_CONTEXT) {
+    if (dtype == MUI_F16) return launch_ra_g<__half>((cudaStream_t)stream, a, pdl);
+    return launch_ra_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl);
+  }
   if (dtype == MUI_F16) return launch_fa_g<__half>((cudaStream_t)stream, a, pdl);
   return launch_fa_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl);
 }

@@ -22,6 +22,7 @@
 #define MUI_DEV_TIMEOUT_EMPTY 2u   // producer gave up waiting for a stage to be released
 #define MUI_DEV_TIMEOUT_PEER 3u    // all-reduce gave up waiting for a peer's flag
 #define MUI_DEV_TIMEOUT_DRAIN 4u   // gave up waiting for own copies in flight at exit
+#define MUI_DEV_BAD_LENGTH 5u      // a kernel variant with a bounded sequence length was given a longer one
 
 // One status word per translation unit (no relocatable device code is needed that way); each kernel
 // file instantiates MUI_STATUS_ACCESSOR(tag) once and mui_device_status() visits all of them.
@@ -81,6 +82,8 @@ __device__ __forceinline__ void trace_end(unsigned long long* rec) {
 // Prefetch hint of the calling host thread: up to 3 matrices the NEXT GEMV launch should start pulling into L2
 // after issuing its own copies; taking the hint clears it.
 void mui_take_prefetch_hint(const void** ptrs, int* rows, int* row_bytes, int* frac1024);
+void mui_set_gemv_reserve_sms(int n);
+int mui_take_gemv_reserve_sms();
 // optional extra stamps of a record (words 2 and 3): earliest moment a CTA got past its wait for the previous
 // kernel, and (complemented) latest moment a CTA had its activations staged
 __device__ __forceinline__ void trace_mark(unsigned long long* rec, int word, bool complement) {

@@ -533,7 +533,8 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   *applicable = true;
   const PipeLayout lay = pipe_layout(G::STAGE_BYTES, stages, x_rows, a.Kp, NB);
   const int units = (total_rows + 7) / 8;  // at least one row block per CTA
-  const int grid = std::max(1, std::min(units, dev->sm_count * ctas_per_sm));
+  const int sms = std::max(1, dev->sm_count - std::min(a.reserve_sms, dev->sm_count / 4));
+  const int grid = std::max(1, std::min(units, sms * ctas_per_sm));
   auto launch = [&](auto kern, int threads, bool* configured) -> mui_status_t {
     if (!*configured) {
       MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
@@ -628,6 +629,7 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
   GemvArgs a = a_in;
   if (a.trace == nullptr) a.trace = mui_trace_next_record(mode == 0 ? 1 : 2);
   mui_take_prefetch_hint(a.pf_ptr, a.pf_rows, a.pf_row_bytes, a.pf_frac);
+  a.reserve_sms = mui_take_gemv_reserve_sms();
   const int nb = a.B <= 1 ? 1 : (a.B <= 2 ? 2 : (a.B <= 4 ? 4 : 8));
   // Activations of all batch rows are staged in shared memory; when they cannot fit (large K with B > 1), run
   // the batch in two halves (the weights are then streamed twice).

@@ -45,6 +45,10 @@ struct mui_llama_stack {
   void* argmax_work;
   long long* out_tokens;
   int out_capacity;
+  int s_upper;           // upper bound of the attended length until the next reset (picks the attention variant)
+  int host_pos;          // tokens in the cache as far as the host has launched steps
+  bool capturing;        // launch_step runs under stream capture
+  bool graph_short;      // the captured step uses the short-context attention kernel
   cudaGraphExec_t graph_exec;
   unsigned graph_flags;
   mui_comm_t* comm;  // tensor-parallel communicator (null on a single GPU)
@@ -156,6 +160,14 @@ mui_status_t launch_mega(mui_llama_stack* s, cudaStream_t stream, unsigned flags
 
 // Hint for the GEMV about to be launched: the weight matrices that follow it in execution order, up to `window`
 // bytes in total (a gate/up pair shares its part of the window evenly, since the kernel consumes both in step).
+bool short_context_enabled() {
+  static const int v = [] {
+    const char* e = getenv("MUI_SHORT_CONTEXT");
+    return e ? atoi(e) : 1;
+  }();
+  return v != 0;
+}
+
 void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t window) {
   const void* ptrs[3] = {nullptr, nullptr, nullptr};
   int rows[3] = {0, 0, 0}, rbytes[3] = {0, 0, 0}, frac[3] = {0, 0, 0};
@@ -214,14 +226,22 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   const size_t e = 2;
   for (int l = 0; l < c.layers; ++l) {
     if (pf) hint_prefetch(s->order, 5 * (size_t)l + 1, s->prefetch_window);
+    const bool fused_attn = D == 128 && Hq / Hkv <= 8 && !(flags & MUI_FLAG_FORCE_GENERIC);
+    // short histories: one CTA per KV head that moves in beside the QKV projection (which leaves it the SMs) and
+    // has the K/V rows in shared memory by the time q arrives
+    const int attended = s->capturing ? s->s_upper : s->host_pos + 1;
+    const bool short_ctx = fused_attn && pdl && short_context_enabled() && attended <= 384 && Hkv * B <= 16;
+    if (s->capturing) s->graph_short = short_ctx;
+    if (short_ctx) mui_set_gemv_reserve_sms(Hkv * B);
     st = mui_linear_forward(stream, c.dtype, B, qkv_n, H, s->ln1[l], c.rms_eps, s->qkv[l], MUI_ACT_IDENTITY, nullptr,
                             nullptr, nullptr, s->h, s->qkv_out, flags);
     if (st != MUI_OK) return st;
-    if (D == 128 && Hq / Hkv <= 8 && !(flags & MUI_FLAG_FORCE_GENERIC)) {
-      // one launch: RoPE + cache write + attention (cluster kernel)
+    if (fused_attn) {
+      // one launch: RoPE + cache write + attention
       st = mui_rope_flash_decode(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->qkv_out, s->cos_t, s->sin_t,
                                  (const int64_t*)position_ids, (const int64_t*)cache_position, s->seq_len32,
-                                 c.attn_scale, s->k_cache[l], s->v_cache[l], s->attn, flags);
+                                 c.attn_scale, s->k_cache[l], s->v_cache[l], s->attn,
+                                 flags | (short_ctx ? MUI_FLAG_SHORT_CONTEXT : 0u));
       if (st != MUI_OK) return st;
     } else {
       const unsigned char* qp = (const unsigned char*)s->qkv_out;
@@ -325,6 +345,10 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
   s->argmax_work = base + lay.argmax_work;
   s->out_tokens = nullptr;
   s->out_capacity = 0;
+  s->s_upper = cfg->max_seq;
+  s->host_pos = 0;
+  s->capturing = false;
+  s->graph_short = false;
   s->graph_exec = nullptr;
   s->graph_flags = 0;
   s->comm = nullptr;
@@ -439,6 +463,9 @@ mui_status_t mui_llama_stack_reset(mui_llama_stack_t* s, void* stream, int posit
   MUI_CUDA_CHECK(cudaMemsetAsync(s->mega_bar, 0, 64, cs));
   s->out_tokens = reinterpret_cast<long long*>(out_tokens_dev);
   s->out_capacity = out_tokens_dev ? out_capacity : 0;
+  // the caller's token buffer bounds how far this run decodes; without one assume the whole cache
+  s->s_upper = out_tokens_dev ? std::min(s->cfg.max_seq, position + out_capacity + 1) : s->cfg.max_seq;
+  s->host_pos = position;
   if (s->graph_exec) {  // the captured argmax node holds the old output pointer
     cudaGraphExecDestroy(s->graph_exec);
     s->graph_exec = nullptr;
@@ -456,7 +483,10 @@ mui_status_t mui_llama_stack_set_tokens(mui_llama_stack_t* s, void* stream, cons
 
 mui_status_t mui_llama_stack_step(mui_llama_stack_t* s, void* stream, unsigned flags) {
   MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
-  return launch_step(s, (cudaStream_t)stream, flags);
+  s->capturing = false;
+  const mui_status_t st = launch_step(s, (cudaStream_t)stream, flags);
+  if (st == MUI_OK) s->host_pos += 1;
+  return st;
 }
 
 mui_status_t mui_llama_stack_capture(mui_llama_stack_t* s, void* stream, unsigned flags) {
@@ -468,7 +498,10 @@ mui_status_t mui_llama_stack_capture(mui_llama_stack_t* s, void* stream, unsigne
     s->graph_exec = nullptr;
   }
   MUI_CUDA_CHECK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
+  s->capturing = true;
+  s->graph_short = false;
   mui_status_t st = launch_step(s, cs, flags);
+  s->capturing = false;
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(cs, &graph);
   if (st != MUI_OK) {
@@ -492,6 +525,10 @@ mui_status_t mui_llama_stack_capture(mui_llama_stack_t* s, void* stream, unsigne
 
 mui_status_t mui_llama_stack_replay(mui_llama_stack_t* s, void* stream, int steps) {
   MUI_REQUIRE(s != nullptr && s->graph_exec != nullptr, MUI_ERR_INVALID_ARG, "no captured graph (call capture first)");
+  MUI_REQUIRE(!s->graph_short || s->host_pos + steps <= 384, MUI_ERR_UNSUPPORTED,
+              "the captured step uses the short-context attention kernel (384 tokens); %d tokens are cached and %d "
+              "more steps were asked for: reset with a larger token buffer and capture again", s->host_pos, steps);
+  s->host_pos += steps;
   for (int i = 0; i < steps; ++i) MUI_CUDA_CHECK(cudaGraphLaunch(s->graph_exec, (cudaStream_t)stream));
   return MUI_OK;
 }

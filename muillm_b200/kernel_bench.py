@@ -96,7 +96,7 @@ def case_down_w8(name, H, I, B, dtype, dev, g, flags):
     return name, _time_graph(fns, 4 * L), nbytes
 
 
-def case_attention(name, S, dtype, dev, g, flags):
+def case_attention(name, S, dtype, dev, g, flags, short=False):
     B, Hq, Hkv, D, max_T = 1, 32, 8, 128, 4096
     L = 12
     qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device=dev, generator=g).to(dtype)
@@ -107,6 +107,8 @@ def case_attention(name, S, dtype, dev, g, flags):
     pos = torch.full((B,), S - 1, dtype=torch.int64, device=dev)
     cpos = torch.tensor([S - 1], dtype=torch.int64, device=dev)
     sl = torch.tensor([S], dtype=torch.int32, device=dev)
+    if short:
+        flags = flags | capi.MUI_FLAG_SHORT_CONTEXT
     fns = [(lambda kc=kc, vc=vc: ops.rope_flash_decode(qkv, cos, sin, pos, cpos, sl, kc, vc, Hq, flags=flags))
            for kc, vc in caches]
     nbytes = 2 * B * Hkv * S * D * 2 + (Hq + 2 * Hkv) * D * 2 + Hq * D * 2
@@ -158,6 +160,8 @@ def run(dtype=torch.float16):
     add(case_linear("QKV 6144x4096, bf16", 6144, 4096, 1, torch.bfloat16, True, False, dev, g, flags))
     for S in (256, 2048, 4096):
         add(case_attention(f"rope+cache+attention 32q/8kv d128, S={S}", S, dtype, dev, g, flags))
+    for S in (64, 256, 384):
+        add(case_attention(f"rope+cache+attention, one CTA per KV head, S={S}", S, dtype, dev, g, flags, short=True))
     add(case_moe("MoE MLP shared+top-1 of 16, H=5120 I=2048, bf16", 5120, 2048, 1, 16, torch.bfloat16, dev, g, flags))
     assert capi.device_status() == 0
     return rows

@@ -151,10 +151,14 @@ def test_flash_decode_softmax_shift_invariance():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("B,Hq,Hkv,S", [(1, 32, 8, 1), (1, 32, 8, 17), (1, 32, 8, 280), (1, 32, 8, 513),
+@pytest.mark.parametrize("B,Hq,Hkv,S", [(1, 32, 8, 1), (1, 32, 8, 2), (1, 32, 8, 17), (1, 32, 8, 280), (1, 32, 8, 385), (1, 32, 8, 386),
+                                        (1, 32, 8, 513),
                                         (2, 8, 1, 2000), (3, 4, 4, 65), (1, 8, 8, 4096)])
-def test_fused_rope_cache_write_attention(dtype, B, Hq, Hkv, S):
-    """One launch = RoPE(q, k_new) + cache write + attention over S tokens (the new one last)."""
+@pytest.mark.parametrize("variant", [0, capi.MUI_FLAG_SHORT_CONTEXT, capi.MUI_FLAG_SHORT_CONTEXT | capi.MUI_FLAG_PDL])
+def test_fused_rope_cache_write_attention(dtype, B, Hq, Hkv, S, variant):
+    """One launch = RoPE(q, k_new) + cache write + attention over S tokens (the new one last): the cluster kernel, and
+    the one-CTA-per-head tensor-core kernel that stages the history in shared memory (at most 384 tokens; a longer
+    sequence must be refused through the device status word, not computed wrongly)."""
     D, max_T = 128, 4096
     g = _gen(S + B + Hq)
     qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
@@ -174,7 +178,13 @@ def test_fused_rope_cache_write_attention(dtype, B, Hq, Hkv, S):
     want = oracle.decode_attention(q_rot, ks, vs)
     kc_g, vc_g = kc.cuda(), vc.cuda()
     got = ops.rope_flash_decode(qkv.cuda(), cos.cuda(), sin.cuda(), position_ids.view(-1).cuda(), cache_position.cuda(),
-                                torch.tensor([S], dtype=torch.int32, device="cuda"), kc_g, vc_g, Hq)
+                                torch.tensor([S], dtype=torch.int32, device="cuda"), kc_g, vc_g, Hq, flags=variant)
+    if (variant & capi.MUI_FLAG_SHORT_CONTEXT) and S > 384:
+        torch.cuda.synchronize()
+        status = capi.device_status(clear=True)
+        assert status >> 24 == 5, f"expected the bad-length status, got {status:#x}"
+        assert torch.equal(kc_g.cpu(), kc), "a refused launch must not touch the cache"
+        return
     _close(got, want)
     # the cache got exactly the rows the stand-alone RoPE kernel writes, and nothing else moved
     _close(kc_g[:, :, pos], kc_ref[:, :, pos])
