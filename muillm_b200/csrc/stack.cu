@@ -366,7 +366,7 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
     }
     s->order.push_back(WeightRef{w->lm_head, cfg->vocab, cfg->hidden * 2});
     const char* e = getenv("MUI_PREFETCH_MB");
-    const long mb = (e && *e) ? atol(e) : 48;
+    const long mb = (e && *e) ? atol(e) : 24;  // measured on the 8B decode step: 8-48 MB within 1 %, none -2 %, 96 MB -3 %
     s->prefetch_window = mb > 0 ? (size_t)mb << 20 : 0;
   }
   // whole-step kernel: per-layer pointer table on the device, scratch, eligibility

@@ -4,6 +4,7 @@
   python -m muillm_b200.profile_cases linear     # QKV-shaped fused-norm GEMV (6144 x 4096), 8 distinct matrices
   python -m muillm_b200.profile_cases attention  # fused RoPE + cache write + attention, 32 q / 8 kv heads, S = 2048
   python -m muillm_b200.profile_cases w8         # int8 (per-row scale) gate/up GEMV, same MLP shape
+  python -m muillm_b200.profile_cases attention_short  # one-CTA-per-KV-head tensor-core attention, S = 256
 
 Each case keeps well under 2 GB on the device, uses inputs larger than L2 in total so that weights come from
 HBM, launches the kernel a handful of times and synchronises.
@@ -54,8 +55,8 @@ def _linear(dtype=torch.float16):
     torch.cuda.synchronize()
 
 
-def _attention(dtype=torch.float16):
-    B, Hq, Hkv, D, S, max_T = 1, 32, 8, 128, 2048, 4096
+def _attention(dtype=torch.float16, S=2048, flags=0):
+    B, Hq, Hkv, D, max_T = 1, 32, 8, 128, 4096
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(0)
     qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device=dev, generator=g).to(dtype)
@@ -67,14 +68,15 @@ def _attention(dtype=torch.float16):
     cpos = torch.tensor([S - 1], dtype=torch.int64, device=dev)
     sl = torch.tensor([S], dtype=torch.int32, device=dev)
     for kc, vc in caches:
-        ops.rope_flash_decode(qkv, cos, sin, pos, cpos, sl, kc, vc, Hq)
+        ops.rope_flash_decode(qkv, cos, sin, pos, cpos, sl, kc, vc, Hq, flags=flags)
     torch.cuda.synchronize()
 
 
 def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "gateup"
     torch.cuda.set_device(0)
-    {"gateup": _gateup, "linear": _linear, "attention": _attention, "w8": lambda: _gateup(w8=True)}[case]()
+    {"gateup": _gateup, "linear": _linear, "attention": _attention, "w8": lambda: _gateup(w8=True),
+     "attention_short": lambda: _attention(S=256, flags=capi.MUI_FLAG_SHORT_CONTEXT)}[case]()
     assert capi.device_status() == 0
     print("ok", case)
 
