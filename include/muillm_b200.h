@@ -466,6 +466,18 @@ MUI_API mui_status_t mui_llama_stack_step(mui_llama_stack_t* stack, void* stream
 /* Captures one step on `stream` (must not be the default stream) into a graph; replay launches it `steps` times. */
 MUI_API mui_status_t mui_llama_stack_capture(mui_llama_stack_t* stack, void* stream, unsigned flags);
 MUI_API mui_status_t mui_llama_stack_replay(mui_llama_stack_t* stack, void* stream, int steps);
+/* The decoder layers only, for callers that keep the final norm, lm_head and sampling outside — what the reference's
+ * MuiLLMParallelDecoderStack::forward does for one new token (csrc/modules/parallel_decoder_stack.cpp:22-45): from
+ * token ids [batch] (embedding lookup) or from hidden states h_in [batch, hidden], with RoPE positions
+ * position_ids [batch] and the cache row cache_position [1] (int64, device); the new token attends
+ * cache_position + 1 rows, which the caller also passes as the host integer seen_tokens (it picks the attention
+ * variant). h_out [batch, hidden] receives the last layer's output. The device-side decode state of the stack is
+ * overwritten; a captured graph of mui_llama_stack_step is unaffected. */
+MUI_API mui_status_t mui_llama_stack_forward_hidden(mui_llama_stack_t* stack, void* stream,
+                                                    const int64_t* token_ids_dev, const void* h_in,
+                                                    const int64_t* position_ids_dev,
+                                                    const int64_t* cache_position_dev, int seen_tokens, void* h_out,
+                                                    unsigned flags);
 /* Device pointers of the last step's logits [batch, vocab] (dtype) and of the int64 state words
  * {step, tokens in cache, cache position, position_ids[batch], next tokens[batch]}. */
 MUI_API mui_status_t mui_llama_stack_logits(mui_llama_stack_t* stack, void** logits_dev, int64_t** state_dev);

@@ -222,6 +222,8 @@ PROTOTYPES = {
     "mui_llama_stack_step": (c_int, [c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_capture": (c_int, [c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_replay": (c_int, [c_void_p, c_void_p, c_int]),
+    "mui_llama_stack_forward_hidden": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_uint]),
     "mui_llama_stack_logits": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p)]),
 }
 

@@ -49,6 +49,8 @@ struct mui_llama_stack {
   int host_pos;          // tokens in the cache as far as the host has launched steps
   bool capturing;        // launch_step runs under stream capture
   bool graph_short;      // the captured step uses the short-context attention kernel
+  bool layers_only;      // launch_step stops after the last decoder layer (mui_llama_stack_forward_hidden)
+  bool skip_embedding;   // launch_step starts from the hidden states already in `h`
   cudaGraphExec_t graph_exec;
   unsigned graph_flags;
   mui_comm_t* comm;  // tensor-parallel communicator (null on a single GPU)
@@ -160,6 +162,23 @@ mui_status_t launch_mega(mui_llama_stack* s, cudaStream_t stream, unsigned flags
 
 // Hint for the GEMV about to be launched: the weight matrices that follow it in execution order, up to `window`
 // bytes in total (a gate/up pair shares its part of the window evenly, since the kernel consumes both in step).
+// Decode state from caller-owned device tensors (mui_llama_stack_forward_hidden): tokens in cache = cache position,
+// attended length = cache position + 1; the step counter is left alone.
+__global__ void set_decode_state_kernel(long long* state, int32_t* seq_len32, const long long* tokens,
+                                        const long long* position_ids, const long long* cache_position, int B) {
+  const int t = threadIdx.x;
+  const long long cp = cache_position[0];
+  if (t == 0) {
+    state[1] = cp;
+    state[2] = cp;
+    *seq_len32 = static_cast<int32_t>(cp + 1);
+  }
+  if (t < B) {
+    state[3 + t] = position_ids[t];
+    if (tokens) state[3 + B + t] = tokens[t];
+  }
+}
+
 bool short_context_enabled() {
   static const int v = [] {
     const char* e = getenv("MUI_SHORT_CONTEXT");
@@ -218,8 +237,10 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   const bool tp = s->comm != nullptr;
   const bool pf = s->prefetch_window > 0;
   const int embed_rows = c.embed_vocab > 0 ? c.embed_vocab : c.vocab;
-  st = mui_launch_embedding(stream, s->embed, (const int64_t*)tokens, s->h, B, H, embed_rows, pdl);
-  if (st != MUI_OK) return st;
+  if (!s->skip_embedding) {
+    st = mui_launch_embedding(stream, s->embed, (const int64_t*)tokens, s->h, B, H, embed_rows, pdl);
+    if (st != MUI_OK) return st;
+  }
   // q,k,v are slices of the packed qkv row: [B, 1, (Hq+2Hkv)*D] viewed as [B, H*, 1, D]
   const mui_strides3_t qs = {(int64_t)qkv_n, (int64_t)D, (int64_t)qkv_n};
   const mui_strides3_t kvs = {(int64_t)Hkv * c.max_seq * D, (int64_t)c.max_seq * D, (int64_t)D};
@@ -274,6 +295,7 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
                               nullptr, nullptr, s->h, s->t, s->h, flags);
     if (st != MUI_OK) return st;
   }
+  if (s->layers_only) return MUI_OK;
   st = mui_linear_forward(stream, c.dtype, B, c.vocab, H, s->final_norm, c.rms_eps, s->lm_head, MUI_ACT_IDENTITY,
                           nullptr, nullptr, nullptr, s->h, s->logits, flags);
   if (st != MUI_OK) return st;
@@ -349,6 +371,8 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
   s->host_pos = 0;
   s->capturing = false;
   s->graph_short = false;
+  s->layers_only = false;
+  s->skip_embedding = false;
   s->graph_exec = nullptr;
   s->graph_flags = 0;
   s->comm = nullptr;
@@ -530,6 +554,38 @@ mui_status_t mui_llama_stack_replay(mui_llama_stack_t* s, void* stream, int step
               "more steps were asked for: reset with a larger token buffer and capture again", s->host_pos, steps);
   s->host_pos += steps;
   for (int i = 0; i < steps; ++i) MUI_CUDA_CHECK(cudaGraphLaunch(s->graph_exec, (cudaStream_t)stream));
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_forward_hidden(mui_llama_stack_t* s, void* stream, const int64_t* token_ids_dev,
+                                            const void* h_in, const int64_t* position_ids_dev,
+                                            const int64_t* cache_position_dev, int seen_tokens, void* h_out,
+                                            unsigned flags) {
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  MUI_REQUIRE((token_ids_dev != nullptr) != (h_in != nullptr), MUI_ERR_INVALID_ARG,
+              "give either token ids or hidden states");
+  MUI_REQUIRE(position_ids_dev && cache_position_dev && h_out, MUI_ERR_INVALID_ARG, "null pointer");
+  MUI_REQUIRE(seen_tokens >= 1 && seen_tokens <= s->cfg.max_seq, MUI_ERR_INVALID_ARG,
+              "seen_tokens %d outside 1..%d", seen_tokens, s->cfg.max_seq);
+  MUI_REQUIRE(!(flags & MUI_FLAG_MEGAKERNEL), MUI_ERR_UNSUPPORTED, "the whole-step kernel includes the lm_head");
+  cudaStream_t cs = (cudaStream_t)stream;
+  const int B = s->cfg.batch;
+  const size_t hbytes = (size_t)B * s->cfg.hidden * 2;
+  set_decode_state_kernel<<<1, 32, 0, cs>>>(s->state, s->seq_len32, reinterpret_cast<const long long*>(token_ids_dev),
+                                            reinterpret_cast<const long long*>(position_ids_dev),
+                                            reinterpret_cast<const long long*>(cache_position_dev), B);
+  MUI_CUDA_CHECK(cudaGetLastError());
+  if (h_in) MUI_CUDA_CHECK(cudaMemcpyAsync(s->h, h_in, hbytes, cudaMemcpyDeviceToDevice, cs));
+  s->capturing = false;
+  s->host_pos = seen_tokens - 1;
+  s->layers_only = true;
+  s->skip_embedding = h_in != nullptr;
+  const mui_status_t st = launch_step(s, cs, flags);
+  s->layers_only = false;
+  s->skip_embedding = false;
+  if (st != MUI_OK) return st;
+  s->host_pos = seen_tokens;
+  MUI_CUDA_CHECK(cudaMemcpyAsync(h_out, s->h, hbytes, cudaMemcpyDeviceToDevice, cs));
   return MUI_OK;
 }
 

@@ -764,15 +764,124 @@ def muillm_parallel_llama4_decoder_module_forward(module, cache, h, mask, chunke
     return module.forward(cache, h, mask, chunked_mask, position_embeds, cache_positions)
 
 
+class _FusedLayers:
+    """The decoder layers of a stack as ONE call into the C decode stack (mui_llama_stack_forward_hidden) instead of
+    ~10 Python-dispatched launches per layer. Built from the module handles' own tensors (nothing is copied) for a
+    given static cache; valid for one new token per sequence without an attention mask."""
+
+    def __init__(self, stack, cache, batch):
+        import ctypes
+        import math
+        from ctypes import c_void_p
+
+        from . import capi
+
+        lib = capi.lib()
+        decs = stack.decoders
+        first = decs[0]
+        att, lin = first.attention, first.multilinear.linear
+        w_qkv = lin.weights
+        dt, dev = w_qkv.dtype, w_qkv.device
+        Hq, Hkv, D = att.num_tp_heads, att.num_tp_key_value_heads, att.head_dim
+        hidden = w_qkv.shape[1]
+        inter = first.mlp.gate_weights.shape[0]
+        max_seq = cache.key_cache[0].shape[2]
+        embed = stack.embed_tokens.weights
+        cos, sin = stack.rotary_embedding.cos_cached, stack.rotary_embedding.sin_cached
+        self.keep = [cos, sin, embed]
+        cfg = capi.LlamaConfig(capi.MUI_F16 if dt == torch.float16 else capi.MUI_BF16, len(decs), hidden, inter, Hq,
+                               Hkv, D, embed.shape[0], max_seq, batch, float(lin.epsilon), 1.0 / math.sqrt(D), 0, 0)
+        nbytes = lib.mui_llama_stack_scratch_bytes(ctypes.byref(cfg))
+        if nbytes == 0:
+            raise RuntimeError("muillm_b200: " + lib.mui_last_error().decode())
+        self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+
+        def arr(tensors):
+            self.keep.extend(tensors)
+            return (c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+        self.arrays = [arr([d.multilinear.linear.weights for d in decs]), arr([d.attention.o_proj.weights for d in decs]),
+                       arr([d.mlp.gate_weights for d in decs]), arr([d.mlp.up_weights for d in decs]),
+                       arr([d.mlp.down_weights for d in decs]), arr([d.multilinear.linear.norm_weights for d in decs]),
+                       arr([d.mlp.norm_weights for d in decs]), arr(list(cache.key_cache)),
+                       arr(list(cache.value_cache))]
+        # final norm and lm_head stay with the caller: the two slots only have to be non-null
+        w = capi.LlamaWeights(embed.data_ptr(), decs[0].mlp.norm_weights.data_ptr(), embed.data_ptr(), cos.data_ptr(),
+                              sin.data_ptr(), *self.arrays)
+        h = c_void_p()
+        capi.check(lib.mui_llama_stack_create(ctypes.byref(cfg), ctypes.byref(w), self.scratch.data_ptr(),
+                                              self.scratch.numel(), ctypes.byref(h)))
+        self.lib, self.h, self.hidden, self.batch, self.dtype = lib, h, hidden, batch, dt
+        self.comm = stack.comm.comm if stack.comm is not None else None
+        if self.comm is not None:
+            capi.check(lib.mui_llama_stack_set_comm(h, self.comm.handle))
+        self.cache_ptrs = [t.data_ptr() for t in cache.key_cache]
+        from .capi import MUI_FLAG_PDL
+        self.flags = MUI_FLAG_PDL
+
+    def __del__(self):
+        h = getattr(self, "h", None)
+        if h:
+            self.lib.mui_llama_stack_destroy(h)
+
+    def forward(self, input_ids, input_embeds, position_ids, cache_positions, seen_tokens):
+        from . import capi
+
+        out = torch.empty((self.batch, 1, self.hidden), dtype=self.dtype, device=self.scratch.device)
+        tok = None if input_embeds is not None else input_ids.reshape(-1).contiguous()
+        emb = input_embeds.contiguous() if input_embeds is not None else None
+        pos = position_ids.reshape(-1).contiguous()
+        capi.check(self.lib.mui_llama_stack_forward_hidden(
+            self.h, torch.cuda.current_stream().cuda_stream, None if tok is None else tok.data_ptr(),
+            None if emb is None else emb.data_ptr(), pos.data_ptr(), cache_positions.data_ptr(), int(seen_tokens),
+            out.data_ptr(), self.flags))
+        return out
+
+
 class muillm_parallel_decoder_stack_ptr(_Handle):
     """csrc/modules/parallel_decoder_stack.cpp:22-45: embedding (unless embeddings are given), the rotary tables
-    once, then the decoders in order."""
+    once, then the decoders in order. One new token per sequence on a static cache without a mask — the decode step —
+    runs as a single call into the C decode stack (set MUILLM_B200_FUSED_STACK=0 to keep the per-module path)."""
 
     def __init__(self, comm, embed_tokens, rotary_embedding, decoders):
         self.comm, self.embed_tokens, self.rotary_embedding, self.decoders = (comm, embed_tokens, rotary_embedding,
                                                                               list(decoders))
+        self._fused = None
+
+    def _fused_for(self, cache, batch, q_len, m):
+        if os.environ.get("MUILLM_B200_FUSED_STACK", "1") == "0":
+            return None
+        if q_len != 1 or m is not None or batch > 8 or cache is None or self.embed_tokens is None or \
+                self.rotary_embedding is None or cache.kind != muillm_kvcache_module_ptr.STATIC:
+            return None
+        f = self._fused
+        if f is not None and f.batch == batch and f.cache_ptrs == [t.data_ptr() for t in cache.key_cache]:
+            return f
+        for d in self.decoders:
+            lin = getattr(getattr(d, "multilinear", None), "linear", None)
+            ok = (isinstance(d, muillm_parallel_decoder_module_ptr) and lin is not None and
+                  lin.norm_weights is not None and lin.mul_bias is None and lin.add_bias is None and
+                  d.multilinear.sharding_dim == 0 and len(d.multilinear.slices) == 3 and
+                  d.attention.o_proj.sharding_dim == 1 and d.attention.o_proj.add_bias is None and
+                  d.attention.o_proj.mul_bias is None and d.mlp.norm_weights is not None and
+                  isinstance(d.mlp, muillm_parallel_igateupdownmlp_module_ptr) and
+                  lin.weights.dtype in (torch.float16, torch.bfloat16) and lin.weights.is_cuda and
+                  d.attention.rotary is not None)
+            if not ok:
+                return None
+        if self.rotary_embedding.cos_cached.dim() != 2 or self.rotary_embedding.cos_cached.dtype != \
+                self.decoders[0].multilinear.linear.weights.dtype:
+            return None
+        self._fused = _FusedLayers(self, cache, batch)
+        return self._fused
 
     def forward(self, cache, input_ids, input_embeds, m, position_ids, cache_positions):
+        batch = (input_embeds if input_embeds is not None else input_ids).shape[0]
+        q_len = (input_embeds if input_embeds is not None else input_ids).shape[1]
+        fused = self._fused_for(cache, batch, q_len, m)
+        if fused is not None:
+            cache._seen_tokens += 1  # the per-module path moves the count in layer 0's rotary module
+            return fused.forward(input_ids, input_embeds, position_ids, cache_positions, cache._seen_tokens)
         h = input_embeds if input_embeds is not None else self.embed_tokens.forward(input_ids)
         cos_sin = None
         if self.rotary_embedding is not None:

@@ -39,10 +39,17 @@ def _build_llama_stack(w, cfg, comm, engine, max_T):
     return stack, keep + decoders + [embed, stack_rotary]
 
 
+CFG128 = dict(layers=2, hidden=512, intermediate=768, heads=8, kv_heads=2, head_dim=128, vocab=320, eps=1e-5,
+              rope_theta=500000.0)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("cache_kind", ["static", "dynamic"])
-def test_decoder_stack_through_module_handles(dtype, cache_kind):
-    cfg, max_T, B = CFG, 48, 2
+@pytest.mark.parametrize("cache_kind,fused,cfg", [("static", "1", CFG), ("static", "0", CFG), ("dynamic", "1", CFG),
+                                                  ("static", "1", CFG128), ("static", "0", CFG128)])
+def test_decoder_stack_through_module_handles(dtype, cache_kind, fused, cfg, monkeypatch):
+    """fused = 1: a decode step on a static cache is one call into the C decode stack; 0: one call per module."""
+    monkeypatch.setenv("MUILLM_B200_FUSED_STACK", fused)
+    max_T, B = 48, 2
     w = oracle.make_llama_weights(cfg, dtype, seed=3, std=0.06)
     engine = ext.muillm_engine_init()
     comm = ext.muillm_comm_init(engine, 1, 1, 0, 0)
@@ -71,6 +78,7 @@ def test_decoder_stack_through_module_handles(dtype, cache_kind):
         tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.float16 else dict(rtol=5e-2, atol=1e-1)
         torch.testing.assert_close(logits.float().cpu().reshape(B, -1), want, **tol)
     assert ext.muillm_kvcache_module_get_set_seen_tokens(cache, 0) == tokens.shape[1]
+    assert (stack._fused is not None) == (fused == "1" and cache_kind == "static")
     if cache_kind == "static":
         k_back, v_back = ext.muillm_static_kvcache_module_sync_back(cache)
         torch.testing.assert_close(k_back[0][:, :, :20].float().cpu(), orc.k_cache[0][:, :, :20].float(), rtol=1e-2,
