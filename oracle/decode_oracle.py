@@ -298,9 +298,14 @@ def all_reduce_fixed_order(partials, out_dtype):
 # Structure follows muillm/modules/decoder/decoder.py:95-165 and muillm/modules/models/llama/model.py:213-435.
 # ---------------------------------------------------------------------------------------------------
 class LlamaOracle:
-    def __init__(self, weights: dict, cfg: dict, max_T: int, batch: int = 1):
+    def __init__(self, weights: dict, cfg: dict, max_T: int, batch: int = 1, all_reduce=None):
+        """all_reduce: None for un-sharded weights; for a tensor-parallel shard (muillm_b200.decoder_stack
+        .shard_llama_weights) a callable that sums an fp32 tensor of partial results over the ranks in rank order —
+        it is applied to the o_proj and down partials before the residual is added and the sum is rounded, the
+        order of operations of the fused GEMV + all-reduce."""
         self.w = weights
         self.cfg = cfg
+        self.all_reduce = all_reduce
         dt = weights["embed"].dtype
         self.dtype = dt
         L, Hkv, D = cfg["layers"], cfg["kv_heads"], cfg["head_dim"]
@@ -328,9 +333,16 @@ class LlamaOracle:
                 q, ks, vs = rope_write_static_cache(q, k, v, self.cos, self.sin, position_ids, self.k_cache[l],
                                                     self.v_cache[l], cache_position, pos + 1)
                 attn = decode_attention(q, ks, vs).reshape(B, Hq * D)
-                h = linear(attn, w["o"][l], residual=h)
-                h = mlp(h, w["gate"][l], w["up"][l], w["down"][l], norm_weights=w["ln2"][l], eps=cfg["eps"],
-                        residual=h)
+                if self.all_reduce is None:
+                    h = linear(attn, w["o"][l], residual=h)
+                    h = mlp(h, w["gate"][l], w["up"][l], w["down"][l], norm_weights=w["ln2"][l], eps=cfg["eps"],
+                            residual=h)
+                else:
+                    part = linear(attn, w["o"][l], out_dtype=torch.float32)
+                    h = (self.all_reduce(part) + h.float()).to(self.dtype)
+                    t = gateup_silu(h, w["gate"][l], w["up"][l], norm_weights=w["ln2"][l], eps=cfg["eps"])
+                    part = linear(t, w["down"][l], out_dtype=torch.float32)
+                    h = (self.all_reduce(part) + h.float()).to(self.dtype)
             self.seen += 1
             logits = linear(h, w["lm_head"], norm_weights=w["norm"], eps=cfg["eps"], out_dtype=torch.float32)
         return logits

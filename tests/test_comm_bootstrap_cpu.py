@@ -100,3 +100,59 @@ def test_sharded_linear_fixed_order_reduce_gloo_world2():
     ys = {r: y for r, y, _ in res}
     assert torch.equal(ys[0], ys[1])  # bit-identical on all ranks
     torch.testing.assert_close(ys[0].float(), res[0][2].float(), rtol=1e-2, atol=1e-3)
+
+
+def _gloo_decoder_worker(rank, world, port, q):
+    import torch.distributed as dist
+
+    from muillm_b200.decoder_stack import shard_llama_weights
+    from oracle import decode_oracle as oracle
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = dict(layers=2, hidden=64, intermediate=96, heads=4, kv_heads=2, head_dim=16, vocab=40, eps=1e-5,
+               rope_theta=10000.0)
+    w = oracle.make_llama_weights(cfg, torch.float16, seed=2, std=0.1)
+    wl, cl = shard_llama_weights(w, cfg, rank, world)
+
+    def all_reduce(part):
+        parts = [torch.zeros_like(part) for _ in range(world)]
+        dist.all_gather(parts, part.contiguous())
+        total = parts[0].clone()
+        for p in parts[1:]:
+            total += p  # rank order, fp32
+        return total
+
+    sharded = oracle.LlamaOracle(wl, cl, max_T=16, all_reduce=all_reduce)
+    toks = torch.randint(0, cfg["vocab"], (1, 6), generator=torch.Generator().manual_seed(3))
+    local_logits = sharded.forward(toks)  # this rank's vocabulary shard
+    shards = [torch.zeros_like(local_logits) for _ in range(world)]
+    dist.all_gather(shards, local_logits)
+    q.put((rank, torch.cat(shards, dim=-1), cl))
+    dist.destroy_process_group()
+
+
+def test_sharded_decoder_matches_unsharded_oracle_gloo_world2():
+    """shard_llama_weights + the rank-ordered fp32 sum reproduce the un-sharded decoder: the host-side sharding of
+    the tensor-parallel decode stack, checked on CPU with two gloo ranks."""
+    from oracle import decode_oracle as oracle
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_gloo_decoder_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=30)
+    cfg = dict(layers=2, hidden=64, intermediate=96, heads=4, kv_heads=2, head_dim=16, vocab=40, eps=1e-5,
+               rope_theta=10000.0)
+    w = oracle.make_llama_weights(cfg, torch.float16, seed=2, std=0.1)
+    toks = torch.randint(0, cfg["vocab"], (1, 6), generator=torch.Generator().manual_seed(3))
+    want = oracle.LlamaOracle(w, cfg, max_T=16).forward(toks)
+    by_rank = {r: (lg, cl) for r, lg, cl in res}
+    assert torch.equal(by_rank[0][0], by_rank[1][0])
+    assert by_rank[1][1]["vocab_offset"] == 20 and by_rank[1][1]["heads"] == 2 and by_rank[1][1]["kv_heads"] == 1
+    torch.testing.assert_close(by_rank[0][0], want, rtol=2e-2, atol=2e-2)
