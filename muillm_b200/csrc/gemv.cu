@@ -375,6 +375,33 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
     pdl_wait_prior_grid();
     if (tid == 0) trace_mark(a.trace, 2, false);
     const unsigned long long comm_seq = (MODE == 0 && a.use_comm) ? comm_begin(a.comm) : 0ull;
+    // Epilogue operands (residual, per-row 8-bit scales) of every row block this thread will finish, loaded now so
+    // that their round trip overlaps the activation staging instead of stalling a row block's epilogue.
+    constexpr int EPI_MAX = 16;
+    const bool epi_pre = nblk <= EPI_MAX;
+    float epi_a[EPI_MAX], epi_b[EPI_MAX];  // MODE 0: residual, scale; MODE 1: gate scale, up scale
+#pragma unroll
+    for (int i = 0; i < EPI_MAX; ++i) {
+      epi_a[i] = (MODE == 0) ? 0.f : 1.f;
+      epi_b[i] = 1.f;
+    }
+    if (epi_pre && tid < ROWS_PER_STAGE * NB) {
+      const int r = tid / NB, b = tid - r * NB;
+      const bool sym = (WB == 8) && a.w8_fmt == MUI_W8_SYM_ROW && a.moe_mode == GEMV_MOE_NONE;
+#pragma unroll
+      for (int i = 0; i < EPI_MAX; ++i) {
+        const int row = r_begin + i * ROWS_PER_STAGE + r;
+        if (i < nblk && row < r_end && b < a.B) {
+          if (MODE == 0) {
+            if (a.residual) epi_a[i] = ld_act_f32<T>(reinterpret_cast<const T*>(a.residual) + (size_t)b * a.N + row);
+            if (sym) epi_b[i] = Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[row]);
+          } else if (sym) {
+            epi_a[i] = Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[row]);
+            epi_b[i] = Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales2)[row]);
+          }
+        }
+      }
+    }
     if (a.moe_mode == GEMV_MOE_SEGMENTS)
       gemv_stage_x_plain<T>(a, a.slots, x_s, x_pitch, tid);
     else
@@ -479,7 +506,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
               float v = 0.f;
 #pragma unroll
               for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) v += rbuf[(w * PIPE_ROWS + r) * NB + b];
-              gemv_store_linear<T>(a, b, row, v, comm_seq);
+              gemv_store_linear<T>(a, b, row, v, comm_seq, epi_pre, epi_b[0], epi_a[0]);
             } else {
               float g = 0.f, u = 0.f;
 #pragma unroll
@@ -489,9 +516,16 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
               }
               float score = 1.f;
               if (a.moe_mode == GEMV_MOE_ROWS) score = gemv_slot_score<T>(a, row / a.N);
-              gemv_store_gateup<T>(a, b, row, total_rows, g, u, score);
+              gemv_store_gateup<T>(a, b, row, total_rows, g, u, score,
+                                   epi_pre && a.moe_mode == GEMV_MOE_NONE, epi_a[0], epi_b[0]);
             }
           }
+        }
+        // next row block's operands move to the front (static register indices)
+#pragma unroll
+        for (int i = 0; i + 1 < EPI_MAX; ++i) {
+          epi_a[i] = epi_a[i + 1];
+          epi_b[i] = epi_b[i + 1];
         }
         ++blk;
       }

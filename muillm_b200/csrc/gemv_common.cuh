@@ -339,15 +339,18 @@ template <> struct W8Cvt<__nv_bfloat16> {
 // epilogues (one output element). Order follows csrc/linear/linear_fp16_kernels.cu:337-353:
 // activation, * mul_bias, + add_bias, + residual; rounded once.
 // ---------------------------------------------------------------------------------------------
+// `pre`: the per-row scale and the residual value were loaded ahead of time (pre_scale, pre_res) instead of here,
+// where a global load would stall the thread — and with it its warp's share of the next tiles — for a round trip.
 template <typename T>
 __device__ __forceinline__ void gemv_store_linear(const GemvArgs& a, int b, int n, float v,
-                                                  unsigned long long comm_seq = 0) {
-  if (a.w8_fmt == MUI_W8_SYM_ROW) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[n]);
+                                                  unsigned long long comm_seq = 0, bool pre = false,
+                                                  float pre_scale = 1.f, float pre_res = 0.f) {
+  if (a.w8_fmt == MUI_W8_SYM_ROW) v *= pre ? pre_scale : Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[n]);
   if (a.activ == MUI_ACT_SILU) v = silu_f32(v);
   if (a.mul_bias) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.mul_bias)[n]);
   if (a.add_bias) v += Elt<T>::to_f32(reinterpret_cast<const T*>(a.add_bias)[n]);
   const size_t o = (size_t)b * a.N + n;
-  if (a.residual) v += ld_act_f32<T>(reinterpret_cast<const T*>(a.residual) + o);
+  if (a.residual) v += pre ? pre_res : ld_act_f32<T>(reinterpret_cast<const T*>(a.residual) + o);
   if (a.use_comm) {
     comm_push(a.comm, comm_seq, o, v);
     return;
@@ -380,10 +383,11 @@ __device__ __forceinline__ void gemv_comm_tail(const GemvArgs& a, unsigned long 
 // applied before the SiLU as csrc/moeffn/gateupmoe_fp16_kernels.cu:355-360 does.
 template <typename T>
 __device__ __forceinline__ void gemv_store_gateup(const GemvArgs& a, int b, int out_row, int out_rows_total, float g,
-                                                  float u, float score) {
+                                                  float u, float score, bool pre = false, float pre_scale_g = 1.f,
+                                                  float pre_scale_u = 1.f) {
   if (a.w8_fmt == MUI_W8_SYM_ROW) {
-    g *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[out_row]);
-    u *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales2)[out_row]);
+    g *= pre ? pre_scale_g : Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[out_row]);
+    u *= pre ? pre_scale_u : Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales2)[out_row]);
   }
   g *= score;
   u *= score;

@@ -84,6 +84,25 @@ def test_batch4_matches_per_sequence_runs():
         assert same >= 8, f"sequence {b}: batched decode diverges from the single run after {same} tokens"
 
 
+def test_batch4_short_context_attention_head_dim_128():
+    """Batch 4 at head dim 128 with dependent launch: the one-CTA-per-head attention kernel serves 2 KV heads x 4
+    sequences beside the QKV projection; logits must match the oracle sequence by sequence."""
+    cfg, dtype = SMALL128, torch.float16
+    w = oracle.make_llama_weights(cfg, dtype, seed=6, std=0.05)
+    g = torch.Generator().manual_seed(9)
+    toks = torch.randint(0, cfg["vocab"], (4, 10), generator=g)
+    stack = LlamaDecodeStack(_to_cuda(w), cfg, max_seq=64, batch=4, max_new_tokens=32, flags=capi.MUI_FLAG_PDL)
+    refs = [oracle.LlamaOracle(w, cfg, max_T=64) for _ in range(4)]
+    for t in range(toks.shape[1]):
+        stack.set_tokens(toks[:, t].contiguous())
+        stack.step()
+        got = stack.logits().float().cpu()
+        for b in range(4):
+            want = refs[b].forward(toks[b:b + 1, t:t + 1])
+            torch.testing.assert_close(got[b:b + 1], want.to(dtype).float(), rtol=2e-2, atol=2e-2)
+    assert capi.device_status() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_whole_step_kernel_logits_match_oracle(dtype):
     """The single persistent kernel per step: teacher-forced logits against the oracle, like the per-kernel path."""

@@ -153,7 +153,8 @@ def test_flash_decode_softmax_shift_invariance():
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("B,Hq,Hkv,S", [(1, 32, 8, 1), (1, 32, 8, 2), (1, 32, 8, 17), (1, 32, 8, 280), (1, 32, 8, 385), (1, 32, 8, 386),
                                         (1, 32, 8, 513),
-                                        (2, 8, 1, 2000), (3, 4, 4, 65), (1, 8, 8, 4096)])
+                                        (2, 8, 1, 2000), (3, 4, 4, 65), (1, 8, 8, 4096), (2, 8, 1, 300), (2, 4, 2, 384),
+                                        (1, 16, 2, 97)])
 @pytest.mark.parametrize("variant", [0, capi.MUI_FLAG_SHORT_CONTEXT, capi.MUI_FLAG_SHORT_CONTEXT | capi.MUI_FLAG_PDL])
 def test_fused_rope_cache_write_attention(dtype, B, Hq, Hkv, S, variant):
     """One launch = RoPE(q, k_new) + cache write + attention over S tokens (the new one last): the cluster kernel, and
