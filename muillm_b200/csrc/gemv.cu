@@ -25,7 +25,7 @@ MUI_STATUS_ACCESSOR(gemv)
 // Tuning knobs of the pipeline kernel, read once from the environment (for benchmarking only):
 //   MUI_PIPE_KC      row-chunk length in elements: 2048 (default) or 1024
 //   MUI_PIPE_CTAS    CTAs per SM the grid is sized for: 1 (default) or 2
-//   MUI_PIPE_SMEM_KB shared-memory budget per CTA in KiB (default 222)
+//   MUI_PIPE_SMEM_KB shared-memory budget per CTA in KiB (default 226 of the 227 a block may have)
 static int env_int(const char* name, int dflt) {
   const char* e = getenv(name);
   return (e && *e) ? atoi(e) : dflt;
@@ -39,7 +39,7 @@ static int mui_pipe_ctas() {
   return v;
 }
 static int mui_pipe_smem_kb() {
-  static int v = env_int("MUI_PIPE_SMEM_KB", 222);
+  static int v = env_int("MUI_PIPE_SMEM_KB", 226);
   return v;
 }
 
@@ -551,7 +551,8 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   using G = PipeGeom<KC, WB>;
   // One CTA per SM with (nearly) all of its shared memory: ~190 KiB of copies in flight per SM is what keeps
   // HBM busy; with half of that the kernel runs ~25 % slower.
-  const int budget_small = std::min(mui_pipe_smem_kb(), 222) * 1024, budget_full = 222 * 1024;
+  // 226 KiB: with K = 14336 the staged activations (28 KiB) and three 64.25 KiB stages need 222.8 KiB
+  const int budget_small = std::min(mui_pipe_smem_kb(), 226) * 1024, budget_full = 226 * 1024;
   const int fixed = pipe_layout(G::STAGE_BYTES, 0, x_rows, a.Kp, NB).total;
   int ctas_per_sm = std::max(1, std::min(2, mui_pipe_ctas()));
   int stages = (budget_small - fixed) / G::STAGE_BYTES;
@@ -571,7 +572,7 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   const int grid = std::max(1, std::min(units, sms * ctas_per_sm));
   auto launch = [&](auto kern, int threads, bool* configured) -> mui_status_t {
     if (!*configured) {
-      MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+      MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
       MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                           cudaSharedmemCarveoutMaxShared));
       *configured = true;
