@@ -200,12 +200,46 @@ def llama4_fixtures(out):
         out[f"l4_slide_states_v_{step}"] = vv[:, :, :n].float().numpy().copy()
 
 
+def hf_llama_d64_fixture(out):
+    """A whole HF Llama with head dim 64 (the smallest the GPU attention kernels take): weights, prompt, greedy tokens."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    g = torch.Generator().manual_seed(21)
+    cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                      num_key_value_heads=1, head_dim=64, vocab_size=256, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      max_position_embeddings=128, attention_bias=False, mlp_bias=False, tie_word_embeddings=False)
+    model = LlamaForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() > 1:
+                p.copy_((torch.randn(p.shape, generator=g) * 0.08).half().float())
+            else:
+                p.copy_((1 + 0.01 * torch.randn(p.shape, generator=g)).half().float())
+    prompt = torch.randint(0, 256, (1, 16), generator=g)
+    with torch.no_grad():
+        gen = model.generate(prompt, max_new_tokens=32, do_sample=False, pad_token_id=0)
+        logits = model(prompt).logits[:, -1]
+    out["prompt"] = prompt.numpy()
+    out["tokens"] = gen[:, 16:].numpy()
+    out["prompt_logits"] = logits.numpy()
+    top2 = torch.topk(logits[0], 2).values
+    out["prompt_top2_margin"] = (top2[0] - top2[1]).numpy()
+    for name, t in model.state_dict().items():
+        out["sd/" + name] = t.half().numpy()
+
+
 def main():
     if sys.argv[1:] == ["llama4"]:
         l4 = {}
         llama4_fixtures(l4)
         np.savez_compressed(os.path.join(HERE, "hf_llama4_ops.npz"), **l4)
         print("hf_llama4_ops.npz", os.path.getsize(os.path.join(HERE, "hf_llama4_ops.npz")) // 1024, "KiB")
+        return
+    if sys.argv[1:] == ["llama_d64"]:
+        d = {}
+        hf_llama_d64_fixture(d)
+        np.savez_compressed(os.path.join(HERE, "hf_llama_d64.npz"), **d)
+        print("hf_llama_d64.npz", os.path.getsize(os.path.join(HERE, "hf_llama_d64.npz")) // 1024, "KiB")
         return
     ref, hf = {}, {}
     # HF first: in this container, running the reference's bf16/fp16 CPU branches first left the later fp32
