@@ -51,6 +51,19 @@ int mui_take_gemv_reserve_sms() {
   return n;
 }
 
+// Bytes at the head of each CTA's range of a hinted matrix that the prefetch leaves out (the consuming kernel's own
+// ring fetches them as soon as it is resident); set together with the hint, consumed with it.
+static thread_local int tls_pf_skip[3] = {0, 0, 0};
+void mui_set_prefetch_skip(const int* skip_bytes, int n) {
+  for (int i = 0; i < 3; ++i) tls_pf_skip[i] = (i < n && skip_bytes[i] > 0) ? skip_bytes[i] : 0;
+}
+void mui_take_prefetch_skip(int* skip_bytes) {
+  for (int i = 0; i < 3; ++i) {
+    skip_bytes[i] = tls_pf_skip[i];
+    tls_pf_skip[i] = 0;
+  }
+}
+
 void mui_take_prefetch_hint(const void** ptrs, int* rows, int* row_bytes, int* frac1024) {
   for (int i = 0; i < 3; ++i) {
     ptrs[i] = tls_pf_ptr[i];

@@ -354,8 +354,10 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
         if (a.pf_ptr[sgm] == nullptr || a.pf_frac[sgm] <= 0) continue;
         const long long rows = a.pf_rows[sgm], rbytes = a.pf_row_bytes[sgm];
         const long long pr0 = rows * blockIdx.x / gridDim.x, pr1 = rows * (blockIdx.x + 1) / gridDim.x;
-        const long long b0 = pr0 * rbytes;
-        const long long nb = ((pr1 - pr0) * rbytes * a.pf_frac[sgm] / 1024) & ~15ll;
+        const long long total = (pr1 - pr0) * rbytes;
+        const long long skip = min(static_cast<long long>(a.pf_skip[sgm]) & ~15ll, total);
+        const long long b0 = pr0 * rbytes + skip;
+        const long long nb = min((total * a.pf_frac[sgm] / 1024) & ~15ll, total - skip);
         const unsigned char* base = reinterpret_cast<const unsigned char*>(a.pf_ptr[sgm]) + b0;
         for (long long off = (long long)lane * 8192; off < nb; off += 32 * 8192)
           bulk_prefetch_l2(base + off, static_cast<uint32_t>(min(8192ll, nb - off)));
@@ -664,6 +666,7 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
   GemvArgs a = a_in;
   if (a.trace == nullptr) a.trace = mui_trace_next_record(mode == 0 ? 1 : 2);
   mui_take_prefetch_hint(a.pf_ptr, a.pf_rows, a.pf_row_bytes, a.pf_frac);
+  mui_take_prefetch_skip(a.pf_skip);
   a.reserve_sms = mui_take_gemv_reserve_sms();
   const int nb = a.B <= 1 ? 1 : (a.B <= 2 ? 2 : (a.B <= 4 ? 4 : 8));
   // Activations of all batch rows are staged in shared memory; when they cannot fit (large K with B > 1), run

@@ -45,6 +45,7 @@ struct GemvArgs {
   int pf_rows[3];
   int pf_row_bytes[3];
   int pf_frac[3];
+  int pf_skip[3];  // bytes left out at the head of each CTA range (fetched by the consumer kernel's own ring)
   int reserve_sms; // SMs the bulk-copy pipeline leaves without a CTA (a small dependent kernel moves in early)
   int use_comm;    // tensor-parallel: push the fp32 results to every rank, then all-reduce into y
   CommDev comm;

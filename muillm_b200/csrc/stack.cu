@@ -160,8 +160,6 @@ mui_status_t launch_mega(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   return mui_launch_mega_step(stream, c.dtype, a, c.heads / c.kv_heads, grid, (flags & MUI_FLAG_PDL) ? 1 : 0);
 }
 
-// Hint for the GEMV about to be launched: the weight matrices that follow it in execution order, up to `window`
-// bytes in total (a gate/up pair shares its part of the window evenly, since the kernel consumes both in step).
 // Decode state from caller-owned device tensors (mui_llama_stack_forward_hidden): tokens in cache = cache position,
 // attended length = cache position + 1; the step counter is left alone.
 __global__ void set_decode_state_kernel(long long* state, int32_t* seq_len32, const long long* tokens,
@@ -195,6 +193,8 @@ bool short_context_enabled() {
   return v != 0;
 }
 
+// Hint for the GEMV about to be launched: the weight matrices that follow it in execution order, up to `window`
+// bytes in total (a gate/up pair shares its part of the window evenly, since the kernel consumes both in step).
 void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t window) {
   const void* ptrs[3] = {nullptr, nullptr, nullptr};
   int rows[3] = {0, 0, 0}, rbytes[3] = {0, 0, 0}, frac[3] = {0, 0, 0};
@@ -225,6 +225,15 @@ void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t win
     }
   }
   mui_prefetch_hint(ptrs, rows, rbytes, frac, n);
+  // the consumer's own ring (three 64 KiB stages per CTA) fetches the head of each CTA range the moment it is
+  // resident: the hint covers what comes after it. A gate/up pair shares one ring.
+  static const int skip_kb = [] {
+    const char* e = getenv("MUI_PREFETCH_SKIP_KB");
+    return e ? atoi(e) : 0;
+  }();
+  int skip[3] = {0, 0, 0};
+  for (int j = 0; j < n; ++j) skip[j] = skip_kb * 1024 / ((n >= 2 && rows[0] == rows[1] && j < 2) ? 2 : 1);
+  mui_set_prefetch_skip(skip, n);
 }
 
 mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags) {
