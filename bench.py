@@ -25,7 +25,7 @@ LLAMA31_8B = dict(layers=32, hidden=4096, intermediate=14336, heads=32, kv_heads
                   eps=1e-5, rope_theta=500000.0)
 PROMPT_LEN = 16
 MAX_SEQ = 4096
-# Llama 3 8B fp16 bs=1 on MI300X: 1 GPU and tensor-parallel 4 (reference README.md:56-57)
+# Llama 3 8B fp16 bs=1 on MI300X: 1 GPU and tensor-parallel 4 (the reference's published figures, its README.md:56-57)
 BASELINE_TOK_S = {1: 210.0, 4: 420.0}
 NOMINAL_HBM_GBS = 8000.0
 

@@ -1,5 +1,5 @@
 """Generates the golden fixtures under tests/golden/ (run once in the authoring container; needs the reference
-checkout at /root/reference and transformers). Committed beside the fixtures it made.
+checkout, whose location is REF below or $MUILLM_REFERENCE, and transformers). Committed beside the fixtures it made.
 
 Sources of truth, in order of authority:
  * the reference's own Python, imported unmodified with a stub `muillm_ext` (the CPU branches never call it):
@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = "/root/reference"
+REF = os.environ.get("MUILLM_REFERENCE", "/root/reference")
 
 
 class _Stub(types.ModuleType):

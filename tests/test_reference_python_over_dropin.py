@@ -8,7 +8,7 @@ import sys
 import pytest
 import torch
 
-REF = "/root/reference"
+REF = os.environ.get("MUILLM_REFERENCE", "/root/reference")
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "muillm")), reason="reference checkout absent")
 
 
