@@ -457,6 +457,18 @@ MUI_API mui_status_t mui_llama_stack_reset(mui_llama_stack_t* stack, void* strea
 /* Token ids (int64, `batch` of them) fed to the next step; host or device pointer. */
 MUI_API mui_status_t mui_llama_stack_set_tokens(mui_llama_stack_t* stack, void* stream, const int64_t* tokens,
                                                 int on_device);
+/* Batches of sequences with different lengths, left-padded to a common length the way the reference's generation
+ * loop receives them from the HF tokenizer (attention_mask + position_ids, muillm/modules/models/llama/model.py:437-615,
+ * masked attention csrc/attention/flash_decoding.cu:307-325): all sequences share the cache row and the attended
+ * length, every sequence has its own RoPE position, and `mask_dev` ([batch, max_seq] of the model dtype, additive:
+ * 0 keeps a cache row, anything else drops it, e.g. the rows of a sequence's padding) is applied by every layer's
+ * attention. With a mask set, a step runs RoPE + cache write and masked split-KV flash decoding as two launches
+ * instead of the fused attention kernel. NULL clears the mask. Changing the mask drops a captured graph; its
+ * CONTENTS may change between replays. mui_llama_stack_set_position_ids overwrites the per-sequence positions the
+ * next step uses (host or device array of `batch` int64); every step then advances them by one. */
+MUI_API mui_status_t mui_llama_stack_set_attention_mask(mui_llama_stack_t* stack, const void* mask_dev);
+MUI_API mui_status_t mui_llama_stack_set_position_ids(mui_llama_stack_t* stack, void* stream,
+                                                      const int64_t* position_ids, int on_device);
 /* Phase timeline of the whole-step kernel (MUI_FLAG_MEGAKERNEL): CTA 0 writes {tag, %globaltimer ns} pairs of
  * uint64 at every phase boundary of every layer (0 layer start, 1/4/6/9/12 after a grid barrier, 2/7/10/13 after
  * staging the activations, 3/8/11/14 after a projection, 5 after attention) into device_buffer (16 bytes per

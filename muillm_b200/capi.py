@@ -217,6 +217,8 @@ PROTOTYPES = {
     "mui_llama_stack_destroy": (c_int, [c_void_p]),
     "mui_llama_stack_set_comm": (c_int, [c_void_p, c_void_p]),
     "mui_llama_stack_reset": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), c_void_p, c_int]),
+    "mui_llama_stack_set_attention_mask": (c_int, [c_void_p, c_void_p]),
+    "mui_llama_stack_set_position_ids": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
     "mui_llama_stack_set_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
     "mui_llama_stack_op_trace": (c_int, [c_void_p, c_void_p, c_int]),
     "mui_llama_stack_step": (c_int, [c_void_p, c_void_p, c_uint]),

@@ -54,6 +54,7 @@ struct mui_llama_stack {
   cudaGraphExec_t graph_exec;
   unsigned graph_flags;
   mui_comm_t* comm;  // tensor-parallel communicator (null on a single GPU)
+  const void* attn_mask;  // additive [B, max_seq] of the model dtype (left-padded batches), or null
   CommDev comm_dev;
   // whole-step kernel
   bool mega_ok;
@@ -239,9 +240,9 @@ void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t win
 mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags) {
   const mui_llama_config_t& c = s->cfg;
   if (flags & MUI_FLAG_MEGAKERNEL) {
-    MUI_REQUIRE(s->mega_ok && s->comm == nullptr, MUI_ERR_UNSUPPORTED,
+    MUI_REQUIRE(s->mega_ok && s->comm == nullptr && s->attn_mask == nullptr, MUI_ERR_UNSUPPORTED,
                 "the whole-step kernel covers batch 1, head_dim 128, at most 4 query heads per KV head, sizes that "
-                "are multiples of 16 and no tensor parallelism");
+                "are multiples of 16, no attention mask and no tensor parallelism");
     return launch_mega(s, stream, flags);
   }
   const int B = c.batch, H = c.hidden, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim;
@@ -264,7 +265,8 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   const size_t e = 2;
   for (int l = 0; l < c.layers; ++l) {
     if (pf) hint_prefetch(s->order, 5 * (size_t)l + 1, s->prefetch_window);
-    const bool fused_attn = D == 128 && Hq / Hkv <= 8 && !(flags & MUI_FLAG_FORCE_GENERIC);
+    // a masked (left-padded) batch takes RoPE + cache write and split-KV flash decoding as two launches
+    const bool fused_attn = D == 128 && Hq / Hkv <= 8 && !(flags & MUI_FLAG_FORCE_GENERIC) && s->attn_mask == nullptr;
     // short histories: one CTA per KV head that moves in beside the QKV projection (which leaves it the SMs) and
     // has the K/V rows in shared memory by the time q arrives
     const int attended = s->capturing ? s->s_upper : s->host_pos + 1;
@@ -288,7 +290,7 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
                             s->q_rot, nullptr, s->k_cache[l], s->v_cache[l], (const int64_t*)cache_position, flags);
       if (st != MUI_OK) return st;
       st = mui_flash_decode(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->seq_len32, c.attn_scale, s->q_rot,
-                            s->k_cache[l], s->v_cache[l], kvs, nullptr, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
+                            s->k_cache[l], s->v_cache[l], kvs, s->attn_mask, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
       if (st != MUI_OK) return st;
     }
     if (pf) hint_prefetch(s->order, 5 * (size_t)l + 2, s->prefetch_window);
@@ -396,6 +398,7 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
   s->graph_exec = nullptr;
   s->graph_flags = 0;
   s->comm = nullptr;
+  s->attn_mask = nullptr;
   s->op_trace = nullptr;
   s->op_trace_cap = 0;
   {
@@ -522,6 +525,24 @@ mui_status_t mui_llama_stack_set_tokens(mui_llama_stack_t* s, void* stream, cons
   const int B = s->cfg.batch;
   MUI_CUDA_CHECK(cudaMemcpyAsync(s->state + 3 + B, tokens, B * sizeof(long long),
                                  on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_set_position_ids(mui_llama_stack_t* s, void* stream, const int64_t* position_ids,
+                                              int on_device) {
+  MUI_REQUIRE(s && position_ids, MUI_ERR_INVALID_ARG, "null pointer");
+  MUI_CUDA_CHECK(cudaMemcpyAsync(s->state + 3, position_ids, s->cfg.batch * sizeof(long long),
+                                 on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  return MUI_OK;
+}
+
+mui_status_t mui_llama_stack_set_attention_mask(mui_llama_stack_t* s, const void* mask_dev) {
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  if (mask_dev != s->attn_mask && s->graph_exec) {  // a captured step holds the old attention launches
+    cudaGraphExecDestroy(s->graph_exec);
+    s->graph_exec = nullptr;
+  }
+  s->attn_mask = mask_dev;
   return MUI_OK;
 }
 

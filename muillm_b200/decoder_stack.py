@@ -129,6 +129,22 @@ class LlamaDecodeStack:
         capi.check(self.lib.mui_llama_stack_set_tokens(self._h, self._stream(), tokens.data_ptr(),
                                                        1 if tokens.is_cuda else 0))
 
+    def set_position_ids(self, position_ids):
+        """Per-sequence RoPE positions of the next step: int64 tensor [batch], host or device."""
+        assert position_ids.dtype == torch.int64 and position_ids.numel() == self.batch
+        capi.check(self.lib.mui_llama_stack_set_position_ids(self._h, self._stream(), position_ids.data_ptr(),
+                                                             1 if position_ids.is_cuda else 0))
+
+    def set_attention_mask(self, mask):
+        """Additive mask [batch, max_seq] of the model dtype on the device (0 keeps a cache row, anything else drops
+        it), applied by every layer's attention; None clears it. The stack keeps a reference to the tensor."""
+        if mask is not None:
+            assert mask.is_cuda and mask.is_contiguous() and mask.dtype == self.dtype
+            assert tuple(mask.shape) == (self.batch, self.max_seq)
+        self._mask = mask
+        capi.check(self.lib.mui_llama_stack_set_attention_mask(self._h, mask.data_ptr() if mask is not None else None))
+        self._captured = False
+
     def step(self):
         capi.check(self.lib.mui_llama_stack_step(self._h, self._stream(), self.flags))
 
@@ -198,3 +214,46 @@ class LlamaDecodeStack:
                 for _ in range(remaining):
                     self.step()
         return self.out_tokens[T - 1: T - 1 + new_tokens].transpose(0, 1).contiguous()
+
+    def greedy_ragged(self, prompts, new_tokens, use_graph=True, pad_token=0):
+        """Greedy decoding of `batch` prompts of different lengths (list of 1-D int64 tensors), left-padded to the
+        longest one as the HF tokenizer hands them to the reference's generation loop: the padding rows of a sequence
+        are masked out of its attention for good and its RoPE positions start at its first real token
+        (position_ids = cumsum(attention_mask) - 1). Returns int64 [batch, new_tokens] (device)."""
+        assert len(prompts) == self.batch
+        lens = [int(p.numel()) for p in prompts]
+        T = max(lens)
+        pads = torch.tensor([T - n for n in lens], dtype=torch.int64)
+        padded = torch.full((self.batch, T), int(pad_token), dtype=torch.int64)
+        for b, p in enumerate(prompts):
+            padded[b, T - lens[b]:] = p.cpu()
+        # a sequence's padding rows are dropped from the step of its first real token on; while it is still being
+        # padded it attends its own padding (results unused), so no step ever has an empty attention set
+        mask = torch.zeros(self.batch, self.max_seq, dtype=self.dtype, device=self.device)
+        self.reset(0)
+        self.set_attention_mask(mask)
+        try:
+            for t in range(T):
+                for b in range(self.batch):
+                    if t > 0 and int(pads[b]) == t:
+                        mask[b, :t] = torch.finfo(self.dtype).min
+                self.set_position_ids(torch.clamp(t - pads, min=0))
+                self.set_tokens(padded[:, t].contiguous())
+                self.step()
+            remaining = new_tokens - 1
+            if remaining > 0:
+                if use_graph:
+                    s = torch.cuda.Stream()
+                    s.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(s):
+                        self.capture()
+                        self.replay(remaining)
+                    torch.cuda.current_stream().wait_stream(s)
+                else:
+                    for _ in range(remaining):
+                        self.step()
+            out = self.out_tokens[T - 1: T - 1 + new_tokens].transpose(0, 1).contiguous()
+            torch.cuda.synchronize()
+        finally:
+            self.set_attention_mask(None)
+        return out

@@ -84,6 +84,30 @@ def test_batch4_matches_per_sequence_runs():
         assert same >= 8, f"sequence {b}: batched decode diverges from the single run after {same} tokens"
 
 
+@pytest.mark.parametrize("cfg", [TINY, SMALL128], ids=["tiny64", "small128"])
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_ragged_left_padded_batch_matches_per_sequence_oracle(cfg, use_graph):
+    """Prompts of different lengths decoded together (left padding, attention mask, per-sequence RoPE positions: the
+    batched case of BASELINE config 4) produce the tokens the oracle produces for each prompt alone."""
+    dtype = torch.float16
+    w = oracle.make_llama_weights(cfg, dtype, seed=11, std=0.08)
+    g = torch.Generator().manual_seed(12)
+    lens = [3, 9, 1, 12]
+    prompts = [torch.randint(0, cfg["vocab"], (n,), generator=g) for n in lens]
+    stack = LlamaDecodeStack(_to_cuda(w), cfg, max_seq=64, batch=4, max_new_tokens=40, flags=capi.MUI_FLAG_PDL)
+    got = stack.greedy_ragged(prompts, 12, use_graph=use_graph).cpu()
+    assert capi.device_status() == 0
+    for b, p in enumerate(prompts):
+        want = oracle.LlamaOracle(w, cfg, max_T=64).greedy(p[None, :], 12)[0]
+        same = (want == got[b]).long().cumprod(0).sum().item()
+        assert same >= 6, f"sequence {b} (length {lens[b]}): {got[b].tolist()} vs oracle {want.tolist()}"
+    # the mask is gone afterwards: an unpadded run on the same stack takes the usual path and still matches
+    eq = torch.stack([prompts[3][:6]] * 4)
+    again = stack.greedy(eq, 4, use_graph=False).cpu()
+    want = oracle.LlamaOracle(w, cfg, max_T=64).greedy(eq[:1], 4)[0]
+    assert torch.equal(again[0], want) and torch.equal(again[3], want)
+
+
 def test_batch4_short_context_attention_head_dim_128():
     """Batch 4 at head dim 128 with dependent launch: the one-CTA-per-head attention kernel serves 2 KV heads x 4
     sequences beside the QKV projection; logits must match the oracle sequence by sequence."""
