@@ -1,0 +1,145 @@
+"""Batch-1 decode of a Llama-4 text model (MoE with a shared expert and top-k sigmoid routing, chunked attention in
+the rope layers, full attention with temperature tuning in the no-rope layers) as a chain of the library's kernels:
+the per-token path the reference runs through MuiLLMParallelLlama4DecoderStack
+(csrc/modules/parallel_llama4_decoder_stack.cpp, parallel_llama4_decoder_module.cpp:25-66,
+parallel_llama4_attention_module.cpp:45-134, parallel_gateupmoe_module.cpp).
+
+Per layer and token, six launches:
+  fused RMSNorm -> QKV GEMV; rope / QK L2 norm / temperature scale (one launch); K/V row written into a static cache;
+  flash decoding over the rows the layer may see; o_proj GEMV + residual; fused RMSNorm -> router GEMV; top-k sigmoid;
+  MoE gate/up+SiLU over the shared and the selected experts; expert down projections summed + residual.
+Chunked attention needs neither a ring buffer nor a mask here: every layer keeps a plain [1, Hkv, max_seq, D] cache and
+a chunked layer hands flash decoding the strided view of the rows of the current chunk.
+
+Each launch is one Python call (there is no whole-step C stack for this architecture yet).
+"""
+import torch
+
+from . import ops
+
+
+def llama4_config_from_hf(c):
+    """dict for Llama4DecodeRunner from a transformers Llama4TextConfig (or an object with the same attributes)."""
+    theta = getattr(c, "rope_theta", None)
+    if theta is None:
+        theta = (getattr(c, "rope_parameters", None) or {}).get("rope_theta", 500000.0)
+    return dict(layers=c.num_hidden_layers, hidden=c.hidden_size, expert_intermediate=c.intermediate_size,
+                heads=c.num_attention_heads, kv_heads=c.num_key_value_heads, head_dim=c.head_dim, vocab=c.vocab_size,
+                experts=c.num_local_experts, top_k=c.num_experts_per_tok, eps=c.rms_norm_eps, rope_theta=float(theta),
+                chunk=c.attention_chunk_size, use_rope=[bool(v) for v in c.no_rope_layers],
+                use_qk_norm=bool(c.use_qk_norm), temperature_tuning=bool(c.attn_temperature_tuning),
+                attn_scale=float(c.attn_scale), floor_scale=float(c.floor_scale))
+
+
+def llama4_weights_from_state_dict(sd, cfg, dtype=torch.bfloat16, device="cuda"):
+    """HF parameter names -> the packed layout the kernels stream: q, k, v rows concatenated; gate and up rows of the
+    shared expert followed by those of every routed expert ([(1+E)*I, H]); down matrices stacked the same way
+    ([(1+E)*H, I]). HF stores the routed experts transposed and gate|up fused ([E, H, 2I] and [E, I, H]); they are
+    split and transposed once here (muillm/modules/moe/gateupdownmlpmoe.py does the same at replacement time)."""
+
+    def t(name):
+        return torch.as_tensor(sd[name]).to(device=device, dtype=dtype).contiguous()
+
+    I = cfg["expert_intermediate"]
+    lm_head = "lm_head.weight" if "lm_head.weight" in sd else "model.embed_tokens.weight"
+    w = {"embed": t("model.embed_tokens.weight"), "lm_head": t(lm_head), "norm": t("model.norm.weight"),
+         "qkv": [], "o": [], "router": [], "gate": [], "up": [], "down": [], "ln1": [], "ln2": []}
+    for l in range(cfg["layers"]):
+        p = f"model.layers.{l}."
+        w["qkv"].append(torch.cat([t(p + "self_attn.q_proj.weight"), t(p + "self_attn.k_proj.weight"),
+                                   t(p + "self_attn.v_proj.weight")], dim=0).contiguous())
+        w["o"].append(t(p + "self_attn.o_proj.weight"))
+        w["ln1"].append(t(p + "input_layernorm.weight"))
+        w["ln2"].append(t(p + "post_attention_layernorm.weight"))
+        w["router"].append(t(p + "feed_forward.router.weight"))
+        gu = t(p + "feed_forward.experts.gate_up_proj")          # [E, H, 2I]
+        dn = t(p + "feed_forward.experts.down_proj")             # [E, I, H]
+        gates = [t(p + "feed_forward.shared_expert.gate_proj.weight")]
+        ups = [t(p + "feed_forward.shared_expert.up_proj.weight")]
+        downs = [t(p + "feed_forward.shared_expert.down_proj.weight")]
+        for e in range(cfg["experts"]):
+            gates.append(gu[e, :, :I].t())
+            ups.append(gu[e, :, I:].t())
+            downs.append(dn[e].t())
+        w["gate"].append(torch.cat(gates, dim=0).contiguous())
+        w["up"].append(torch.cat(ups, dim=0).contiguous())
+        w["down"].append(torch.cat(downs, dim=0).contiguous())
+    return w
+
+
+class Llama4DecodeRunner:
+    """Greedy batch-1 decoding of a Llama-4 text model over the packed weights of llama4_weights_from_state_dict."""
+
+    def __init__(self, weights, cfg, max_seq, flags=0):
+        self.w, self.cfg, self.max_seq, self.flags = weights, dict(cfg), max_seq, flags
+        dev, dt = weights["embed"].device, weights["embed"].dtype
+        self.device, self.dtype = dev, dt
+        Hkv, D = cfg["kv_heads"], cfg["head_dim"]
+        self.k_cache = [torch.zeros(1, Hkv, max_seq, D, dtype=dt, device=dev) for _ in range(cfg["layers"])]
+        self.v_cache = [torch.zeros(1, Hkv, max_seq, D, dtype=dt, device=dev) for _ in range(cfg["layers"])]
+        # interleaved-pair rotation angles per position, as (cos, sin) pairs: what HF's Llama4TextRotaryEmbedding
+        # returns as complex numbers (freqs_cis)
+        inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+        ang = torch.outer(torch.arange(max_seq, dtype=torch.float32), inv)
+        self.freqs = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(dev).contiguous()  # [max_seq, D/2, 2]
+        self.pos = 0
+
+    def reset(self):
+        self.pos = 0
+
+    def step(self, token):
+        """One token (python int or 0-dim tensor) in, logits [1, vocab] (model dtype) out; advances the position."""
+        c, w, f = self.cfg, self.w, self.flags
+        Hq, Hkv, D = c["heads"], c["kv_heads"], c["head_dim"]
+        pos = self.pos
+        if pos >= self.max_seq:
+            raise RuntimeError("the static cache is full")
+        tok = torch.as_tensor([int(token)], dtype=torch.int64, device=self.device)
+        h = w["embed"].index_select(0, tok).view(1, 1, c["hidden"])
+        cache_position = torch.tensor([pos], dtype=torch.int64, device=self.device)
+        pe = self.freqs[pos: pos + 1].unsqueeze(0)   # [1, 1, D/2, 2]
+        for l in range(c["layers"]):
+            rope = c["use_rope"][l]
+            qkv = ops.muillm_linear_forward(None, h, w["qkv"][l], norm_weights=w["ln1"][l], epsilon=c["eps"], flags=f)
+            q = qkv[..., : Hq * D].view(1, Hq, 1, D)
+            k = qkv[..., Hq * D: (Hq + Hkv) * D].view(1, Hkv, 1, D)
+            v = qkv[..., (Hq + Hkv) * D:].view(1, Hkv, 1, D)
+            tune = c["temperature_tuning"] and not rope
+            norm = c["use_qk_norm"] and rope
+            if rope or norm or tune:
+                q, k = ops.llama4_qk_prologue(q, k, position_embeds=pe if rope else None,
+                                              qk_norm_eps=c["eps"] if norm else None,
+                                              cache_position=cache_position if tune else None,
+                                              attn_scale=c["attn_scale"], floor_scale=c["floor_scale"], flags=f)
+            k_all, v_all = ops.muillm_static_kvcache_update(k, v, self.k_cache[l], self.v_cache[l], cache_position,
+                                                            pos + 1, flags=f)
+            if rope and c["chunk"]:
+                # chunked attention: only the rows of the chunk the new token belongs to
+                start = (pos // c["chunk"]) * c["chunk"]
+                k_all, v_all = k_all.narrow(2, start, pos + 1 - start), v_all.narrow(2, start, pos + 1 - start)
+            q = q if q.is_contiguous() else q.contiguous()
+            attn = ops.muillm_causal_transformer_decoding_no_mask(q, k_all, v_all, flags=f)
+            h = ops.muillm_linear_forward(None, attn, w["o"][l], residual=h, flags=f)
+            logits = ops.muillm_linear_forward(None, h, w["router"][l], norm_weights=w["ln2"][l], epsilon=c["eps"],
+                                               flags=f)
+            scores, idx = ops.muillm_topk_sigmoid_forward(logits, c["top_k"], flags=f)
+            h = ops.muillm_gateupsilumoe_forward(None, 1, c["experts"], w["ln2"][l], c["eps"], w["gate"][l],
+                                                 w["up"][l], w["down"][l], h, h, scores.reshape(-1), idx.reshape(-1),
+                                                 flags=f)
+        self.pos = pos + 1
+        return ops.muillm_linear_forward(None, h, w["lm_head"], norm_weights=w["norm"], epsilon=c["eps"],
+                                         flags=f).view(1, -1)
+
+    def greedy(self, prompt, new_tokens):
+        """prompt: 1-D int64 tensor; returns the new_tokens greedy continuation (int64, device)."""
+        self.reset()
+        logits = None
+        for t in prompt.reshape(-1).tolist():
+            logits = self.step(t)
+        out = []
+        for _ in range(new_tokens):
+            nxt = int(torch.argmax(logits.float(), dim=-1).item())
+            out.append(nxt)
+            if len(out) < new_tokens:
+                logits = self.step(nxt)
+        return torch.tensor(out, dtype=torch.int64, device=self.device)

@@ -228,7 +228,63 @@ def hf_llama_d64_fixture(out):
         out["sd/" + name] = t.half().numpy()
 
 
+LLAMA4_TINY = dict(vocab_size=256, hidden_size=128, intermediate_size=64, intermediate_size_mlp=128,
+                   num_hidden_layers=4, num_attention_heads=2, num_key_value_heads=1, head_dim=64, num_local_experts=4,
+                   num_experts_per_tok=1, interleave_moe_layer_step=1, attention_chunk_size=8, rope_theta=500000.0,
+                   rms_norm_eps=1e-5, use_qk_norm=True, attn_temperature_tuning=True, floor_scale=4, attn_scale=0.1,
+                   max_position_embeddings=128, no_rope_layer_interval=4, tie_word_embeddings=False, pad_token_id=0,
+                   bos_token_id=1, eos_token_id=2)
+
+
+def hf_llama4_model_fixture(out):
+    """A whole HF Llama-4 text model (MoE with a shared expert and top-1 sigmoid routing in every layer, chunked
+    attention of 8 tokens with rope + QK L2 norm in layers 0-2, full attention with temperature tuning and no rope
+    in layer 3): fp16-representable weights, a 12-token prompt and the 24 tokens generate(do_sample=False) produced in
+    fp32, so the run crosses four chunk boundaries. The seed is the first whose smallest top-2 logit margin over the
+    24 steps exceeds 0.05, which keeps a 16-bit implementation on the same tokens."""
+    from transformers import Llama4ForCausalLM, Llama4TextConfig
+
+    cfg = Llama4TextConfig(attn_implementation="eager", **LLAMA4_TINY)
+    for seed in range(40, 80):
+        g = torch.Generator().manual_seed(seed)
+        model = Llama4ForCausalLM(cfg).eval()
+        with torch.no_grad():
+            for p in model.parameters():
+                if p.dim() > 1:
+                    p.copy_((torch.randn(p.shape, generator=g) * 0.08).half().float())
+                else:
+                    p.copy_((1 + 0.01 * torch.randn(p.shape, generator=g)).half().float())
+        prompt = torch.randint(3, 256, (1, 12), generator=g)
+        with torch.no_grad():
+            gen = model.generate(prompt, max_new_tokens=24, do_sample=False, pad_token_id=0, eos_token_id=None,
+                                 output_scores=True, return_dict_in_generate=True)
+        margins = []
+        for sc in gen.scores:
+            top2 = torch.topk(sc[0].float(), 2).values
+            margins.append(float(top2[0] - top2[1]))
+        if min(margins) > 0.05:
+            break
+    else:
+        raise RuntimeError("no seed with clear margins")
+    out["seed"] = np.array(seed)
+    out["prompt"] = prompt.numpy()
+    out["tokens"] = gen.sequences[:, 12:].numpy()
+    out["margins"] = np.array(margins, dtype=np.float32)
+    out["no_rope_layers"] = np.array(cfg.no_rope_layers)
+    with torch.no_grad():
+        out["prompt_logits"] = model(prompt).logits[:, -1].numpy()
+    for name, t in model.state_dict().items():
+        out["sd/" + name] = t.half().numpy()
+
+
 def main():
+    if sys.argv[1:] == ["llama4_model"]:
+        d = {}
+        hf_llama4_model_fixture(d)
+        np.savez_compressed(os.path.join(HERE, "hf_llama4_model.npz"), **d)
+        print("hf_llama4_model.npz", os.path.getsize(os.path.join(HERE, "hf_llama4_model.npz")) // 1024, "KiB",
+              "seed", int(d["seed"]), "min margin", float(d["margins"].min()), "no_rope_layers", d["no_rope_layers"])
+        return
     if sys.argv[1:] == ["llama4"]:
         l4 = {}
         llama4_fixtures(l4)
