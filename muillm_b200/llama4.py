@@ -67,11 +67,41 @@ def llama4_weights_from_state_dict(sd, cfg, dtype=torch.bfloat16, device="cuda")
     return w
 
 
+def shard_llama4_weights(w, cfg, rank, world):
+    """Tensor-parallel shard of packed Llama-4 weights, partitioned as the reference does
+    (muillm/modules/parallelmultilinear.py:340-387, muillm/modules/moe/parallelgateupdownmlpmoe.py): whole query / KV
+    heads per rank, o_proj by input columns, every expert's intermediate dimension split across the ranks; embedding,
+    router, norms and lm_head replicated. Returns (weights, per-rank cfg)."""
+    Hq, Hkv, D, H = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["hidden"]
+    I, E = cfg["expert_intermediate"], cfg["experts"] + 1
+    if Hq % world or Hkv % world or I % world:
+        raise RuntimeError("heads, KV heads and the expert intermediate size must be divisible by the world size")
+    hq, hkv, il = Hq // world, Hkv // world, I // world
+    out = {k: w[k] for k in ("embed", "lm_head", "norm", "router", "ln1", "ln2")}
+    out.update(qkv=[], o=[], gate=[], up=[], down=[])
+    for l in range(cfg["layers"]):
+        qkv = w["qkv"][l]
+        q, k, v = qkv[: Hq * D], qkv[Hq * D: (Hq + Hkv) * D], qkv[(Hq + Hkv) * D:]
+        out["qkv"].append(torch.cat([q[rank * hq * D: (rank + 1) * hq * D], k[rank * hkv * D: (rank + 1) * hkv * D],
+                                     v[rank * hkv * D: (rank + 1) * hkv * D]], dim=0).contiguous())
+        out["o"].append(w["o"][l][:, rank * hq * D: (rank + 1) * hq * D].contiguous())
+        sl = slice(rank * il, (rank + 1) * il)
+        out["gate"].append(w["gate"][l].view(E, I, H)[:, sl].reshape(E * il, H).contiguous())
+        out["up"].append(w["up"][l].view(E, I, H)[:, sl].reshape(E * il, H).contiguous())
+        out["down"].append(w["down"][l].view(E, H, I)[:, :, sl].reshape(E * H, il).contiguous())
+    local = dict(cfg)
+    local.update(heads=hq, kv_heads=hkv, expert_intermediate=il)
+    return out, local
+
+
 class Llama4DecodeRunner:
     """Greedy batch-1 decoding of a Llama-4 text model over the packed weights of llama4_weights_from_state_dict."""
 
-    def __init__(self, weights, cfg, max_seq, flags=0):
+    def __init__(self, weights, cfg, max_seq, flags=0, comm=None):
+        """With `comm` (a MuiCommunicator of more than one rank) weights and cfg are this rank's shard
+        (shard_llama4_weights): o_proj and the expert down projections end in the fused all-reduce."""
         self.w, self.cfg, self.max_seq, self.flags = weights, dict(cfg), max_seq, flags
+        self.comm = comm
         dev, dt = weights["embed"].device, weights["embed"].dtype
         self.device, self.dtype = dev, dt
         Hkv, D = cfg["kv_heads"], cfg["head_dim"]
@@ -119,13 +149,20 @@ class Llama4DecodeRunner:
                 k_all, v_all = k_all.narrow(2, start, pos + 1 - start), v_all.narrow(2, start, pos + 1 - start)
             q = q if q.is_contiguous() else q.contiguous()
             attn = ops.muillm_causal_transformer_decoding_no_mask(q, k_all, v_all, flags=f)
-            h = ops.muillm_linear_forward(None, attn, w["o"][l], residual=h, flags=f)
+            if self.comm is not None:
+                h = self.comm.parallel_linear(attn, w["o"][l], residual=h, flags=f)
+            else:
+                h = ops.muillm_linear_forward(None, attn, w["o"][l], residual=h, flags=f)
             logits = ops.muillm_linear_forward(None, h, w["router"][l], norm_weights=w["ln2"][l], epsilon=c["eps"],
                                                flags=f)
             scores, idx = ops.muillm_topk_sigmoid_forward(logits, c["top_k"], flags=f)
-            h = ops.muillm_gateupsilumoe_forward(None, 1, c["experts"], w["ln2"][l], c["eps"], w["gate"][l],
-                                                 w["up"][l], w["down"][l], h, h, scores.reshape(-1), idx.reshape(-1),
-                                                 flags=f)
+            if self.comm is not None:
+                h = self.comm.parallel_moe_mlp(1, c["experts"], w["ln2"][l], c["eps"], w["gate"][l], w["up"][l],
+                                               w["down"][l], h, h, scores.reshape(-1), idx.reshape(-1), flags=f)
+            else:
+                h = ops.muillm_gateupsilumoe_forward(None, 1, c["experts"], w["ln2"][l], c["eps"], w["gate"][l],
+                                                     w["up"][l], w["down"][l], h, h, scores.reshape(-1),
+                                                     idx.reshape(-1), flags=f)
         self.pos = pos + 1
         return ops.muillm_linear_forward(None, h, w["lm_head"], norm_weights=w["norm"], epsilon=c["eps"],
                                          flags=f).view(1, -1)

@@ -137,6 +137,46 @@ def _case_parallel_moe(rank, world, comm):
                 torch.testing.assert_close(got.float().cpu(), want.float(), **tol)
 
 
+def _case_tp_llama4_runner(rank, world, comm):
+    """Llama-4 architecture (MoE + shared expert, chunked and full attention layers) sharded over the ranks against
+    the same model on one GPU (which tests/test_gpu_llama4_model.py holds to Hugging Face), token by token on the
+    single-GPU run's own greedy tokens."""
+    from muillm_b200 import capi
+    from muillm_b200.llama4 import Llama4DecodeRunner, shard_llama4_weights
+
+    cfg = dict(layers=3, hidden=256, expert_intermediate=64, heads=8, kv_heads=8, head_dim=64, vocab=512, experts=4,
+               top_k=1, eps=1e-5, rope_theta=500000.0, chunk=8, use_rope=[True, True, False], use_qk_norm=True,
+               temperature_tuning=True, attn_scale=0.1, floor_scale=4.0)
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(3)
+    H, I, D, E = cfg["hidden"], cfg["expert_intermediate"], cfg["head_dim"], cfg["experts"] + 1
+
+    def rn(*shape):
+        return (torch.randn(*shape, generator=g) * 0.08).to(dtype).cuda()
+
+    def nw():
+        return (1 + 0.01 * torch.randn(H, generator=g)).to(dtype).cuda()
+
+    L = cfg["layers"]
+    w = {"embed": rn(cfg["vocab"], H), "lm_head": rn(cfg["vocab"], H), "norm": nw(),
+         "qkv": [rn((cfg["heads"] + 2 * cfg["kv_heads"]) * D, H) for _ in range(L)],
+         "o": [rn(H, cfg["heads"] * D) for _ in range(L)], "router": [rn(cfg["experts"], H) for _ in range(L)],
+         "gate": [rn(E * I, H) for _ in range(L)], "up": [rn(E * I, H) for _ in range(L)],
+         "down": [rn(E * H, I) for _ in range(L)], "ln1": [nw() for _ in range(L)], "ln2": [nw() for _ in range(L)]}
+    prompt = torch.randint(0, cfg["vocab"], (10,), generator=g)
+    single = Llama4DecodeRunner(w, cfg, max_seq=64)
+    wl, cl = shard_llama4_weights(w, cfg, rank, world)
+    for flags in (0, capi.MUI_FLAG_PDL):
+        single.reset()
+        tp = Llama4DecodeRunner(wl, cl, max_seq=64, flags=flags, comm=comm)
+        tok = int(prompt[0])
+        for step in range(28):
+            a = single.step(tok)
+            b = tp.step(tok)
+            torch.testing.assert_close(b.float(), a.float(), rtol=3e-2, atol=3e-2)
+            tok = int(prompt[step + 1]) if step + 1 < prompt.numel() else int(torch.argmax(a.float()).item())
+
+
 def _case_tp_decode_stack(rank, world, comm):
     from muillm_b200 import capi
     from muillm_b200.decoder_stack import LlamaDecodeStack, shard_llama_weights
@@ -183,3 +223,7 @@ def test_tp_decode_stack_greedy_tokens():
 
 def test_parallel_moe_mlp_fused_all_reduce():
     _run("_case_parallel_moe")
+
+
+def test_tp_llama4_runner_matches_single_gpu():
+    _run("_case_tp_llama4_runner")
