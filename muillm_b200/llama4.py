@@ -67,11 +67,11 @@ def llama4_weights_from_state_dict(sd, cfg, dtype=torch.bfloat16, device="cuda")
     return w
 
 
-def shard_llama4_weights(w, cfg, rank, world):
+def shard_llama4_weights(w, cfg, rank, world, shard_lm_head=False):
     """Tensor-parallel shard of packed Llama-4 weights, partitioned as the reference does
     (muillm/modules/parallelmultilinear.py:340-387, muillm/modules/moe/parallelgateupdownmlpmoe.py): whole query / KV
     heads per rank, o_proj by input columns, every expert's intermediate dimension split across the ranks; embedding,
-    router, norms and lm_head replicated. Returns (weights, per-rank cfg)."""
+    router and norms replicated, the lm_head replicated or split by rows. Returns (weights, per-rank cfg)."""
     Hq, Hkv, D, H = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["hidden"]
     I, E = cfg["expert_intermediate"], cfg["experts"] + 1
     if Hq % world or Hkv % world or I % world:
@@ -90,7 +90,14 @@ def shard_llama4_weights(w, cfg, rank, world):
         out["up"].append(w["up"][l].view(E, I, H)[:, sl].reshape(E * il, H).contiguous())
         out["down"].append(w["down"][l].view(E, H, I)[:, :, sl].reshape(E * H, il).contiguous())
     local = dict(cfg)
-    local.update(heads=hq, kv_heads=hkv, expert_intermediate=il)
+    local.update(heads=hq, kv_heads=hkv, expert_intermediate=il, world=world, rank=rank)
+    if shard_lm_head:
+        # rows of the head per rank and a distributed arg-max (Llama4DecodeRunner._argmax) instead of full logits
+        V = cfg["vocab"]
+        if V % world:
+            raise RuntimeError("the vocabulary must be divisible by the world size to shard the lm_head")
+        out["lm_head"] = w["lm_head"][rank * (V // world): (rank + 1) * (V // world)].contiguous()
+        local.update(lm_head_sharded=True, vocab_offset=rank * (V // world))
     return out, local
 
 
@@ -117,17 +124,12 @@ class Llama4DecodeRunner:
     def reset(self):
         self.pos = 0
 
-    def step(self, token):
-        """One token (python int or 0-dim tensor) in, logits [1, vocab] (model dtype) out; advances the position."""
+    def _layers(self, h, cache_position, pe, pos=None, seq_len_dev=None):
+        """The decoder layers for one token. Host mode: `pos` is the python position (chunked layers attend a view of
+        their chunk). Device mode (`pos` None): the attended length comes from the device int32 `seq_len_dev`, which is
+        what lets a captured step replay; the caches must then not be longer than the attention chunk."""
         c, w, f = self.cfg, self.w, self.flags
         Hq, Hkv, D = c["heads"], c["kv_heads"], c["head_dim"]
-        pos = self.pos
-        if pos >= self.max_seq:
-            raise RuntimeError("the static cache is full")
-        tok = torch.as_tensor([int(token)], dtype=torch.int64, device=self.device)
-        h = w["embed"].index_select(0, tok).view(1, 1, c["hidden"])
-        cache_position = torch.tensor([pos], dtype=torch.int64, device=self.device)
-        pe = self.freqs[pos: pos + 1].unsqueeze(0)   # [1, 1, D/2, 2]
         for l in range(c["layers"]):
             rope = c["use_rope"][l]
             qkv = ops.muillm_linear_forward(None, h, w["qkv"][l], norm_weights=w["ln1"][l], epsilon=c["eps"], flags=f)
@@ -141,14 +143,15 @@ class Llama4DecodeRunner:
                                               qk_norm_eps=c["eps"] if norm else None,
                                               cache_position=cache_position if tune else None,
                                               attn_scale=c["attn_scale"], floor_scale=c["floor_scale"], flags=f)
+            seen = self.max_seq if pos is None else pos + 1
             k_all, v_all = ops.muillm_static_kvcache_update(k, v, self.k_cache[l], self.v_cache[l], cache_position,
-                                                            pos + 1, flags=f)
-            if rope and c["chunk"]:
+                                                            seen, flags=f)
+            if pos is not None and rope and c["chunk"]:
                 # chunked attention: only the rows of the chunk the new token belongs to
                 start = (pos // c["chunk"]) * c["chunk"]
                 k_all, v_all = k_all.narrow(2, start, pos + 1 - start), v_all.narrow(2, start, pos + 1 - start)
             q = q if q.is_contiguous() else q.contiguous()
-            attn = ops.muillm_causal_transformer_decoding_no_mask(q, k_all, v_all, flags=f)
+            attn = ops._flash_decode(q, k_all, v_all, None, flags=f, seq_len_dev=seq_len_dev)
             if self.comm is not None:
                 h = self.comm.parallel_linear(attn, w["o"][l], residual=h, flags=f)
             else:
@@ -163,9 +166,78 @@ class Llama4DecodeRunner:
                 h = ops.muillm_gateupsilumoe_forward(None, 1, c["experts"], w["ln2"][l], c["eps"], w["gate"][l],
                                                      w["up"][l], w["down"][l], h, h, scores.reshape(-1),
                                                      idx.reshape(-1), flags=f)
-        self.pos = pos + 1
+        # logits of this rank's rows of the lm_head (all of them unless the head was sharded)
         return ops.muillm_linear_forward(None, h, w["lm_head"], norm_weights=w["norm"], epsilon=c["eps"],
                                          flags=f).view(1, -1)
+
+    def step(self, token):
+        """One token (python int or 0-dim tensor) in, logits [1, vocab] (model dtype) out; advances the position."""
+        c, w = self.cfg, self.w
+        pos = self.pos
+        if pos >= self.max_seq:
+            raise RuntimeError("the static cache is full")
+        tok = torch.as_tensor([int(token)], dtype=torch.int64, device=self.device)
+        h = w["embed"].index_select(0, tok).view(1, 1, c["hidden"])
+        cache_position = torch.tensor([pos], dtype=torch.int64, device=self.device)
+        pe = self.freqs[pos: pos + 1].unsqueeze(0)   # [1, 1, D/2, 2]
+        logits = self._layers(h, cache_position, pe, pos=pos)
+        self.pos = pos + 1
+        return logits
+
+    # ---- device-resident loop: token, position and attended length live on the GPU, so a step can be captured ----
+    def _argmax(self, logits):
+        """Next token from this rank's logits; with a row-sharded lm_head the ranks exchange their (max, index) pairs
+        through one small fp32 all-reduce (each rank fills only its own slot) and pick the same winner."""
+        lf = logits.float().view(-1)
+        val, idx = torch.max(lf, dim=0)
+        off = int(self.cfg.get("vocab_offset", 0))
+        if self.comm is None or not self.cfg.get("lm_head_sharded", False):
+            return (idx + off).view(1)
+        world, rank = self.cfg["world"], self.cfg["rank"]
+        mine = torch.zeros(world, 2, dtype=torch.float32, device=self.device)
+        mine[rank, 0] = val
+        mine[rank, 1] = (idx + off).float()          # vocabulary indices are exact in fp32 (< 2**24)
+        allp = self.comm.all_reduce_sum(mine)
+        win = torch.argmax(allp[:, 0])                # ties go to the lower rank, i.e. the lower index
+        return allp[win, 1].long().view(1)
+
+    def start_device_loop(self, token, pos):
+        """Puts the decode state on the device: the next step consumes `token` at position `pos`."""
+        if self.cfg["chunk"] and self.max_seq > self.cfg["chunk"]:
+            raise RuntimeError("the device loop needs caches no longer than the attention chunk")
+        self.d_token = torch.tensor([int(token)], dtype=torch.int64, device=self.device)
+        self.d_pos = torch.tensor([int(pos)], dtype=torch.int64, device=self.device)
+        self.d_len = torch.tensor([int(pos) + 1], dtype=torch.int32, device=self.device)
+        self.pos = None
+        self._graph = None
+
+    def step_device(self):
+        """One decode step entirely from device state; leaves the arg-max token as the next input."""
+        c, w = self.cfg, self.w
+        h = w["embed"].index_select(0, self.d_token).view(1, 1, c["hidden"])
+        pe = self.freqs.index_select(0, self.d_pos).unsqueeze(0)
+        logits = self._layers(h, self.d_pos, pe, pos=None, seq_len_dev=self.d_len)
+        self.d_token.copy_(self._argmax(logits))
+        self.d_pos.add_(1)
+        self.d_len.add_(1)
+
+    def capture(self, warmup=2):
+        """Captures step_device as a CUDA graph on a side stream (after `warmup` eager steps there, which also
+        create the per-stream workspaces); replay(n) then runs n steps without host work per launch."""
+        self._stream = torch.cuda.Stream()
+        self._stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self._stream):
+            for _ in range(warmup):
+                self.step_device()
+        self._stream.synchronize()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph, stream=self._stream):
+            self.step_device()
+        return self
+
+    def replay(self, steps=1):
+        for _ in range(steps):
+            self._graph.replay()
 
     def greedy(self, prompt, new_tokens):
         """prompt: 1-D int64 tensor; returns the new_tokens greedy continuation (int64, device)."""

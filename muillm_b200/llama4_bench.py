@@ -1,0 +1,145 @@
+"""Tensor-parallel batch-1 decode of a Llama-4-Scout-17B-16E-architecture model (BASELINE config 5), random-init bf16:
+
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+      -m muillm_b200.llama4_bench --steps 128 --warmup 8 [--layers 48]
+
+48 layers, hidden 5120, 40 query / 8 KV heads, head dim 128, 16 routed experts (top-1 sigmoid) + a shared expert with
+intermediate 8192, chunked attention window 8192, vocabulary 202048; 32-token random prompt, then greedy tokens from a
+captured CUDA graph of Llama4DecodeRunner.step_device (token fed back on the device). Every rank builds only its own
+shard, seeded per tensor, so the full model never exists on one device. Rank 0 prints one JSON line; the time is the
+maximum over ranks of CUDA-event time around the replays.
+
+Bytes a rank streams per token: its rows of QKV and o_proj, the router, the gate/up/down shards of the shared and of
+the one selected expert in every layer, and its rows of the lm_head.
+"""
+import argparse
+import json
+import os
+
+import torch
+
+SCOUT = dict(layers=48, hidden=5120, expert_intermediate=8192, heads=40, kv_heads=8, head_dim=128, vocab=202048,
+             experts=16, top_k=1, eps=1e-5, rope_theta=500000.0, chunk=8192, use_qk_norm=True, temperature_tuning=True,
+             attn_scale=0.1, floor_scale=8192.0)
+PROMPT_LEN = 32
+MAX_SEQ = 1024
+
+
+def local_weights(cfg, rank, world, dtype, dev):
+    """This rank's shard, generated in place (normal(0, 0.02) weights, norm weights 1 + normal(0, 0.01))."""
+    H, D = cfg["hidden"], cfg["head_dim"]
+    hq, hkv, il = cfg["heads"] // world, cfg["kv_heads"] // world, cfg["expert_intermediate"] // world
+    E = cfg["experts"] + 1
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    gr = torch.Generator(device=dev).manual_seed(7)   # replicated tensors: same seed on every rank
+
+    def rn(gen, *shape):
+        return torch.empty(*shape, dtype=dtype, device=dev).normal_(0.0, 0.02, generator=gen)
+
+    def nw():
+        return (1.0 + 0.01 * torch.randn(H, device=dev, generator=gr)).to(dtype)
+
+    L = cfg["layers"]
+    w = {"embed": rn(gr, cfg["vocab"], H), "norm": nw(), "lm_head": rn(g, cfg["vocab"] // world, H),
+         "ln1": [nw() for _ in range(L)], "ln2": [nw() for _ in range(L)],
+         "router": [rn(gr, cfg["experts"], H) for _ in range(L)],
+         "qkv": [rn(g, (hq + 2 * hkv) * D, H) for _ in range(L)], "o": [rn(g, H, hq * D) for _ in range(L)],
+         "gate": [rn(g, E * il, H) for _ in range(L)], "up": [rn(g, E * il, H) for _ in range(L)],
+         "down": [rn(g, E * H, il) for _ in range(L)]}
+    local = dict(cfg)
+    local.update(heads=hq, kv_heads=hkv, expert_intermediate=il, world=world, rank=rank,
+                 lm_head_sharded=world > 1, vocab_offset=rank * (cfg["vocab"] // world))
+    return w, local
+
+
+def bytes_per_token_per_rank(cfg, world):
+    H, D = cfg["hidden"], cfg["head_dim"]
+    hq, hkv, il = cfg["heads"] // world, cfg["kv_heads"] // world, cfg["expert_intermediate"] // world
+    per_layer = (hq + 2 * hkv) * D * H + H * hq * D + cfg["experts"] * H + (1 + cfg["top_k"]) * 3 * il * H + 2 * H
+    return 2 * (cfg["layers"] * per_layer + (cfg["vocab"] // world) * H + H)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=SCOUT["layers"])
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+
+    import torch.distributed as dist
+
+    from . import capi
+    from .comm import MuiCommunicator
+    from .llama4 import Llama4DecodeRunner
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(SCOUT, layers=args.layers)
+    cfg["use_rope"] = [(l + 1) % 4 != 0 for l in range(cfg["layers"])]
+    w, local = local_weights(cfg, rank, world, torch.bfloat16, dev)
+    comm = None
+    if world > 1:
+        comm = MuiCommunicator(rank=rank, world_size=world, key="l4bench" + os.environ.get("MASTER_PORT", "0"),
+                               capacity_elems=1 << 16)
+    run = Llama4DecodeRunner(w, local, max_seq=MAX_SEQ, flags=capi.MUI_FLAG_PDL, comm=comm)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg["vocab"], (PROMPT_LEN,), generator=g).tolist()
+    for t in prompt[:-1]:
+        run.step(t)
+    run.start_device_loop(prompt[-1], pos=PROMPT_LEN - 1)
+    K, W = args.steps, max(3, args.warmup)
+    if args.no_graph:
+        for _ in range(W):
+            run.step_device()
+        step = run.step_device
+        stream = torch.cuda.current_stream()
+    else:
+        run.capture(warmup=W)
+        step = run._graph.replay
+        stream = run._stream
+    barrier()
+    s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        s_ev.record(stream)
+        for _ in range(K):
+            step()
+        e_ev.record(stream)
+    barrier()
+    seconds = s_ev.elapsed_time(e_ev) * 1e-3
+    status = capi.device_status()
+    t = torch.tensor([seconds], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    seconds = float(t.item())
+    if rank == 0:
+        nbytes = bytes_per_token_per_rank(cfg, world)
+        line = {"metric": "bs=1 decode tokens/s/user (Llama-4-Scout-17B-16E arch)", "value": K / seconds,
+                "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": seconds / K * 1e3,
+                "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"Llama-4-Scout-arch decode (BASELINE config 5), {cfg['layers']} layers, bs=1, "
+                                       f"{PROMPT_LEN}-token prompt, static caches of {MAX_SEQ}",
+                           "parallelism": f"tp{world}", "launch": "eager launches" if args.no_graph else
+                           "CUDA graph of one Python-chained step, programmatic dependent launch"},
+                "hbm_fraction": {"bytes_per_step_per_rank": nbytes, "achieved_gbs": nbytes * K / seconds / 1e9,
+                                 "of_nominal_8tbs": nbytes * K / seconds / 1e9 / 8000.0},
+                "reference_published_tok_s": {"4x MI300X": 190.0}, "device_status": status}
+        print(json.dumps(line), flush=True)
+    barrier()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -44,3 +44,31 @@ def test_prompt_logits_close_to_hf_fp32():
     for t in d["prompt"][0].tolist():
         logits = run.step(t)
     torch.testing.assert_close(logits.float().cpu(), torch.from_numpy(d["prompt_logits"]), rtol=2e-2, atol=2e-2)
+
+
+def test_captured_device_loop_equals_host_loop():
+    """Token, position and attended length kept on the device and the step replayed as a CUDA graph produce the
+    tokens of the host-driven loop (same model with one chunk spanning the cache, which the device loop requires)."""
+    d = np.load(os.path.join(GOLD, "hf_llama4_model.npz"))
+    sd = {k[3:]: torch.from_numpy(d[k]) for k in d.files if k.startswith("sd/")}
+    cfg = dict(CFG, chunk=64)
+    w = llama4_weights_from_state_dict(sd, cfg, dtype=torch.float16)
+    prompt = torch.from_numpy(d["prompt"])[0]
+    want = Llama4DecodeRunner(w, cfg, max_seq=64, flags=capi.MUI_FLAG_PDL).greedy(prompt, 16).cpu().tolist()
+    run = Llama4DecodeRunner(w, cfg, max_seq=64, flags=capi.MUI_FLAG_PDL)
+    logits = None
+    for t in prompt.tolist():
+        logits = run.step(t)
+    got = [int(torch.argmax(logits.float()).item())]
+    run.start_device_loop(got[0], pos=prompt.numel())
+    run.step_device()
+    got.append(int(run.d_token.item()))
+    run.capture(warmup=2)           # two more eager steps on the capture stream
+    torch.cuda.synchronize()
+    for i in range(12):
+        run.replay(1)
+        torch.cuda.synchronize()
+        got.append(int(run.d_token.item()))
+    # tokens 2 and 3 were produced (and consumed) by the warm-up steps inside capture()
+    assert got[:2] == want[:2] and got[2:] == want[4:16], f"{got} vs {want}"
+    assert capi.device_status() == 0
