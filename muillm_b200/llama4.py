@@ -199,7 +199,7 @@ class Llama4DecodeRunner:
         mine[rank, 1] = (idx + off).float()          # vocabulary indices are exact in fp32 (< 2**24)
         allp = self.comm.all_reduce_sum(mine)
         win = torch.argmax(allp[:, 0])                # ties go to the lower rank, i.e. the lower index
-        return allp[win, 1].long().view(1)
+        return allp[:, 1].index_select(0, win.view(1)).long()   # no host round trip: the step stays capturable
 
     def start_device_loop(self, token, pos):
         """Puts the decode state on the device: the next step consumes `token` at position `pos`."""
