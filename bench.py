@@ -120,31 +120,20 @@ def make_gpu_weights(cfg, dtype, device, seed):
 
 
 def time_dominant_kernel(w, cfg, flags):
-    """Average duration of the fused gate/up+SiLU GEMV at the model's shape, CUDA events around 4 passes over the
-    32 layers' distinct weights (7.5 GB per pass, so every launch streams from HBM)."""
+    """Average duration of the fused gate/up+SiLU GEMV at the model's (per-rank) shape: a CUDA graph of 4 passes over
+    the 32 layers' distinct weights (7.5 GB per pass on one GPU, so every launch streams from HBM), launched
+    back to back with dependent launch as in the decode step, CUDA events around 3 replays."""
     import torch
 
+    from benchmarks.timing import time_graph
     from muillm_b200 import ops
 
-    H = cfg["hidden"]
+    H, I, L = cfg["hidden"], cfg["intermediate"], cfg["layers"]
     x = torch.randn(1, H, device=w["embed"].device, dtype=w["embed"].dtype)
-    L = cfg["layers"]
-
-    def one_pass():
-        for l in range(L):
-            ops.gateup_silu(x, w["gate"][l], w["up"][l], norm_weights=w["ln2"][l], epsilon=cfg["eps"], flags=flags)
-
-    one_pass()
-    torch.cuda.synchronize()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    passes = 4
-    s.record()
-    for _ in range(passes):
-        one_pass()
-    e.record()
-    torch.cuda.synchronize()
-    seconds = s.elapsed_time(e) * 1e-3 / (passes * L)
-    I = cfg["intermediate"]
+    t = torch.empty(1, I, device=x.device, dtype=x.dtype)
+    fns = [(lambda l=l: ops.gateup_silu(x, w["gate"][l], w["up"][l], norm_weights=w["ln2"][l], epsilon=cfg["eps"],
+                                        flags=flags, out=t)) for l in range(L)]
+    seconds = time_graph(fns, 4 * L, replays=3, warm_replays=1)
     algo_bytes = 2 * I * H * 2 + H * 2 * 2 + I * 2  # gate+up weights, x + norm weight, t out
     return seconds, algo_bytes
 
@@ -214,6 +203,7 @@ def run_gpu(args):
     import torch
     import torch.distributed as dist
 
+    from benchmarks.parity import tp_parity
     from muillm_b200 import capi
     from muillm_b200.comm import MuiCommunicator
     from muillm_b200.decoder_stack import LlamaDecodeStack, shard_llama_weights
@@ -233,16 +223,23 @@ def run_gpu(args):
     w = make_gpu_weights(cfg, dtype, dev, seed=0)
     comm = None
     local_cfg = cfg
+    full_w = None
     if world > 1:
         # tensor parallelism: every rank builds the same seeded weights and keeps its shard
         comm = MuiCommunicator(rank=rank, world_size=world, key="bench" + os.environ.get("MASTER_PORT", "0"),
                                capacity_elems=1 << 16)
+        full_w = w if rank == 0 else None  # rank 0 keeps the un-sharded weights until the parity check is done
         w, local_cfg = shard_llama_weights(w, cfg, rank, world)
         torch.cuda.empty_cache()
-    stack = LlamaDecodeStack(w, local_cfg, max_seq=MAX_SEQ, batch=1, max_new_tokens=PROMPT_LEN + W + K + 8,
+    stack = LlamaDecodeStack(w, local_cfg, max_seq=MAX_SEQ, batch=1, max_new_tokens=max(PROMPT_LEN + W + K, 48) + 8,
                              flags=flags, comm=comm)
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg["vocab"], (1, PROMPT_LEN), generator=g)
+    parity = None
+    if world > 1:
+        parity = tp_parity(stack, full_w, cfg, prompt, rank, world, dev, flags)
+        full_w = None
+        torch.cuda.empty_cache()
 
     def barrier():
         if world > 1:
@@ -338,7 +335,8 @@ def run_gpu(args):
                                                f"(I={local_cfg['intermediate']}, H=4096)",
                      "achieved": achieved, "peak": peak, "peak_source": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": GATEUP_DRAM_TRAFFIC_BYTES if world == 1 else None,
-                     "algorithmic_bytes": k_bytes, "avg_launch_us": k_seconds * 1e6},
+                     "algorithmic_bytes": k_bytes, "avg_launch_us": k_seconds * 1e6,
+                     "timing": "CUDA graph of back-to-back launches over the layers' distinct weights"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
         "gpu_launches": K * stack.launches_per_step,
         "clocks": clocks.summary(),
@@ -346,13 +344,15 @@ def run_gpu(args):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if parity is not None:
+        line["parity"] = parity
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at this shape, from the ncu capture
-# summarised in profiles/gemv_gateup_llama8b.md (mean of the two captured launches)
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at the single-GPU shape (14336 x 4096 x 2, fp16),
+# mean of the two launches of an `ncu --set full` capture of this kernel
 GATEUP_DRAM_TRAFFIC_BYTES = 238540416
 
 

@@ -1,4 +1,4 @@
-"""Per-kernel HBM throughput of the decode path: `python -m muillm_b200.kernel_bench [--json out.json]`.
+"""Per-kernel HBM throughput of the decode path: `python -m benchmarks.kernel_bench [--json out.json]`.
 
 Every case runs one kernel over several distinct weight sets (in total larger than the 126 MB L2, so each launch
 streams from HBM), as a CUDA graph of back-to-back launches with programmatic dependent launch, timed with CUDA
@@ -14,7 +14,7 @@ import json
 
 import torch
 
-from . import capi, ops
+from muillm_b200 import capi, ops
 
 NOMINAL_GBS = 8000.0
 

@@ -1,7 +1,7 @@
 """Tensor-parallel batch-1 decode of a Llama-4-Scout-17B-16E-architecture model (BASELINE config 5), random-init bf16:
 
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-      -m muillm_b200.llama4_bench --steps 128 --warmup 8 [--layers 48]
+      -m benchmarks.llama4_bench --steps 128 --warmup 8 [--layers 48]
 
 48 layers, hidden 5120, 40 query / 8 KV heads, head dim 128, 16 routed experts (top-1 sigmoid) + a shared expert with
 intermediate 8192, chunked attention window 8192, vocabulary 202048; 32-token random prompt, then greedy tokens from a
@@ -69,9 +69,9 @@ def main():
 
     import torch.distributed as dist
 
-    from . import capi
-    from .comm import MuiCommunicator
-    from .llama4 import Llama4DecodeRunner
+    from muillm_b200 import capi
+    from muillm_b200.comm import MuiCommunicator
+    from muillm_b200.llama4 import Llama4DecodeRunner
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -1,10 +1,10 @@
 """Small fixed workloads for profiling one kernel at a time (e.g. under `ncu -k regex:<kernel> -c 2`).
 
-  python -m muillm_b200.profile_cases gateup     # fused gate/up+SiLU GEMV, Llama-3-8B MLP shape, 4 distinct layers
-  python -m muillm_b200.profile_cases linear     # QKV-shaped fused-norm GEMV (6144 x 4096), 8 distinct matrices
-  python -m muillm_b200.profile_cases attention  # fused RoPE + cache write + attention, 32 q / 8 kv heads, S = 2048
-  python -m muillm_b200.profile_cases w8         # int8 (per-row scale) gate/up GEMV, same MLP shape
-  python -m muillm_b200.profile_cases attention_short  # one-CTA-per-KV-head tensor-core attention, S = 256
+  python -m benchmarks.profile_cases gateup     # fused gate/up+SiLU GEMV, Llama-3-8B MLP shape, 4 distinct layers
+  python -m benchmarks.profile_cases linear     # QKV-shaped fused-norm GEMV (6144 x 4096), 8 distinct matrices
+  python -m benchmarks.profile_cases attention  # fused RoPE + cache write + attention, 32 q / 8 kv heads, S = 2048
+  python -m benchmarks.profile_cases w8         # int8 (per-row scale) gate/up GEMV, same MLP shape
+  python -m benchmarks.profile_cases attention_short  # one-CTA-per-KV-head tensor-core attention, S = 256
 
 Each case keeps well under 2 GB on the device, uses inputs larger than L2 in total so that weights come from
 HBM, launches the kernel a handful of times and synchronises.
@@ -13,7 +13,7 @@ import sys
 
 import torch
 
-from . import capi, ops
+from muillm_b200 import capi, ops
 
 
 def _gateup(dtype=torch.float16, w8=False):

@@ -49,8 +49,6 @@ typedef enum { MUI_W8_SYM_ROW = 0, MUI_W8_GROUP_MIN = 1 } mui_w8_format_t;
 #define MUI_FLAG_PDL 1u          /* launch with programmatic stream serialization (overlaps the weight prefetch
                                     of this kernel with the tail of the previous kernel on the stream) */
 #define MUI_FLAG_FORCE_GENERIC 2u /* use the plain-load kernel even where the bulk-copy pipeline applies */
-#define MUI_FLAG_MEGAKERNEL 8u    /* decode stack only: run the whole step as ONE persistent kernel (one CTA per SM,
-                                    continuous weight stream, grid barriers between operations); batch 1 only */
 #define MUI_FLAG_FORCE_PIPELINE 4u /* fail with MUI_ERR_UNSUPPORTED instead of falling back to the plain-load kernel */
 #define MUI_FLAG_SHORT_CONTEXT 16u  /* mui_rope_flash_decode / decode stack: at most a few hundred tokens are attended;
                                       one CTA per KV head stages the whole K/V history in shared memory (up to 384 rows
@@ -77,13 +75,18 @@ MUI_API mui_status_t mui_device_status(unsigned* code, int clear);
 
 /* ---- launch tracing (the reference has none built in; its examples wrap generate() in torch.profiler,
  * examples/llama3_8b.py:61-67) ------------------------------------------------------------------------------
- * After mui_trace_enable(stream, buf, n) the calling thread's next n launches of the GEMV, gate/up, flash-decoding
- * and RoPE kernels each fill one record of four uint64 %globaltimer values (ns) {first CTA start, ~last CTA end, first CTA
- * past its wait for the previous kernel, ~last CTA with its activations staged; the last two only for the
- * pipeline GEMV} in the device buffer `buf` (n * 32 bytes, filled with 0xFF by this call on `stream`). Records are bound at launch
- * (or capture) time, so a captured graph keeps writing its records on every replay. mui_trace_enable(…, NULL, 0)
- * switches tracing off. mui_trace_count returns how many records were handed out and their kernel tags
- * (1 linear GEMV, 2 gate/up GEMV, 3 flash decoding, 4 RoPE). */
+ * After mui_trace_enable(stream, buf, n) the calling thread's next n launches of the GEMV, gate/up, flash-decoding,
+ * RoPE and all-reduce kernels each fill one record of eight uint64 words in the device buffer `buf` (n * 64 bytes,
+ * filled with 0xFF by this call on `stream`). Words are %globaltimer values in ns; "~" marks words stored
+ * complemented (so that one atomicMin serves minima and maxima alike):
+ *   [0] first CTA start          [1] ~last CTA end
+ *   [2] first CTA past its wait for the previous kernel      [3] ~last CTA with its activations staged
+ *   [4] ~last CTA done pushing its partial sums to the peers  [5] ~last CTA that has seen every peer's partials
+ *   [6] first CTA that has seen every peer's partials         [7] unused
+ * [2]-[3] are written by the pipeline GEMV only, [4]-[6] by tensor-parallel launches only. Records are bound at
+ * launch (or capture) time, so a captured graph keeps writing its records on every replay. mui_trace_enable(…, NULL,
+ * 0) switches tracing off. mui_trace_count returns how many records were handed out and their kernel tags
+ * (1 linear GEMV, 2 gate/up GEMV, 3 flash decoding, 4 RoPE, 5 stand-alone all-reduce). */
 MUI_API mui_status_t mui_trace_enable(void* stream, void* device_buffer, int max_records);
 MUI_API int mui_trace_count(int* tags_out, int max_tags);
 
@@ -197,7 +200,9 @@ MUI_API mui_status_t mui_flash_decode(void* stream, mui_dtype_t dtype, int B, in
  * (thread-block cluster of 8 CTAs per (KV head, sequence), partials merged through distributed shared memory: no
  * global scratch). qkv is the packed output of the QKV projection [B, (Hq + 2*Hkv) * D] (q rows, then k, then v);
  * position_ids [B] (int64, RoPE position per sequence), cache_position [1] (int64, row written) and seq_len_dev
- * (int32) live on the device; out is [B, Hq * D]. D == 128, Hq / Hkv <= 8. Replaces the pair
+ * (int32) live on the device; out is [B, Hq * D]. D == 128, Hq / Hkv <= 8. cos/sin tables hold at least max_seq
+ * rows; a cache_position or position id outside [0, max_seq) records MUI_DEV_BAD_LENGTH in the device status word
+ * and the launch writes nothing (a replayed graph cannot run past the cache). Replaces the pair
  * muillm_rope_forward_static_cache + flash_decode_no_mask on the decode path (csrc/rope/rotary.cu:603-756,
  * csrc/attention/flash_decoding.cu:288-305; MuiLLMParallelAttention::forward chains them,
  * csrc/modules/parallel_attention_module.cpp:45-90). */
@@ -469,11 +474,6 @@ MUI_API mui_status_t mui_llama_stack_set_tokens(mui_llama_stack_t* stack, void* 
 MUI_API mui_status_t mui_llama_stack_set_attention_mask(mui_llama_stack_t* stack, const void* mask_dev);
 MUI_API mui_status_t mui_llama_stack_set_position_ids(mui_llama_stack_t* stack, void* stream,
                                                       const int64_t* position_ids, int on_device);
-/* Phase timeline of the whole-step kernel (MUI_FLAG_MEGAKERNEL): CTA 0 writes {tag, %globaltimer ns} pairs of
- * uint64 at every phase boundary of every layer (0 layer start, 1/4/6/9/12 after a grid barrier, 2/7/10/13 after
- * staging the activations, 3/8/11/14 after a projection, 5 after attention) into device_buffer (16 bytes per
- * record) on the steps launched afterwards. NULL switches it off. */
-MUI_API mui_status_t mui_llama_stack_op_trace(mui_llama_stack_t* stack, void* device_buffer, int max_records);
 MUI_API mui_status_t mui_llama_stack_step(mui_llama_stack_t* stack, void* stream, unsigned flags);
 /* Captures one step on `stream` (must not be the default stream) into a graph; replay launches it `steps` times. */
 MUI_API mui_status_t mui_llama_stack_capture(mui_llama_stack_t* stack, void* stream, unsigned flags);

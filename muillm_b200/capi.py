@@ -33,7 +33,6 @@ MUI_W8_GROUP_MIN = 1
 MUI_FLAG_PDL = 1
 MUI_FLAG_FORCE_GENERIC = 2
 MUI_FLAG_FORCE_PIPELINE = 4
-MUI_FLAG_MEGAKERNEL = 8
 MUI_FLAG_SHORT_CONTEXT = 16
 
 
@@ -220,7 +219,6 @@ PROTOTYPES = {
     "mui_llama_stack_set_attention_mask": (c_int, [c_void_p, c_void_p]),
     "mui_llama_stack_set_position_ids": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
     "mui_llama_stack_set_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
-    "mui_llama_stack_op_trace": (c_int, [c_void_p, c_void_p, c_int]),
     "mui_llama_stack_step": (c_int, [c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_capture": (c_int, [c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_replay": (c_int, [c_void_p, c_void_p, c_int]),

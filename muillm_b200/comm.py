@@ -42,14 +42,16 @@ class MuiCommunicator:
         capi.check(self.lib.mui_comm_info(self._h, None, None, ctypes.byref(cap)))
         return cap.value
 
-    def all_reduce_sum(self, tensor, flags=0):
-        """Returns the sum over ranks of `tensor` (fp16, bf16 or fp32), same shape (csrc/module.cpp muillm_all_reduce_sum)."""
+    def all_reduce_sum(self, tensor, flags=0, out=None):
+        """Returns the sum over ranks of `tensor` (fp16, bf16 or fp32), same shape (csrc/module.cpp
+        muillm_all_reduce_sum); written into `out` when given."""
         _check_input(tensor, "tensor")
         if tensor.dtype == torch.float32:
             code = capi.MUI_COMM_F32
         else:
             code = _dtype_code(tensor)
-        out = torch.empty_like(tensor)
+        if out is None:
+            out = torch.empty_like(tensor)
         capi.check(self.lib.mui_comm_all_reduce_sum(self._h, _stream(), code, _ptr(tensor), _ptr(out), tensor.numel(),
                                                     flags))
         return out
@@ -62,14 +64,14 @@ class MuiCommunicator:
                                                tensor.numel() * tensor.element_size(), flags))
         return out
 
-    def parallel_linear(self, x, weights, mul_bias=None, add_bias=None, residual=None, flags=0):
+    def parallel_linear(self, x, weights, mul_bias=None, add_bias=None, residual=None, flags=0, out=None):
         """K-sharded linear + fused all-reduce: x [..., K_local], weights [N, K_local] -> [..., N] on every rank;
         add_bias / residual are applied once (rank 0), as muillm/modules/parallellinear.py:464-467 does."""
         for t, n in ((x, "x"), (weights, "weights"), (mul_bias, "mul_bias"), (add_bias, "add_bias"),
                      (residual, "residual")):
             _check_input(t, n)
         N, K = weights.shape
-        y = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+        y = out if out is not None else torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
         capi.check(self.lib.mui_parallel_linear_forward(
             self._h, _stream(), _dtype_code(x), _rows(x), N, K, None, 0.0, _ptr(weights), _ptr(mul_bias),
             _ptr(add_bias), _ptr(residual), _ptr(x), _ptr(y), flags))

@@ -34,7 +34,7 @@ static thread_local int tls_trace_tags[4096];
 unsigned long long* mui_trace_next_record(int kernel_tag) {
   if (tls_trace_buf == nullptr || tls_trace_next >= tls_trace_cap) return nullptr;
   tls_trace_tags[tls_trace_next] = kernel_tag;
-  return tls_trace_buf + 4 * (size_t)(tls_trace_next++);
+  return tls_trace_buf + 8 * (size_t)(tls_trace_next++);
 }
 
 // ---- L2 prefetch hint (per host thread) ----
@@ -162,7 +162,7 @@ mui_status_t mui_trace_enable(void* stream, void* device_buffer, int max_records
     return MUI_OK;
   }
   MUI_REQUIRE(max_records <= 4096, MUI_ERR_INVALID_ARG, "at most 4096 trace records");
-  MUI_CUDA_CHECK(cudaMemsetAsync(device_buffer, 0xFF, (size_t)max_records * 32, (cudaStream_t)stream));
+  MUI_CUDA_CHECK(cudaMemsetAsync(device_buffer, 0xFF, (size_t)max_records * 64, (cudaStream_t)stream));
   tls_trace_buf = reinterpret_cast<unsigned long long*>(device_buffer);
   tls_trace_cap = max_records;
   tls_trace_next = 0;

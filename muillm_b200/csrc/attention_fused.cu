@@ -104,6 +104,12 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_cluster_kernel(c
   const long long pos_id = __ldcg(a.position_ids + b);
   const long long cache_pos = __ldcg(a.cache_position);
   const int S = min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
+  // Past the end of the cache or of the rotary tables ([max_seq, D]): record it and leave, writing nothing. The
+  // values are the same for every CTA of the cluster, so all of them leave before the first cluster barrier.
+  if (cache_pos < 0 || cache_pos >= a.max_seq || pos_id < 0 || pos_id >= a.max_seq) {
+    if (tid == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(cache_pos));
+    return;
+  }
   const int cached = S - 1;
   const T* row = reinterpret_cast<const T*>(a.qkv) + (size_t)b * (a.Hq + 2 * a.Hkv) * FA_D;
   uint4 q_raw[GP];
@@ -352,7 +358,7 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(
   const long long pos_id = __ldcg(a.position_ids + b);
   const long long cache_pos = __ldcg(a.cache_position);
   const int S = min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
-  if (S > RA_ROWS) {
+  if (S > RA_ROWS || cache_pos < 0 || cache_pos >= a.max_seq || pos_id < 0 || pos_id >= a.max_seq) {
     if (tid == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(S));
     return;
   }

@@ -70,19 +70,33 @@ template <> struct ArIO<float> {
 
 // Stand-alone all-reduce: dst = sum over ranks of src (count elements), same protocol as the fused GEMV tail.
 template <typename T>
-__global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(const CommDev c, const T* src, T* dst, long long count) {
+__global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(const CommDev c, const T* src, T* dst, long long count,
+                                                               unsigned long long* trace) {
+  trace_start(trace);
   pdl_wait_prior_grid();
   pdl_launch_dependents();
   const int tid = threadIdx.x;
+  if (tid == 0) trace_mark(trace, 2, false);
   const unsigned long long seq = comm_begin(c);
   const long long e0 = count * blockIdx.x / gridDim.x, e1 = count * (blockIdx.x + 1) / gridDim.x;
   for (long long i = e0 + tid; i < e1; i += AR_THREADS) comm_push(c, seq, (size_t)i, ArIO<T>::ld(src + i));
   __syncthreads();  // every thread has read the counter before this CTA announces itself
   unsigned ticket = 0;
-  if (tid == 0) ticket = comm_cta_arrive(c);
+  if (tid == 0) {
+    trace_mark(trace, 4, true);
+    ticket = comm_cta_arrive(c);
+  }
   for (long long i = e0 + tid; i < e1; i += AR_THREADS) {
     float v;
     if (comm_reduce_elem(c, seq, (size_t)i, &v)) ArIO<T>::st(dst + i, v);
+  }
+  if (trace != nullptr) {
+    __syncthreads();
+    if (tid == 0) {
+      trace_mark(trace, 5, true);
+      trace_mark(trace, 6, false);
+      trace_end(trace);
+    }
   }
   if (tid == 0) comm_cta_finish(c, seq, ticket, gridDim.x);
 }
@@ -371,15 +385,16 @@ mui_status_t mui_comm_all_reduce_sum(mui_comm_t* c, void* stream, int dtype, con
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
   const dim3 grid(ar_grid((long long)count)), block(AR_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
+  unsigned long long* trace = mui_trace_next_record(5);
   if (dtype == MUI_F16) {
     MUI_CUDA_CHECK(mui_launch(allreduce_kernel<__half>, grid, block, 0, st, pdl, d, (const __half*)src, (__half*)dst,
-                              (long long)count));
+                              (long long)count, trace));
   } else if (dtype == MUI_BF16) {
     MUI_CUDA_CHECK(mui_launch(allreduce_kernel<__nv_bfloat16>, grid, block, 0, st, pdl, d, (const __nv_bfloat16*)src,
-                              (__nv_bfloat16*)dst, (long long)count));
+                              (__nv_bfloat16*)dst, (long long)count, trace));
   } else {
     MUI_CUDA_CHECK(mui_launch(allreduce_kernel<float>, grid, block, 0, st, pdl, d, (const float*)src, (float*)dst,
-                              (long long)count));
+                              (long long)count, trace));
   }
   return MUI_OK;
 }

@@ -13,6 +13,11 @@
 //      MUI_DEV_TIMEOUT_PEER with the late rank and leaves the output element untouched;
 //   3. the last CTA of the grid to finish advances the sequence counter (read from device memory at kernel
 //      start, so a launch captured in a CUDA graph replays correctly).
+// The in-cell sequence number is the low 32 bits of the 64-bit counter and is compared for equality with the
+// expected one. It wraps after 2^32 collectives (about a day of decoding at 50 k collectives per second); a stale
+// cell could only be mistaken for a fresh one if it had not been rewritten for exactly 2^32 collectives, i.e. if no
+// collective of the same parity had covered its index in all that time. Decode loops repeat their message sizes
+// every step, so every cell in use is rewritten every other collective.
 // Generation g is overwritten for collective s+2 only after this rank's kernel of collective s+1 completed, in
 // which it received every peer's s+1 cells, and a peer writes those only from a kernel that started after its
 // own kernel of collective s (which read generation g) completed: no barrier is needed.
@@ -47,20 +52,31 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned 
   return v;
 }
 
+// A peer wait that ran out is sticky: once the status word of this translation unit carries MUI_DEV_TIMEOUT_PEER,
+// every later wait (other elements, other ranks, later launches until the host clears the word) gives up at once,
+// so a collective with a missing peer ends after ONE wait limit whatever its element count.
+__device__ __forceinline__ bool comm_peer_timed_out() {
+  return (*reinterpret_cast<volatile unsigned*>(&g_mui_dev_status) >> 24) == MUI_DEV_TIMEOUT_PEER;
+}
+
 // Polls rank r's cell of element idx until it carries `seq`; returns false (status recorded) on timeout.
 __device__ __forceinline__ bool comm_take(const CommDev& c, unsigned long long seq, int r, size_t idx, float* out) {
   const unsigned long long* cell = c.peer_cells[c.rank] + ((size_t)(seq & 1ull) * c.world + r) * c.capacity + idx;
   const unsigned want = static_cast<unsigned>(seq & 0xffffffffull);
   unsigned long long v = ld_relaxed_sys_u64(cell);
   if (static_cast<unsigned>(v >> 32) != want) {
+    if (comm_peer_timed_out()) return false;
     const uint64_t t0 = global_timer_ns();
     unsigned spins = 0;
     while (true) {
       v = ld_relaxed_sys_u64(cell);
       if (static_cast<unsigned>(v >> 32) == want) break;
-      if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > MUI_COMM_WAIT_NS) {
-        mui_dev_set_status(MUI_DEV_TIMEOUT_PEER, static_cast<unsigned>(r));
-        return false;
+      if ((++spins & 0xff) == 0) {
+        if (comm_peer_timed_out()) return false;
+        if (global_timer_ns() - t0 > MUI_COMM_WAIT_NS) {
+          mui_dev_set_status(MUI_DEV_TIMEOUT_PEER, static_cast<unsigned>(r));
+          return false;
+        }
       }
     }
   }

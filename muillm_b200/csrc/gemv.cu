@@ -374,6 +374,9 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
     }
   } else {
     // ------------------------------ consumer warps ------------------------------
+    GemvNormPre norm_pre;
+    if (a.moe_mode != GEMV_MOE_SEGMENTS) gemv_prefetch_norm<T, NB>(a, tid, norm_pre);
+    else norm_pre.have = false;
     pdl_wait_prior_grid();
     if (tid == 0) trace_mark(a.trace, 2, false);
     const unsigned long long comm_seq = (MODE == 0 && a.use_comm) ? comm_begin(a.comm) : 0ull;
@@ -407,7 +410,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
     if (a.moe_mode == GEMV_MOE_SEGMENTS)
       gemv_stage_x_plain<T>(a, a.slots, x_s, x_pitch, tid);
     else
-      gemv_stage_x<T, NB>(a, a.B, x_s, x_pitch, red, tid);
+      gemv_stage_x<T, NB>(a, a.B, x_s, x_pitch, red, tid, &norm_pre);
     if (tid == 0) trace_mark(a.trace, 3, true);
 
     float d[4] = {0.f, 0.f, 0.f, 0.f};

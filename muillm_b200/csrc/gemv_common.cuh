@@ -70,9 +70,31 @@ __device__ __forceinline__ float gemv_slot_score(const GemvArgs& a, int slot) {
 // element stride between staged rows (>= Kp).
 // NBX = number of activation rows staged (batch rows, or MoE segments).
 // ---------------------------------------------------------------------------------------------
+// Norm weights of the one-row fast path of gemv_stage_x, loaded into registers BEFORE the wait for the previous
+// kernel (they are constants, unlike the activations): one L2 round trip less between two dependent kernels.
+struct GemvNormPre {
+  uint4 w[4];
+  bool have;
+};
+template <typename T, int NBX>
+__device__ __forceinline__ bool gemv_stage_fast_path(const GemvArgs& a) {
+  const int K = a.K;
+  return NBX == 1 && ((K & 7) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) && a.norm_w != nullptr &&
+         ((reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0) && K <= GEMV_CONSUMER_THREADS * 8 * 4 && a.B >= 1;
+}
+template <typename T, int NBX>
+__device__ __forceinline__ void gemv_prefetch_norm(const GemvArgs& a, int tid, GemvNormPre& pre) {
+  pre.have = gemv_stage_fast_path<T, NBX>(a);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int k = (j * GEMV_CONSUMER_THREADS + tid) * 8;
+    pre.w[j] = (pre.have && k < a.K) ? ld_cached16(reinterpret_cast<const T*>(a.norm_w) + k) : make_uint4(0, 0, 0, 0);
+  }
+}
+
 template <typename T, int NBX>
 __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present, T* x_s, int pitch, float* red,
-                                             int tid) {
+                                             int tid, const GemvNormPre* pre = nullptr) {
   const int K = a.K, Kp = a.Kp;
   const T* __restrict__ x = reinterpret_cast<const T*>(a.x);
   const T* __restrict__ nw = reinterpret_cast<const T*>(a.norm_w);
@@ -114,7 +136,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
       if (k < K) {
         float f[8], wv[8];
         unpack8<T>(keep[j], f);
-        unpack8<T>(ld_cached16(nw + k), wv);
+        unpack8<T>((pre != nullptr && pre->have) ? pre->w[j] : ld_cached16(nw + k), wv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = Elt<T>::to_f32(Elt<T>::from_f32(f[i] * r)) * wv[i];
         *reinterpret_cast<uint4*>(x_s + k) = pack8<T>(f);
@@ -370,12 +392,22 @@ __device__ __forceinline__ void gemv_comm_tail(const GemvArgs& a, unsigned long 
   T* y = reinterpret_cast<T*>(a.y);
   const int total = num_rows * a.B;
   unsigned ticket = 0;
-  if (tid == 0) ticket = comm_cta_arrive(a.comm);  // result is looked at after the polls below
+  if (tid == 0) {
+    trace_mark(a.trace, 4, true);
+    ticket = comm_cta_arrive(a.comm);  // result is looked at after the polls below
+  }
   for (int i = tid; i < total; i += nthreads) {
     const int b = i / num_rows, n = row_of(i - b * num_rows);
     const size_t o = (size_t)b * a.N + n;
     float v;
     if (comm_reduce_elem(a.comm, seq, o, &v)) y[o] = Elt<T>::from_f32(v);
+  }
+  if (a.trace != nullptr) {  // tracing only: the stamp below stands for the whole CTA
+    named_bar_sync(bar_id, nthreads);
+    if (tid == 0) {
+      trace_mark(a.trace, 5, true);
+      trace_mark(a.trace, 6, false);
+    }
   }
   if (tid == 0) comm_cta_finish(a.comm, seq, ticket, gridDim.x);
 }

@@ -52,16 +52,27 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) rope_kernel(const RopeArgs a)
     head -= a.Hq;
     in = reinterpret_cast<const T*>(a.k_in) + b * a.ks.batch + head * a.ks.head + t * a.ks.tok;
     if (a.k_out) out_plain = reinterpret_cast<T*>(a.k_out) + (((size_t)b * a.Hkv + head) * a.T + t) * D;
-    if (a.k_cache)
-      out_cache = reinterpret_cast<T*>(a.k_cache) +
-                  (((size_t)b * a.Hkv + head) * a.max_T + static_cast<size_t>(__ldcg(a.cache_position + t))) * D;
+    if (a.k_cache) {
+      // a cache row outside the cache (a replayed graph that ran past the end) is recorded and not written
+      const long long cp = __ldcg(a.cache_position + t);
+      if (cp < 0 || cp >= a.max_T) {
+        if (lane == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(cp));
+        if (!out_plain) return;
+      } else {
+        out_cache = reinterpret_cast<T*>(a.k_cache) + (((size_t)b * a.Hkv + head) * a.max_T + (size_t)cp) * D;
+      }
+    }
     rotate = a.apply_rope != 0;
   } else {
     head -= a.Hq + a.Hkv;
     if (a.v_in == nullptr || a.v_cache == nullptr) return;
     in = reinterpret_cast<const T*>(a.v_in) + b * a.vs.batch + head * a.vs.head + t * a.vs.tok;
-    out_cache = reinterpret_cast<T*>(a.v_cache) +
-                (((size_t)b * a.Hkv + head) * a.max_T + static_cast<size_t>(__ldcg(a.cache_position + t))) * D;
+    const long long cp = __ldcg(a.cache_position + t);
+    if (cp < 0 || cp >= a.max_T) {
+      if (lane == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(cp));
+      return;
+    }
+    out_cache = reinterpret_cast<T*>(a.v_cache) + (((size_t)b * a.Hkv + head) * a.max_T + (size_t)cp) * D;
     rotate = false;
   }
 

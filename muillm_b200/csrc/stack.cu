@@ -9,7 +9,7 @@
 // csrc/modules/parallel_decoder_stack.cpp:22-45, MuiLLMParallelDecoder::forward,
 // csrc/modules/parallel_decoder_module.cpp:22-62); single-GPU decode goes through Python per layer there
 // (muillm/modules/decoder/decoder.py:95-165).
-#include "mega.cuh"
+#include "gemv_common.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -56,16 +56,6 @@ struct mui_llama_stack {
   mui_comm_t* comm;  // tensor-parallel communicator (null on a single GPU)
   const void* attn_mask;  // additive [B, max_seq] of the model dtype (left-padded batches), or null
   CommDev comm_dev;
-  // whole-step kernel
-  bool mega_ok;
-  MegaLayer* mega_layers;  // device
-  float* attn_part;
-  float* mega_argmax_val;
-  int* mega_argmax_idx;
-  unsigned long long* mega_bar;
-  int mega_x_elems;
-  unsigned long long* op_trace;
-  int op_trace_cap;
   std::vector<WeightRef> order;  // weight matrices in execution order: per layer qkv, o, gate, up, down; then lm_head
   size_t prefetch_window;
 };
@@ -75,8 +65,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct ScratchLayout {
-  size_t state, seq_len, h, qkv, q_rot, attn, t, logits, fd_ws, fd_ws_bytes, argmax_work, mega_layers, attn_part,
-      mega_argmax, mega_bar, total;
+  size_t state, seq_len, h, qkv, q_rot, attn, t, logits, fd_ws, fd_ws_bytes, argmax_work, total;
 };
 
 ScratchLayout scratch_layout(const mui_llama_config_t& c) {
@@ -99,10 +88,6 @@ ScratchLayout scratch_layout(const mui_llama_config_t& c) {
   l.fd_ws_bytes = mui_flash_decode_workspace_bytes(c.batch, c.heads, c.kv_heads, c.head_dim, c.max_seq);
   l.fd_ws = take(l.fd_ws_bytes);
   l.argmax_work = take(mui_argmax_work_bytes(c.batch));
-  l.mega_layers = take((size_t)c.layers * sizeof(MegaLayer));
-  l.attn_part = take((size_t)c.heads * MG_MAX_SPLITS * (c.head_dim + 2) * sizeof(float));
-  l.mega_argmax = take(1024 * 8);
-  l.mega_bar = take(64);
   l.total = off;
   return l;
 }
@@ -118,47 +103,6 @@ mui_status_t validate_cfg(const mui_llama_config_t* c) {
   MUI_REQUIRE(c->batch >= 1 && c->batch <= 8, MUI_ERR_UNSUPPORTED, "batch %d outside 1..8", c->batch);
   MUI_REQUIRE(c->max_seq >= 1, MUI_ERR_INVALID_ARG, "max_seq must be positive");
   return MUI_OK;
-}
-
-mui_status_t launch_mega(mui_llama_stack* s, cudaStream_t stream, unsigned flags) {
-  const mui_llama_config_t& c = s->cfg;
-  const MuiDeviceInfo* dev = mui_current_device_info();
-  if (!dev) return MUI_ERR_CUDA;
-  MegaArgs a;
-  memset(&a, 0, sizeof(a));
-  a.layers = s->mega_layers;
-  a.embed = s->embed;
-  a.final_norm = s->final_norm;
-  a.lm_head = s->lm_head;
-  a.cos_t = s->cos_t;
-  a.sin_t = s->sin_t;
-  a.state = s->state;
-  a.seq_len32 = s->seq_len32;
-  a.out_tokens = s->out_tokens;
-  a.out_capacity = s->out_capacity;
-  a.h = s->h;
-  a.qkv_out = s->qkv_out;
-  a.t = s->t;
-  a.logits = s->logits;
-  a.attn_part = s->attn_part;
-  a.argmax_val = s->mega_argmax_val;
-  a.argmax_idx = s->mega_argmax_idx;
-  a.bar = s->mega_bar;
-  a.L = c.layers;
-  a.H = c.hidden;
-  a.I = c.intermediate;
-  a.Hq = c.heads;
-  a.Hkv = c.kv_heads;
-  a.V = c.vocab;
-  a.max_seq = c.max_seq;
-  a.embed_vocab = c.embed_vocab > 0 ? c.embed_vocab : c.vocab;
-  a.x_elems = s->mega_x_elems;
-  a.eps = c.rms_eps;
-  a.scale_log2 = c.attn_scale * 1.4426950408889634f;
-  a.op_trace = s->op_trace;
-  a.op_trace_cap = s->op_trace_cap;
-  const int grid = std::min(dev->sm_count, 1024);
-  return mui_launch_mega_step(stream, c.dtype, a, c.heads / c.kv_heads, grid, (flags & MUI_FLAG_PDL) ? 1 : 0);
 }
 
 // Decode state from caller-owned device tensors (mui_llama_stack_forward_hidden): tokens in cache = cache position,
@@ -239,12 +183,6 @@ void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t win
 
 mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags) {
   const mui_llama_config_t& c = s->cfg;
-  if (flags & MUI_FLAG_MEGAKERNEL) {
-    MUI_REQUIRE(s->mega_ok && s->comm == nullptr && s->attn_mask == nullptr, MUI_ERR_UNSUPPORTED,
-                "the whole-step kernel covers batch 1, head_dim 128, at most 4 query heads per KV head, sizes that "
-                "are multiples of 16, no attention mask and no tensor parallelism");
-    return launch_mega(s, stream, flags);
-  }
   const int B = c.batch, H = c.hidden, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim;
   const int qkv_n = (Hq + 2 * Hkv) * D;
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
@@ -399,8 +337,6 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
   s->graph_flags = 0;
   s->comm = nullptr;
   s->attn_mask = nullptr;
-  s->op_trace = nullptr;
-  s->op_trace_cap = 0;
   {
     const int qkv_rows = (cfg->heads + 2 * cfg->kv_heads) * cfg->head_dim;
     const int od = cfg->heads * cfg->head_dim;
@@ -416,44 +352,7 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
     const long mb = (e && *e) ? atol(e) : 24;  // measured on the 8B decode step: 8-48 MB within 1 %, none -2 %, 96 MB -3 %
     s->prefetch_window = mb > 0 ? (size_t)mb << 20 : 0;
   }
-  // whole-step kernel: per-layer pointer table on the device, scratch, eligibility
-  s->mega_layers = reinterpret_cast<MegaLayer*>(base + lay.mega_layers);
-  s->attn_part = reinterpret_cast<float*>(base + lay.attn_part);
-  s->mega_argmax_val = reinterpret_cast<float*>(base + lay.mega_argmax);
-  s->mega_argmax_idx = reinterpret_cast<int*>(base + lay.mega_argmax + 4096);
-  s->mega_bar = reinterpret_cast<unsigned long long*>(base + lay.mega_bar);
-  const int G = cfg->heads / cfg->kv_heads;
-  s->mega_x_elems = (mui_mega_x_elems(cfg->hidden, cfg->intermediate, cfg->heads, cfg->kv_heads) + 7) & ~7;
-  const MuiDeviceInfo* dev = mui_current_device_info();
-  s->mega_ok = dev != nullptr && cfg->batch == 1 && cfg->head_dim == 128 && G <= 4 && (cfg->hidden % 16) == 0 &&
-               (cfg->intermediate % 16) == 0 && cfg->kv_heads <= dev->sm_count &&
-               mui_mega_smem_bytes(s->mega_x_elems, cfg->heads) <= (size_t)227 * 1024;
-  if (s->mega_ok) {
-    const void* all[] = {w->embed, w->final_norm, w->lm_head};
-    for (const void* p : all) s->mega_ok = s->mega_ok && ((reinterpret_cast<uintptr_t>(p) & 15) == 0);
-    std::vector<MegaLayer> host(cfg->layers);
-    for (int l = 0; l < cfg->layers; ++l) {
-      host[l] = MegaLayer{w->qkv[l], w->o[l], w->gate[l], w->up[l], w->down[l], w->ln1[l], w->ln2[l], w->k_cache[l],
-                          w->v_cache[l]};
-      const void* ptrs[] = {w->qkv[l], w->o[l], w->gate[l], w->up[l], w->down[l], w->ln1[l], w->ln2[l], w->k_cache[l],
-                            w->v_cache[l]};
-      for (const void* p : ptrs) s->mega_ok = s->mega_ok && ((reinterpret_cast<uintptr_t>(p) & 15) == 0);
-    }
-    cudaError_t e = cudaMemcpy(s->mega_layers, host.data(), host.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) {
-      mui_set_error("copying the layer table failed: %s", cudaGetErrorString(e));
-      delete s;
-      return MUI_ERR_CUDA;
-    }
-  }
   *out = s;
-  return MUI_OK;
-}
-
-mui_status_t mui_llama_stack_op_trace(mui_llama_stack_t* s, void* device_buffer, int max_records) {
-  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
-  s->op_trace = reinterpret_cast<unsigned long long*>(device_buffer);
-  s->op_trace_cap = device_buffer ? max_records : 0;
   return MUI_OK;
 }
 
@@ -507,7 +406,6 @@ mui_status_t mui_llama_stack_reset(mui_llama_stack_t* s, void* stream, int posit
   // flash-decoding and arg-max arrival counters start at zero
   MUI_CUDA_CHECK(cudaMemsetAsync(s->fd_ws, 0, 4096, cs));
   MUI_CUDA_CHECK(cudaMemsetAsync(s->argmax_work, 0, 64, cs));
-  MUI_CUDA_CHECK(cudaMemsetAsync(s->mega_bar, 0, 64, cs));
   s->out_tokens = reinterpret_cast<long long*>(out_tokens_dev);
   s->out_capacity = out_tokens_dev ? out_capacity : 0;
   // the caller's token buffer bounds how far this run decodes; without one assume the whole cache
@@ -548,6 +446,10 @@ mui_status_t mui_llama_stack_set_attention_mask(mui_llama_stack_t* s, const void
 
 mui_status_t mui_llama_stack_step(mui_llama_stack_t* s, void* stream, unsigned flags) {
   MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  // a step writes cache row host_pos and reads row host_pos of the rotary tables: both end at max_seq
+  MUI_REQUIRE(s->host_pos < s->cfg.max_seq, MUI_ERR_UNSUPPORTED,
+              "the KV cache is full: %d tokens cached, max_seq %d (reset the stack or build it with a longer cache)",
+              s->host_pos, s->cfg.max_seq);
   s->capturing = false;
   const mui_status_t st = launch_step(s, (cudaStream_t)stream, flags);
   if (st == MUI_OK) s->host_pos += 1;
@@ -590,6 +492,9 @@ mui_status_t mui_llama_stack_capture(mui_llama_stack_t* s, void* stream, unsigne
 
 mui_status_t mui_llama_stack_replay(mui_llama_stack_t* s, void* stream, int steps) {
   MUI_REQUIRE(s != nullptr && s->graph_exec != nullptr, MUI_ERR_INVALID_ARG, "no captured graph (call capture first)");
+  MUI_REQUIRE(steps >= 0 && s->host_pos + steps <= s->cfg.max_seq, MUI_ERR_UNSUPPORTED,
+              "%d more steps do not fit the KV cache: %d tokens cached, max_seq %d", steps, s->host_pos,
+              s->cfg.max_seq);
   MUI_REQUIRE(!s->graph_short || s->host_pos + steps <= 384, MUI_ERR_UNSUPPORTED,
               "the captured step uses the short-context attention kernel (384 tokens); %d tokens are cached and %d "
               "more steps were asked for: reset with a larger token buffer and capture again", s->host_pos, steps);
@@ -608,7 +513,6 @@ mui_status_t mui_llama_stack_forward_hidden(mui_llama_stack_t* s, void* stream, 
   MUI_REQUIRE(position_ids_dev && cache_position_dev && h_out, MUI_ERR_INVALID_ARG, "null pointer");
   MUI_REQUIRE(seen_tokens >= 1 && seen_tokens <= s->cfg.max_seq, MUI_ERR_INVALID_ARG,
               "seen_tokens %d outside 1..%d", seen_tokens, s->cfg.max_seq);
-  MUI_REQUIRE(!(flags & MUI_FLAG_MEGAKERNEL), MUI_ERR_UNSUPPORTED, "the whole-step kernel includes the lm_head");
   cudaStream_t cs = (cudaStream_t)stream;
   const int B = s->cfg.batch;
   const size_t hbytes = (size_t)B * s->cfg.hidden * 2;

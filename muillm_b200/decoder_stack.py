@@ -179,10 +179,7 @@ class LlamaDecodeStack:
     @property
     def launches_per_step(self):
         """Kernels one decode step launches: embedding, per layer {QKV, attention (one fused launch at head dim 128,
-        else RoPE + flash decoding), o_proj, gate/up, down}, lm_head, arg-max; a single launch for the whole-step
-        kernel."""
-        if self.flags & capi.MUI_FLAG_MEGAKERNEL:
-            return 1
+        else RoPE + flash decoding), o_proj, gate/up, down}, lm_head, arg-max."""
         fused = self.cfg["head_dim"] == 128 and not (self.flags & capi.MUI_FLAG_FORCE_GENERIC)
         return 3 + (5 if fused else 6) * self.cfg["layers"]
 
@@ -215,11 +212,13 @@ class LlamaDecodeStack:
                     self.step()
         return self.out_tokens[T - 1: T - 1 + new_tokens].transpose(0, 1).contiguous()
 
-    def greedy_ragged(self, prompts, new_tokens, use_graph=True, pad_token=0):
+    def greedy_ragged(self, prompts, new_tokens, use_graph=True, pad_token=0, timing=None):
         """Greedy decoding of `batch` prompts of different lengths (list of 1-D int64 tensors), left-padded to the
         longest one as the HF tokenizer hands them to the reference's generation loop: the padding rows of a sequence
         are masked out of its attention for good and its RoPE positions start at its first real token
-        (position_ids = cumsum(attention_mask) - 1). Returns int64 [batch, new_tokens] (device)."""
+        (position_ids = cumsum(attention_mask) - 1). Returns int64 [batch, new_tokens] (device). With a dict as
+        `timing` (graph path), the CUDA-event time of the graph replays is left in timing["replay_seconds"] together
+        with timing["replay_steps"]; `timing["warm_steps"]` of the new tokens run as untimed replays first."""
         assert len(prompts) == self.batch
         lens = [int(p.numel()) for p in prompts]
         T = max(lens)
@@ -247,8 +246,21 @@ class LlamaDecodeStack:
                     s.wait_stream(torch.cuda.current_stream())
                     with torch.cuda.stream(s):
                         self.capture()
-                        self.replay(remaining)
+                        warm = min(int(timing.get("warm_steps", 0)), remaining) if timing is not None else 0
+                        if warm:
+                            self.replay(warm)
+                        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        if timing is not None and callable(timing.get("barrier")):
+                            s.synchronize()
+                            timing["barrier"]()
+                        ev0.record(s)
+                        self.replay(remaining - warm)
+                        ev1.record(s)
                     torch.cuda.current_stream().wait_stream(s)
+                    if timing is not None:
+                        torch.cuda.synchronize()
+                        timing["replay_seconds"] = ev0.elapsed_time(ev1) * 1e-3
+                        timing["replay_steps"] = remaining - warm
                 else:
                     for _ in range(remaining):
                         self.step()

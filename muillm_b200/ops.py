@@ -81,14 +81,15 @@ def muillm_gateupsilu_forward(engine, norm_weights, epsilon, gate_weights, up_we
     return y
 
 
-def gateup_silu(x, gate_weights, up_weights, norm_weights=None, epsilon=0.0, flags=0):
+def gateup_silu(x, gate_weights, up_weights, norm_weights=None, epsilon=0.0, flags=0, out=None):
     """t = silu(G xn) * (U xn) only (the first kernel of the MLP)."""
     for t, n in ((x, "x"), (gate_weights, "gate_weights"), (up_weights, "up_weights"),
                  (norm_weights, "norm_weights")):
         _check_input(t, n)
     I, H = gate_weights.shape
     B = _rows(x)
-    out = torch.empty(x.shape[:-1] + (I,), dtype=x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (I,), dtype=x.dtype, device=x.device)
     capi.check(capi.lib().mui_gateup_silu_forward(
         _stream(), _dtype_code(x), B, I, H, _ptr(norm_weights), float(epsilon), _ptr(gate_weights),
         _ptr(up_weights), _ptr(x), _ptr(out), flags))

@@ -18,7 +18,7 @@ def _worker(rank, key, q, done):
         from muillm_b200 import capi, ops
         from muillm_b200.comm import MuiCommunicator
 
-        comm = MuiCommunicator(rank=rank, world_size=2, key=key, capacity_elems=1024, timeout_s=60.0)
+        comm = MuiCommunicator(rank=rank, world_size=2, key=key, capacity_elems=1 << 18, timeout_s=60.0)
         if rank == 0:
             x = torch.ones(8, device="cuda", dtype=torch.float32)
             torch.cuda.synchronize()
@@ -27,11 +27,20 @@ def _worker(rank, key, q, done):
             torch.cuda.synchronize()
             waited = time.perf_counter() - t0
             status = capi.device_status(clear=True)
+            # a large count (several elements per thread, 296 CTAs): the first wait that runs out makes every later
+            # one give up at once, so the whole kernel still ends after about one wait limit
+            big = torch.ones(200000, device="cuda", dtype=torch.float32)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            comm.all_reduce_sum(big)
+            torch.cuda.synchronize()
+            waited_big = time.perf_counter() - t0
+            status_big = capi.device_status(clear=True)
             # the context is intact: another kernel of the library runs and is correct
             y = ops.muillm_rmsnorm_forward(torch.ones(16, device="cuda", dtype=torch.float16),
                                            torch.full((2, 16), 3.0, device="cuda", dtype=torch.float16), 0.0)
             torch.cuda.synchronize()
-            q.put(("ok", status, waited, capi.device_status(), y.float().mean().item()))
+            q.put(("ok", status, waited, capi.device_status(), y.float().mean().item(), waited_big, status_big))
         done.wait(90)  # rank 1 keeps its segment mapped until rank 0 has finished
         comm.close()
     except Exception as e:  # pragma: no cover
@@ -52,8 +61,9 @@ def test_all_reduce_reports_a_peer_that_never_arrives():
         for p in procs:
             p.join(timeout=60)
     assert res[0] == "ok", res
-    _, status, waited, status_after, mean = res
+    _, status, waited, status_after, mean, waited_big, status_big = res
     assert status >> 24 == 3, f"expected MUI_DEV_TIMEOUT_PEER, got {status:#x}"
     assert status & 0xFFFFFF == 1, "the late rank is rank 1"
     assert 1.5 < waited < 10.0, f"the bounded wait took {waited:.2f} s"
+    assert status_big >> 24 == 3 and 1.5 < waited_big < 10.0, f"large count: {waited_big:.2f} s, status {status_big:#x}"
     assert status_after == 0 and abs(mean - 1.0) < 1e-2

@@ -9,6 +9,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from oracle import decode_oracle as oracle  # noqa: E402
+from parity_utils import check_greedy_tokens  # noqa: E402
 
 
 def _world():
@@ -192,16 +193,9 @@ def _case_tp_decode_stack(rank, world, comm):
     wl = {k: ([t.cuda() for t in v] if isinstance(v, list) else v.cuda()) for k, v in wl.items()}
     for flags, graph in ((0, False), (capi.MUI_FLAG_PDL, True)):
         stack = LlamaDecodeStack(wl, cl, max_seq=64, batch=1, flags=flags, comm=comm)
-        got = stack.greedy(prompt, 32, use_graph=graph).cpu()
-        same = (got[0] == want[0]).long().cumprod(0).sum().item()
-        if same < 32:
-            # the sharded fp32 sums round differently from the single-device order; tokens may part ways only at a
-            # near-tie of the oracle's two best logits (teacher-forced on the common prefix), anything else is a bug
-            o = oracle.LlamaOracle(w, cfg, max_T=64)
-            logits = o.forward(torch.cat((prompt, want[:, :same]), dim=1))[0]
-            margin = (logits[want[0, same]] - logits[got[0, same]]).item()
-            assert 0 <= margin < 1e-2, (f"flags={flags} graph={graph}: tensor-parallel tokens diverge after {same} "
-                                        f"with logit margin {margin}: {got.tolist()}")
+        # all 32 positions are checked: identical tokens, or (teacher-forced on the oracle's sequence) a flip only
+        # where the oracle's two best logits are a near-tie — the sharded fp32 sums round in another order
+        check_greedy_tokens(stack, w, cfg, prompt, want, 64, graph, label=f"tp{world} flags={flags} graph={graph}")
         del stack
 
 

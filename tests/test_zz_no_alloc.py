@@ -14,6 +14,7 @@ import pytest
 import torch
 
 from muillm_b200 import capi, ops
+from oracle import decode_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -43,6 +44,9 @@ def test_static_scratch_matches_workspace_entry_point_twice(dtype):
         got = _static_scratch_decode(q, k, v)
         torch.cuda.synchronize()
         torch.testing.assert_close(got.float(), want.float(), rtol=1e-2, atol=1e-3)
+        # and against the CPU oracle, so that the two entry points cannot be wrong together
+        ref = oracle.decode_attention(q.cpu(), k.cpu(), v.cpu())
+        torch.testing.assert_close(got.float().cpu(), ref.float(), rtol=1e-2, atol=1e-3)
     assert capi.device_status() == 0
 
 
