@@ -237,7 +237,8 @@ def run_gpu(args):
     prompt = torch.randint(0, cfg["vocab"], (1, PROMPT_LEN), generator=g)
     parity = None
     if world > 1:
-        parity = tp_parity(stack, full_w, cfg, prompt, rank, world, dev, flags)
+        parity = tp_parity(stack, lambda: LlamaDecodeStack(full_w, cfg, max_seq=256, batch=1, max_new_tokens=64,
+                                                           flags=flags), prompt, rank, dev)
         full_w = None
         torch.cuda.empty_cache()
 

@@ -147,7 +147,8 @@ def main():
     pcfg = dict(LLAMA70B, layers=args.parity_layers)
     wl, lcfg, full = build_weights(pcfg, rank, world, dtype, dev, keep_full=(rank == 0))
     stack = LlamaDecodeStack(wl, lcfg, max_seq=256, batch=1, max_new_tokens=64, flags=flags, comm=comm)
-    par = tp_parity(stack, full, pcfg, prompt, rank, world, dev, flags)
+    par = tp_parity(stack, lambda: LlamaDecodeStack(full, pcfg, max_seq=256, batch=1, max_new_tokens=64, flags=flags),
+                    prompt, rank, dev)
     par.update(case="parity", gpus=world, layers=args.parity_layers, width="hidden 8192, 64q/8kv, intermediate 28672")
     emit(par)
     del stack, wl, full

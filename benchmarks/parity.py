@@ -1,21 +1,20 @@
 """Parity check that the multi-GPU benchmarks run inside their own processes before they time anything."""
 
 
-def tp_parity(stack, full_weights, cfg, prompt, rank, world, dev, flags, n_tokens=32):
+def tp_parity(stack, make_ref, prompt, rank, dev, n_tokens=32):
     """Parity of the sharded stack inside the bench process: the first `n_tokens` greedy tokens of the tensor-parallel
-    stack against the same tokens of an un-sharded decode stack built on rank 0 from the same seeded weights, then
+    stack against the same tokens of an un-sharded decode stack (`make_ref()`, called on rank 0 only, builds it from
+    the same seeded weights), then
     both fed the un-sharded run's sequence token by token: every position's arg-max must agree, or the un-sharded
     logits must hold the two candidates within 1e-2 (the sharded fp32 sums round in another order)."""
     import torch
     import torch.distributed as dist
 
-    from muillm_b200.decoder_stack import LlamaDecodeStack
-
     T = prompt.shape[1]
     ref_tokens = torch.zeros(1, n_tokens, dtype=torch.int64, device=dev)
     ref = None
     if rank == 0:
-        ref = LlamaDecodeStack(full_weights, cfg, max_seq=256, batch=1, max_new_tokens=T + n_tokens + 8, flags=flags)
+        ref = make_ref()
         ref_tokens.copy_(ref.greedy(prompt, n_tokens, use_graph=True))
     dist.broadcast(ref_tokens, 0)
     got = stack.greedy(prompt, n_tokens, use_graph=True)

@@ -212,6 +212,26 @@ MUI_API mui_status_t mui_rope_flash_decode(void* stream, mui_dtype_t dtype, int 
                                            const int32_t* seq_len_dev, float scale, void* k_cache, void* v_cache,
                                            void* out, unsigned flags);
 
+/* The same fused launch for a Llama-4 attention layer: instead of the rotate-half RoPE, q and the new k go through
+ * the Llama-4 prologue — interleaved-pair rotation by freqs[position] ([max_pos, D/2, 2] fp32 (cos, sin); use_rope),
+ * L2 norm over the head dim (use_qk_norm, norm_eps), and for q the temperature scale
+ * log1p(floor((cache_position + 1) / floor_scale)) * attn_scale + 1 (temperature_tuning) — each stage rounded to the
+ * 16-bit type exactly like mui_llama4_qk_prologue; then the new row is written and the token attends. With chunk > 0
+ * the layer's caches [B, Hkv, cache_rows, D] are a ring indexed by cache_position % chunk and the token attends the
+ * rows of its own chunk, rows 0 .. cache_position % chunk (chunked attention; cache_rows >= min(chunk, longest
+ * sequence)); with chunk == 0 the cache is plain and rows 0 .. cache_position are attended. cache_position [1] is the
+ * absolute position of the new token. D == 128, Hq / Hkv <= 8. One launch where the reference's
+ * MuiLLMParallelLlama4Attention::forward chains rope, QK norm, temperature tuning, the hybrid chunked cache update and
+ * flash decoding (csrc/modules/parallel_llama4_attention_module.cpp:66-147,
+ * csrc/modules/hybrid_chunked_kvcache.cpp:23-77). */
+MUI_API mui_status_t mui_llama4_rope_flash_decode(void* stream, mui_dtype_t dtype, int B, int Hq, int Hkv, int D,
+                                                  int cache_rows, int max_pos, const void* qkv, const float* freqs,
+                                                  const int64_t* position_ids, const int64_t* cache_position,
+                                                  int use_rope, int use_qk_norm, float norm_eps,
+                                                  int temperature_tuning, float attn_scale, float floor_scale,
+                                                  int chunk, float scale, void* k_cache, void* v_cache, void* out,
+                                                  unsigned flags);
+
 /* Flash decoding for callers that may not allocate device memory. No counterpart in the reference (there,
  * torch allocates the partial buffers on every call, csrc/attention/flash_decoding.cu:154-158). Meant for hosts
  * that pass this library nothing but input and output buffers because all device memory is already carved up by
@@ -301,6 +321,16 @@ MUI_API mui_status_t mui_add_tokens_check_finished(void* stream, int B, int T, c
  * Replaces muillm_topk_sigmoid_forward (csrc/topk/topk.cu:34-93). */
 MUI_API mui_status_t mui_topk_sigmoid_forward(void* stream, mui_dtype_t dtype, int rows, int M, int k,
                                               const void* logits, void* values, int64_t* indices, unsigned flags);
+/* Router of one token in one launch: logits[e] = router_weights[e, :] . rmsnorm(x) (E x H weights, fused norm as in
+ * mui_linear_forward, each logit rounded to the 16-bit type), then the top k of them with their sigmoid, as
+ * mui_topk_sigmoid_forward gives. logits_scratch: E floats; counter: one zero-initialised uint32 that every call
+ * leaves at zero. E <= 1024. Replaces the router GEMV + muillm_topk_sigmoid_forward pair of
+ * MuiLLMParallelGateUpDownMLPMoE::forward (csrc/modules/parallel_gateupmoe_module.cpp:45-77). */
+MUI_API mui_status_t mui_router_topk_sigmoid_forward(void* stream, mui_dtype_t dtype, int E, int H, int k,
+                                                     const void* norm_weights, float epsilon,
+                                                     const void* router_weights, const void* x, float* logits_scratch,
+                                                     unsigned int* counter, void* values, int64_t* indices,
+                                                     unsigned flags);
 
 /* ---- (a7) MoE MLP for one token -------------------------------------------------------------------
  * Computed experts = the num_shared shared ones (score 1) followed by the top_k routed ones named by
@@ -446,6 +476,54 @@ MUI_API size_t mui_llama_stack_scratch_bytes(const mui_llama_config_t* cfg);
 MUI_API mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_llama_weights_t* weights,
                                             void* scratch, size_t scratch_bytes, mui_llama_stack_t** out);
 MUI_API mui_status_t mui_llama_stack_destroy(mui_llama_stack_t* stack);
+/* The same decode stack for a Llama-4 text model, batch 1: per layer {fused-norm QKV GEMV, the fused Llama-4
+ * attention launch (mui_llama4_rope_flash_decode; layers with use_rope[l] != 0 are chunked-attention layers with rope
+ * and, if use_qk_norm, the QK L2 norm, the others attend everything and get the temperature scale if
+ * temperature_tuning), o_proj + residual, router + top-k sigmoid, gate/up + SiLU of the shared and the selected
+ * experts, expert down projections summed + residual}: six launches per layer, where the reference's
+ * MuiLLMParallelLlama4DecoderStack chains about a dozen (csrc/modules/parallel_llama4_decoder_stack.cpp:18-60,
+ * parallel_llama4_decoder_module.cpp:25-66). Rope layers keep ring caches of min(max_seq, chunk) rows, the others
+ * plain caches of max_seq rows (the hybrid chunked cache, csrc/modules/hybrid_chunked_kvcache.cpp:23-77). Expert
+ * weights are packed shared-first: gate/up [(num_shared + num_experts) * expert_intermediate, hidden], down
+ * [(num_shared + num_experts) * hidden, expert_intermediate]. Head dims other than 128 run the prologue, the cache
+ * write and flash decoding as separate launches. The handle is a mui_llama_stack_t: reset, set_tokens, step,
+ * capture, replay, logits, set_comm (expert intermediate, heads and lm_head rows sharded; router replicated) and
+ * destroy are the functions below and above. */
+typedef struct mui_llama4_config {
+  mui_dtype_t dtype;
+  int layers, hidden, expert_intermediate, heads, kv_heads, head_dim, vocab;
+  int max_seq;             /* longest sequence: rows of the full-attention caches and of the rotary table */
+  int chunk;               /* attention chunk of the rope layers; 0 = they attend everything too */
+  int num_experts, top_k, num_shared;
+  float rms_eps;
+  float softmax_scale;     /* normally 1/sqrt(head_dim) */
+  int use_qk_norm, temperature_tuning;
+  float attn_scale, floor_scale;
+  int embed_vocab, vocab_offset; /* tensor parallelism, as in mui_llama_config_t */
+} mui_llama4_config_t;
+
+typedef struct mui_llama4_weights {
+  const void* embed;
+  const void* final_norm;
+  const void* lm_head;
+  const float* freqs;           /* [max_seq, head_dim/2, 2] fp32 (cos, sin) of the interleaved rotation */
+  const int* use_rope;          /* host array [layers] */
+  const void* const* qkv;
+  const void* const* o;
+  const void* const* router;    /* per layer [num_experts, hidden] */
+  const void* const* gate;
+  const void* const* up;
+  const void* const* down;
+  const void* const* ln1;
+  const void* const* ln2;
+  void* const* k_cache;         /* per layer [1, kv_heads, rows, head_dim], rows = mui_llama4_stack_cache_rows() */
+  void* const* v_cache;
+} mui_llama4_weights_t;
+
+MUI_API int mui_llama4_stack_cache_rows(const mui_llama4_config_t* cfg, int use_rope);
+MUI_API size_t mui_llama4_stack_scratch_bytes(const mui_llama4_config_t* cfg);
+MUI_API mui_status_t mui_llama4_stack_create(const mui_llama4_config_t* cfg, const mui_llama4_weights_t* weights,
+                                             void* scratch, size_t scratch_bytes, mui_llama_stack_t** out);
 /* Tensor-parallel decode: with a communicator of world > 1 attached, the weights are this rank's shards — QKV and
  * gate/up by output rows (whole heads per rank), o_proj and down by input columns with the all-reduce fused into
  * their GEMV (residual on rank 0), lm_head by rows with the arg-max finished by exchanging each rank's best

@@ -76,6 +76,31 @@ class LlamaWeights(Structure):
     ]
 
 
+class Llama4Config(Structure):
+    _fields_ = [
+        ("dtype", c_int),
+        ("layers", c_int), ("hidden", c_int), ("expert_intermediate", c_int), ("heads", c_int), ("kv_heads", c_int),
+        ("head_dim", c_int), ("vocab", c_int),
+        ("max_seq", c_int), ("chunk", c_int),
+        ("num_experts", c_int), ("top_k", c_int), ("num_shared", c_int),
+        ("rms_eps", c_float), ("softmax_scale", c_float),
+        ("use_qk_norm", c_int), ("temperature_tuning", c_int),
+        ("attn_scale", c_float), ("floor_scale", c_float),
+        ("embed_vocab", c_int), ("vocab_offset", c_int),
+    ]
+
+
+class Llama4Weights(Structure):
+    _fields_ = [
+        ("embed", c_void_p), ("final_norm", c_void_p), ("lm_head", c_void_p),
+        ("freqs", c_void_p), ("use_rope", POINTER(c_int)),
+        ("qkv", POINTER(c_void_p)), ("o", POINTER(c_void_p)), ("router", POINTER(c_void_p)),
+        ("gate", POINTER(c_void_p)), ("up", POINTER(c_void_p)), ("down", POINTER(c_void_p)),
+        ("ln1", POINTER(c_void_p)), ("ln2", POINTER(c_void_p)), ("k_cache", POINTER(c_void_p)),
+        ("v_cache", POINTER(c_void_p)),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/muillm_b200.h declares appears here
 PROTOTYPES = {
     "mui_status_string": (c_char_p, [c_int]),
@@ -214,6 +239,16 @@ PROTOTYPES = {
     "mui_llama_stack_create": (
         c_int, [POINTER(LlamaConfig), POINTER(LlamaWeights), c_void_p, c_size_t, POINTER(c_void_p)]),
     "mui_llama_stack_destroy": (c_int, [c_void_p]),
+    "mui_llama4_stack_cache_rows": (c_int, [POINTER(Llama4Config), c_int]),
+    "mui_llama4_stack_scratch_bytes": (c_size_t, [POINTER(Llama4Config)]),
+    "mui_llama4_stack_create": (
+        c_int, [POINTER(Llama4Config), POINTER(Llama4Weights), c_void_p, c_size_t, POINTER(c_void_p)]),
+    "mui_llama4_rope_flash_decode": (
+        c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_uint]),
+    "mui_router_topk_sigmoid_forward": (
+        c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_void_p, c_void_p, c_uint]),
     "mui_llama_stack_set_comm": (c_int, [c_void_p, c_void_p]),
     "mui_llama_stack_reset": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), c_void_p, c_int]),
     "mui_llama_stack_set_attention_mask": (c_int, [c_void_p, c_void_p]),

@@ -39,7 +39,51 @@ struct FaArgs {
   float scale_log2;
   int B, Hq, Hkv, max_seq, G;
   unsigned long long* trace;
+  // Llama-4 prologue (l4 != 0) instead of the rotate-half rope: interleaved-pair rotation from an fp32 table, L2
+  // norm of q and k over the head dim, temperature scale of q — any subset (FA_L4_* bits), each stage rounded to the
+  // 16-bit type like the stand-alone prologue kernel. With chunk > 0 the layer's cache is a ring of `max_seq` rows
+  // indexed by position % chunk and the token attends the rows of its own chunk only.
+  const float* freqs;  // [max_pos, D/2, 2] (cos, sin)
+  int max_pos;         // rows of the rotary table
+  int l4, chunk;
+  float eps, attn_scale, floor_scale;
 };
+
+constexpr int FA_L4_ON = 1, FA_L4_ROPE = 2, FA_L4_NORM = 4, FA_L4_TEMP = 8;
+
+// Llama-4 prologue on the 8 consecutive head-dim elements a lane holds (4 interleaved pairs); the 16 lanes of a
+// half-warp hold one 128-element row, so the L2 norm sums over lane bits 0-3. `temp` applies to queries only.
+template <typename T>
+__device__ __forceinline__ void fa_l4_prologue8(float (&x)[8], const float2 (&fr)[4], int l4, float eps, bool is_q,
+                                                float temp) {
+  if (l4 & FA_L4_ROPE) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float re = x[2 * j], im = x[2 * j + 1];
+      const float r = re * fr[j].x - im * fr[j].y;
+      const float i = re * fr[j].y + im * fr[j].x;
+      x[2 * j] = Elt<T>::to_f32(Elt<T>::from_f32(r));
+      x[2 * j + 1] = Elt<T>::to_f32(Elt<T>::from_f32(i));
+    }
+  }
+  if (l4 & FA_L4_NORM) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ss += x[2 * j] * x[2 * j] + x[2 * j + 1] * x[2 * j + 1];
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) ss += __shfl_xor_sync(MUI_FULL_MASK, ss, o);
+    const float r = rsqrtf(ss / static_cast<float>(FA_D) + eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = Elt<T>::to_f32(Elt<T>::from_f32(x[i] * r));
+  }
+  if ((l4 & FA_L4_TEMP) && is_q) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = Elt<T>::to_f32(Elt<T>::from_f32(x[i] * temp));
+  }
+}
+__device__ __forceinline__ float fa_l4_temperature(long long pos, float attn_scale, float floor_scale) {
+  return log1pf(floorf((static_cast<float>(pos) + 1.0f) / floor_scale)) * attn_scale + 1.0f;
+}
 
 __device__ __forceinline__ unsigned cluster_ctarank() {
   unsigned r;
@@ -102,12 +146,15 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_cluster_kernel(c
 
   // first round of loads: state and the new token's q, k, v (independent of each other)
   const long long pos_id = __ldcg(a.position_ids + b);
-  const long long cache_pos = __ldcg(a.cache_position);
-  const int S = min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
-  // Past the end of the cache or of the rotary tables ([max_seq, D]): record it and leave, writing nothing. The
-  // values are the same for every CTA of the cluster, so all of them leave before the first cluster barrier.
-  if (cache_pos < 0 || cache_pos >= a.max_seq || pos_id < 0 || pos_id >= a.max_seq) {
-    if (tid == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(cache_pos));
+  const long long abs_pos = __ldcg(a.cache_position);
+  // Llama-4: the row and the attended length follow from the position (ring of `chunk` rows, or a plain cache)
+  const long long cache_pos = (a.l4 && a.chunk > 0) ? abs_pos % a.chunk : abs_pos;
+  const int S = a.l4 ? static_cast<int>(min(cache_pos + 1, (long long)a.max_seq))
+                     : min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
+  // Past the end of the cache or of the rotary tables: record it and leave, writing nothing. The values are the
+  // same for every CTA of the cluster, so all of them leave before the first cluster barrier.
+  if (abs_pos < 0 || cache_pos >= a.max_seq || pos_id < 0 || pos_id >= a.max_pos) {
+    if (tid == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(abs_pos));
     return;
   }
   const int cached = S - 1;
@@ -123,8 +170,24 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_cluster_kernel(c
   T* kc = reinterpret_cast<T*>(a.k_cache) + ((size_t)b * a.Hkv + kvh) * a.max_seq * FA_D;
   T* vc = reinterpret_cast<T*>(a.v_cache) + ((size_t)b * a.Hkv + kvh) * a.max_seq * FA_D;
   float cs[8], sn[8];
-  unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.cos_t) + (size_t)pos_id * FA_D + d0), cs);
-  unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.sin_t) + (size_t)pos_id * FA_D + d0), sn);
+  float2 fr[4];
+  float temp = 1.f;
+  if (a.l4) {
+    float4 f01 = make_float4(1.f, 0.f, 1.f, 0.f), f23 = f01;
+    if (a.l4 & FA_L4_ROPE) {
+      const float4* f4 = reinterpret_cast<const float4*>(a.freqs + ((size_t)pos_id * (FA_D / 2) + d0 / 2) * 2);
+      f01 = __ldg(f4);
+      f23 = __ldg(f4 + 1);
+    }
+    fr[0] = make_float2(f01.x, f01.y);
+    fr[1] = make_float2(f01.z, f01.w);
+    fr[2] = make_float2(f23.x, f23.y);
+    fr[3] = make_float2(f23.z, f23.w);
+    if (a.l4 & FA_L4_TEMP) temp = fa_l4_temperature(abs_pos, a.attn_scale, a.floor_scale);
+  } else {
+    unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.cos_t) + (size_t)pos_id * FA_D + d0), cs);
+    unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.sin_t) + (size_t)pos_id * FA_D + d0), sn);
+  }
 
   float m[GP], l[GP], acc[GP][8];
 #pragma unroll
@@ -142,13 +205,15 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_cluster_kernel(c
 #pragma unroll
     for (int g = 0; g < GP; ++g) {
       unpack8<T>(q_raw[g], qf[g]);
-      fa_rope8<T>(qf[g], cs, sn, low);
+      if (a.l4) fa_l4_prologue8<T>(qf[g], fr, a.l4, a.eps, true, temp);
+      else fa_rope8<T>(qf[g], cs, sn, low);
 #pragma unroll
       for (int i = 0; i < 8; ++i) qf[g][i] *= a.scale_log2;
     }
     float kn[8];
     unpack8<T>(k_raw, kn);
-    fa_rope8<T>(kn, cs, sn, low);
+    if (a.l4) fa_l4_prologue8<T>(kn, fr, a.l4, a.eps, false, 1.f);
+    else fa_rope8<T>(kn, cs, sn, low);
     k_new = pack8<T>(kn);
     q_ready = true;
   };
@@ -356,9 +421,11 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(
 
   // ---- before the dependency wait: decode state + K/V history (nothing the previous kernel writes) ----
   const long long pos_id = __ldcg(a.position_ids + b);
-  const long long cache_pos = __ldcg(a.cache_position);
-  const int S = min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
-  if (S > RA_ROWS || cache_pos < 0 || cache_pos >= a.max_seq || pos_id < 0 || pos_id >= a.max_seq) {
+  const long long abs_pos = __ldcg(a.cache_position);
+  const long long cache_pos = (a.l4 && a.chunk > 0) ? abs_pos % a.chunk : abs_pos;
+  const int S = a.l4 ? static_cast<int>(min(cache_pos + 1, (long long)a.max_seq))
+                     : min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
+  if (S > RA_ROWS || abs_pos < 0 || cache_pos >= a.max_seq || pos_id < 0 || pos_id >= a.max_pos) {
     if (tid == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(S));
     return;
   }
@@ -387,8 +454,24 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(
   constexpr int LPT = FA_D / 8;  // 16 lanes hold one 128-element row
   const int sub = lane / LPT, dlane = lane % LPT, d0 = dlane * 8;
   float cs[8], sn[8];
-  unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.cos_t) + (size_t)pos_id * FA_D + d0), cs);
-  unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.sin_t) + (size_t)pos_id * FA_D + d0), sn);
+  float2 fr[4];
+  float temp = 1.f;
+  if (a.l4) {
+    float4 f01 = make_float4(1.f, 0.f, 1.f, 0.f), f23 = f01;
+    if (a.l4 & FA_L4_ROPE) {
+      const float4* f4 = reinterpret_cast<const float4*>(a.freqs + ((size_t)pos_id * (FA_D / 2) + d0 / 2) * 2);
+      f01 = __ldg(f4);
+      f23 = __ldg(f4 + 1);
+    }
+    fr[0] = make_float2(f01.x, f01.y);
+    fr[1] = make_float2(f01.z, f01.w);
+    fr[2] = make_float2(f23.x, f23.y);
+    fr[3] = make_float2(f23.z, f23.w);
+    if (a.l4 & FA_L4_TEMP) temp = fa_l4_temperature(abs_pos, a.attn_scale, a.floor_scale);
+  } else {
+    unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.cos_t) + (size_t)pos_id * FA_D + d0), cs);
+    unpack8<T>(ld_cached16(reinterpret_cast<const T*>(a.sin_t) + (size_t)pos_id * FA_D + d0), sn);
+  }
   pdl_launch_dependents();
   pdl_wait_prior_grid();
   if (tid == 0) trace_mark(a.trace, 2, false);
@@ -403,7 +486,9 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(
     else if (slot == G + 1) raw = ld_act16(row + ((size_t)a.Hq + a.Hkv + kvh) * FA_D + d0);
     float x[8];
     unpack8<T>(raw, x);
-    fa_rope8<T>(x, cs, sn, dlane < (LPT / 2));  // every lane takes part in the shuffles
+    // every lane takes part in the shuffles
+    if (a.l4) fa_l4_prologue8<T>(x, fr, a.l4, a.eps, slot < G, temp);
+    else fa_rope8<T>(x, cs, sn, dlane < (LPT / 2));
     const uint4 rot = pack8<T>(x);
     if (slot < G) {
       *reinterpret_cast<uint4*>(Qs + (size_t)slot * FA_D + d0) = rot;
@@ -622,6 +707,64 @@ extern "C" mui_status_t mui_rope_flash_decode(void* stream, mui_dtype_t dtype, i
   a.max_seq = max_seq;
   a.G = Hq / Hkv;
   a.trace = mui_trace_next_record(3);
+  a.freqs = nullptr;
+  a.max_pos = max_seq;
+  a.l4 = 0;
+  a.chunk = 0;
+  a.eps = a.attn_scale = a.floor_scale = 0.f;
+  const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
+  if (flags & MUI_FLAG_SHORT_CONTEXT) {
+    if (dtype == MUI_F16) return launch_ra_g<__half>((cudaStream_t)stream, a, pdl);
+    return launch_ra_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl);
+  }
+  if (dtype == MUI_F16) return launch_fa_g<__half>((cudaStream_t)stream, a, pdl);
+  return launch_fa_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl);
+}
+
+extern "C" mui_status_t mui_llama4_rope_flash_decode(void* stream, mui_dtype_t dtype, int B, int Hq, int Hkv, int D,
+                                                     int cache_rows, int max_pos, const void* qkv,
+                                                     const float* freqs, const int64_t* position_ids,
+                                                     const int64_t* cache_position, int use_rope, int use_qk_norm,
+                                                     float norm_eps, int temperature_tuning, float attn_scale,
+                                                     float floor_scale, int chunk, float scale, void* k_cache,
+                                                     void* v_cache, void* out, unsigned flags) {
+  MUI_REQUIRE(dtype == MUI_F16 || dtype == MUI_BF16, MUI_ERR_UNSUPPORTED, "dtype %d unsupported", (int)dtype);
+  MUI_REQUIRE(D == FA_D, MUI_ERR_UNSUPPORTED, "head dim %d unsupported by the fused kernel (128)", D);
+  MUI_REQUIRE(B >= 1 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && Hq / Hkv <= 8 && cache_rows >= 1 && max_pos >= 1,
+              MUI_ERR_INVALID_ARG, "bad sizes B=%d Hq=%d Hkv=%d cache_rows=%d max_pos=%d", B, Hq, Hkv, cache_rows,
+              max_pos);
+  MUI_REQUIRE(chunk >= 0, MUI_ERR_INVALID_ARG, "chunk must not be negative");
+  MUI_REQUIRE(qkv && position_ids && cache_position && k_cache && v_cache && out && (!use_rope || freqs),
+              MUI_ERR_INVALID_ARG, "null pointer");
+  MUI_REQUIRE(((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) |
+                reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(freqs) |
+                reinterpret_cast<uintptr_t>(out)) & 15) == 0,
+              MUI_ERR_INVALID_ARG, "pointers must be 16-byte aligned");
+  MUI_REQUIRE(!temperature_tuning || floor_scale > 0.f, MUI_ERR_INVALID_ARG, "floor_scale must be positive");
+  FaArgs a;
+  a.qkv = qkv;
+  a.cos_t = a.sin_t = nullptr;
+  a.position_ids = reinterpret_cast<const long long*>(position_ids);
+  a.cache_position = reinterpret_cast<const long long*>(cache_position);
+  a.seq_len_dev = nullptr;
+  a.k_cache = k_cache;
+  a.v_cache = v_cache;
+  a.out = out;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.B = B;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.max_seq = cache_rows;
+  a.G = Hq / Hkv;
+  a.trace = mui_trace_next_record(3);
+  a.freqs = freqs;
+  a.max_pos = max_pos;
+  a.l4 = FA_L4_ON | (use_rope ? FA_L4_ROPE : 0) | (use_qk_norm ? FA_L4_NORM : 0) |
+         (temperature_tuning ? FA_L4_TEMP : 0);
+  a.chunk = chunk;
+  a.eps = norm_eps;
+  a.attn_scale = attn_scale;
+  a.floor_scale = floor_scale;
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
   if (flags & MUI_FLAG_SHORT_CONTEXT) {
     if (dtype == MUI_F16) return launch_ra_g<__half>((cudaStream_t)stream, a, pdl);

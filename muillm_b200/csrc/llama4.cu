@@ -22,6 +22,7 @@ struct PrologueArgs {
   const void *q_in, *k_in;
   void *q_out, *k_out;
   const float* pos_embeds;        // [B, T, D/2, 2] (cos, sin) or null
+  const int64_t* pos_index;       // optional [B, T]: pos_embeds is then a table [positions, D/2, 2] indexed by it
   const int64_t* cache_position;  // [T] or null
   mui_strides3_t qs, ks;
   int B, T, Hq, Hk, D;
@@ -64,7 +65,9 @@ __global__ void __launch_bounds__(PRO_WARPS * 32) qk_prologue_kernel(const Prolo
     }
   }
   if (a.do_rope) {
-    const float2* cs = reinterpret_cast<const float2*>(a.pos_embeds) + ((size_t)b * a.T + t) * pairs;
+    const size_t prow = a.pos_index ? static_cast<size_t>(__ldcg(a.pos_index + (size_t)b * a.T + t))
+                                    : ((size_t)b * a.T + t);
+    const float2* cs = reinterpret_cast<const float2*>(a.pos_embeds) + prow * pairs;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int p = lane + 32 * j;
@@ -326,6 +329,33 @@ mui_status_t mui_llama4_qk_prologue(void* stream, mui_dtype_t dtype, int B, int 
   a.eps = norm_eps; a.attn_scale = attn_scale; a.floor_scale = floor_scale;
   return launch_prologue(static_cast<cudaStream_t>(stream), dtype, a, flags);
 }
+
+}  // extern "C"
+
+// Decode-stack use: the rotation angles come from the table row position_ids[b * T + t] (device side), so the launch
+// can be captured and replayed.
+mui_status_t mui_llama4_qk_prologue_indexed(cudaStream_t stream, mui_dtype_t dtype, int B, int T, int Hq, int Hk, int D,
+                                            const float* freqs_table, const int64_t* position_ids, int use_rope,
+                                            int use_qk_norm, float norm_eps, const int64_t* cache_position,
+                                            float attn_scale, float floor_scale, const void* q_in,
+                                            mui_strides3_t q_strides, const void* k_in, mui_strides3_t k_strides,
+                                            void* q_out, void* k_out, unsigned flags) {
+  if (mui_status_t s = check_prologue_sizes(dtype, B, T, Hq, Hk, D)) return s;
+  PrologueArgs a{};
+  a.q_in = q_in; a.k_in = k_in; a.q_out = q_out; a.k_out = k_out;
+  a.pos_embeds = use_rope ? freqs_table : nullptr;
+  a.pos_index = position_ids;
+  a.cache_position = cache_position;
+  a.qs = q_strides; a.ks = k_strides;
+  a.B = B; a.T = T; a.Hq = Hq; a.Hk = Hk; a.D = D;
+  a.do_rope = use_rope ? 1 : 0;
+  a.do_norm = use_qk_norm ? 1 : 0;
+  a.do_temp = cache_position ? 1 : 0;
+  a.eps = norm_eps; a.attn_scale = attn_scale; a.floor_scale = floor_scale;
+  return launch_prologue(stream, dtype, a, flags);
+}
+
+extern "C" {
 
 mui_status_t mui_sliding_kvcache_update(void* stream, mui_dtype_t dtype, int B, int T, int max_T, int Hk, int Hv,
                                         int D, const void* k_in, mui_strides3_t k_strides, const void* v_in,

@@ -24,6 +24,12 @@ mui_status_t mui_launch_argmax_advance(cudaStream_t stream, mui_dtype_t dtype, c
                                        void* work, int pdl, const CommDev* comm, int index_offset);
 mui_status_t mui_comm_device_view(mui_comm_t* c, CommDev* out);
 size_t mui_argmax_work_bytes(int B);
+mui_status_t mui_llama4_qk_prologue_indexed(cudaStream_t stream, mui_dtype_t dtype, int B, int T, int Hq, int Hk, int D,
+                                            const float* freqs_table, const int64_t* position_ids, int use_rope,
+                                            int use_qk_norm, float norm_eps, const int64_t* cache_position,
+                                            float attn_scale, float floor_scale, const void* q_in,
+                                            mui_strides3_t q_strides, const void* k_in, mui_strides3_t k_strides,
+                                            void* q_out, void* k_out, unsigned flags);
 
 struct WeightRef {
   const void* ptr;
@@ -39,7 +45,7 @@ struct mui_llama_stack {
   unsigned char* scratch;
   long long* state;      // [3 + 2B] int64: step, tokens in cache, cache_position, position_ids[B], tokens[B]
   int32_t* seq_len32;    // tokens attended by the current step (= tokens in cache + 1)
-  void *h, *qkv_out, *q_rot, *attn, *t, *logits;
+  void *h, *qkv_out, *q_rot, *k_rot, *attn, *t, *logits;
   void* fd_ws;
   size_t fd_ws_bytes;
   void* argmax_work;
@@ -58,6 +64,19 @@ struct mui_llama_stack {
   CommDev comm_dev;
   std::vector<WeightRef> order;  // weight matrices in execution order: per layer qkv, o, gate, up, down; then lm_head
   size_t prefetch_window;
+  // Llama-4 (MoE, chunked / full attention layers); `cfg` then carries the common sizes with intermediate =
+  // expert_intermediate and batch = 1
+  bool l4;
+  mui_llama4_config_t l4cfg;
+  std::vector<const void*> router;
+  std::vector<int> use_rope, cache_rows;
+  const float* freqs;
+  float* router_logits;           // [num_experts]
+  unsigned int* router_counter;   // arrival counter of the router kernel (zero between launches)
+  void* router_scores;            // [top_k] 16-bit
+  long long* router_idx;          // [top_k]
+  long long* chunk_row;           // separate-launch attention path: cache row and attended length of the chunked
+  int32_t* chunk_len32;           //   layers for the current step
 };
 
 namespace {
@@ -65,10 +84,12 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct ScratchLayout {
-  size_t state, seq_len, h, qkv, q_rot, attn, t, logits, fd_ws, fd_ws_bytes, argmax_work, total;
+  size_t state, seq_len, h, qkv, q_rot, attn, t, logits, fd_ws, fd_ws_bytes, argmax_work, router, k_rot, total;
 };
 
-ScratchLayout scratch_layout(const mui_llama_config_t& c) {
+// t_rows: rows of the MLP intermediate (1 for a dense MLP, computed experts for MoE); router_experts > 0 adds the
+// router scratch and the rotated-key row of the separate-launch Llama-4 attention path
+ScratchLayout scratch_layout(const mui_llama_config_t& c, int t_rows = 1, int router_experts = 0) {
   ScratchLayout l;
   const size_t B = c.batch, e = 2;
   size_t off = 0;
@@ -83,13 +104,65 @@ ScratchLayout scratch_layout(const mui_llama_config_t& c) {
   l.qkv = take(B * (size_t)(c.heads + 2 * c.kv_heads) * c.head_dim * e);
   l.q_rot = take(B * (size_t)c.heads * c.head_dim * e);
   l.attn = take(B * (size_t)c.heads * c.head_dim * e);
-  l.t = take(B * (size_t)c.intermediate * e);
+  l.t = take(B * (size_t)t_rows * c.intermediate * e);
   l.logits = take(B * (size_t)c.vocab * e);
   l.fd_ws_bytes = mui_flash_decode_workspace_bytes(c.batch, c.heads, c.kv_heads, c.head_dim, c.max_seq);
   l.fd_ws = take(l.fd_ws_bytes);
   l.argmax_work = take(mui_argmax_work_bytes(c.batch));
+  l.router = l.k_rot = 0;
+  if (router_experts > 0) {
+    // [0,64): counter; [64,128): chunk row (int64) + chunk length (int32); [256, ...): logits fp32, scores, indices
+    l.router = take(256 + (size_t)router_experts * 4 + 64 * 2 + 64 * 8);
+    l.k_rot = take(B * (size_t)c.kv_heads * c.head_dim * e);
+  }
   l.total = off;
   return l;
+}
+
+mui_llama_config_t common_cfg(const mui_llama4_config_t& c) {
+  mui_llama_config_t o;
+  memset(&o, 0, sizeof(o));
+  o.dtype = c.dtype;
+  o.layers = c.layers;
+  o.hidden = c.hidden;
+  o.intermediate = c.expert_intermediate;
+  o.heads = c.heads;
+  o.kv_heads = c.kv_heads;
+  o.head_dim = c.head_dim;
+  o.vocab = c.vocab;
+  o.max_seq = c.max_seq;
+  o.batch = 1;
+  o.rms_eps = c.rms_eps;
+  o.attn_scale = c.softmax_scale;
+  o.embed_vocab = c.embed_vocab;
+  o.vocab_offset = c.vocab_offset;
+  return o;
+}
+
+mui_status_t validate_cfg_l4(const mui_llama4_config_t* c) {
+  MUI_REQUIRE(c != nullptr, MUI_ERR_INVALID_ARG, "config is null");
+  MUI_REQUIRE(c->num_experts >= 1 && c->num_experts <= 1024 && c->top_k >= 1 && c->top_k <= c->num_experts &&
+                  c->num_shared >= 0 && c->num_shared + c->top_k <= 8,
+              MUI_ERR_UNSUPPORTED, "experts=%d top_k=%d shared=%d (at most 8 experts are computed per token)",
+              c->num_experts, c->top_k, c->num_shared);
+  MUI_REQUIRE(c->chunk >= 0, MUI_ERR_INVALID_ARG, "chunk must not be negative");
+  MUI_REQUIRE(!c->temperature_tuning || c->floor_scale > 0.f, MUI_ERR_INVALID_ARG, "floor_scale must be positive");
+  MUI_REQUIRE((c->head_dim & 1) == 0, MUI_ERR_UNSUPPORTED, "head_dim must be even");
+  return MUI_OK;
+}
+
+int l4_cache_rows(const mui_llama4_config_t& c, int use_rope) {
+  return (use_rope && c.chunk > 0) ? std::min(c.max_seq, c.chunk) : c.max_seq;
+}
+
+// Separate-launch Llama-4 attention path: row and attended length of the chunked layers for this step
+__global__ void l4_chunk_state_kernel(const long long* state, long long* chunk_row, int32_t* chunk_len32, int chunk) {
+  pdl_wait_prior_grid();
+  pdl_launch_dependents();
+  const long long pos = __ldcg(state + 2);
+  const long long row = chunk > 0 ? pos % chunk : pos;
+  *chunk_row = row;
+  *chunk_len32 = static_cast<int32_t>(row + 1);
 }
 
 mui_status_t validate_cfg(const mui_llama_config_t* c) {
@@ -181,7 +254,112 @@ void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t win
   mui_set_prefetch_skip(skip, n);
 }
 
+// One decode step of a Llama-4 text model (batch 1): six launches per layer on the fused path.
+mui_status_t launch_step_l4(mui_llama_stack* s, cudaStream_t stream, unsigned flags) {
+  const mui_llama_config_t& c = s->cfg;
+  const mui_llama4_config_t& c4 = s->l4cfg;
+  const int H = c.hidden, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim, I = c.intermediate;
+  const int qkv_n = (Hq + 2 * Hkv) * D;
+  const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
+  const long long* tokens = s->state + 4;
+  const int64_t* position_ids = reinterpret_cast<const int64_t*>(s->state + 3);
+  const int64_t* cache_position = reinterpret_cast<const int64_t*>(s->state + 2);
+  const bool tp = s->comm != nullptr;
+  const int embed_rows = c.embed_vocab > 0 ? c.embed_vocab : c.vocab;
+  mui_status_t st;
+  if (!s->skip_embedding) {
+    st = mui_launch_embedding(stream, s->embed, (const int64_t*)tokens, s->h, 1, H, embed_rows, pdl);
+    if (st != MUI_OK) return st;
+  }
+  const bool fused_attn = D == 128 && Hq / Hkv <= 8 && !(flags & MUI_FLAG_FORCE_GENERIC);
+  const int attended = s->capturing ? s->s_upper : s->host_pos + 1;
+  if (!fused_attn && c4.chunk > 0) {
+    MUI_CUDA_CHECK(mui_launch(l4_chunk_state_kernel, dim3(1), dim3(1), 0, stream, pdl, (const long long*)s->state,
+                              s->chunk_row, s->chunk_len32, c4.chunk));
+  }
+  const mui_strides3_t qs = {(int64_t)qkv_n, (int64_t)D, (int64_t)qkv_n};
+  const mui_strides3_t krs = {(int64_t)Hkv * D, (int64_t)D, (int64_t)D};
+  const size_t e = 2;
+  for (int l = 0; l < c.layers; ++l) {
+    const int rope = s->use_rope[l];
+    const int rows = s->cache_rows[l];
+    const int norm = (c4.use_qk_norm && rope) ? 1 : 0;
+    const int tune = (c4.temperature_tuning && !rope) ? 1 : 0;
+    const int chunk = (rope && c4.chunk > 0) ? c4.chunk : 0;
+    // the one-CTA-per-KV-head attention kernel serves up to 384 attended rows: always enough for a short chunk
+    const int layer_attended = chunk > 0 ? std::min(attended, chunk) : attended;
+    const bool short_ctx = fused_attn && pdl && short_context_enabled() && layer_attended <= 384 && Hkv <= 16;
+    if (s->capturing && short_ctx && !(chunk > 0 && chunk <= 384)) s->graph_short = true;
+    if (short_ctx) mui_set_gemv_reserve_sms(Hkv);
+    st = mui_linear_forward(stream, c.dtype, 1, qkv_n, H, s->ln1[l], c.rms_eps, s->qkv[l], MUI_ACT_IDENTITY, nullptr,
+                            nullptr, nullptr, s->h, s->qkv_out, flags);
+    if (st != MUI_OK) return st;
+    if (fused_attn) {
+      st = mui_llama4_rope_flash_decode(stream, c.dtype, 1, Hq, Hkv, D, rows, c.max_seq, s->qkv_out, s->freqs,
+                                        position_ids, cache_position, rope, norm, c.rms_eps, tune, c4.attn_scale,
+                                        c4.floor_scale, chunk, c.attn_scale, s->k_cache[l], s->v_cache[l], s->attn,
+                                        flags | (short_ctx ? MUI_FLAG_SHORT_CONTEXT : 0u));
+      if (st != MUI_OK) return st;
+    } else {
+      const unsigned char* qp = (const unsigned char*)s->qkv_out;
+      const int64_t* row_ptr = chunk > 0 ? reinterpret_cast<const int64_t*>(s->chunk_row) : cache_position;
+      const int32_t* len_ptr = chunk > 0 ? s->chunk_len32 : s->seq_len32;
+      const void* q_for_attn = s->q_rot;
+      const void* k_for_cache = s->k_rot;
+      if (rope || norm || tune) {
+        st = mui_llama4_qk_prologue_indexed(stream, c.dtype, 1, 1, Hq, Hkv, D, s->freqs, position_ids, rope, norm,
+                                            c.rms_eps, tune ? cache_position : nullptr, c4.attn_scale, c4.floor_scale,
+                                            qp, qs, qp + (size_t)Hq * D * e, qs, s->q_rot, s->k_rot, flags);
+        if (st != MUI_OK) return st;
+      } else {
+        // nothing to do to q and k: q must still be contiguous for flash decoding (it is: one token), k is read
+        // through its strides
+        q_for_attn = qp;
+        k_for_cache = nullptr;
+      }
+      st = mui_static_kvcache_update(stream, c.dtype, 1, 1, rows, Hkv, D,
+                                     k_for_cache ? k_for_cache : (const void*)(qp + (size_t)Hq * D * e),
+                                     k_for_cache ? krs : qs, qp + (size_t)(Hq + Hkv) * D * e, qs, s->k_cache[l],
+                                     s->v_cache[l], row_ptr, flags);
+      if (st != MUI_OK) return st;
+      const mui_strides3_t kvs = {(int64_t)Hkv * rows * D, (int64_t)rows * D, (int64_t)D};
+      st = mui_flash_decode(stream, c.dtype, 1, Hq, Hkv, D, rows, len_ptr, c.attn_scale, q_for_attn, s->k_cache[l],
+                            s->v_cache[l], kvs, nullptr, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
+      if (st != MUI_OK) return st;
+    }
+    if (short_ctx && oproj_reserve_enabled()) mui_set_gemv_reserve_sms(Hkv);
+    if (tp)
+      st = mui_parallel_linear_forward(s->comm, stream, c.dtype, 1, H, Hq * D, nullptr, 0.f, s->o[l], nullptr, nullptr,
+                                       s->h, s->attn, s->h, flags);
+    else
+      st = mui_linear_forward(stream, c.dtype, 1, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr, nullptr,
+                              s->h, s->attn, s->h, flags);
+    if (st != MUI_OK) return st;
+    st = mui_router_topk_sigmoid_forward(stream, c.dtype, c4.num_experts, H, c4.top_k, s->ln2[l], c.rms_eps,
+                                         s->router[l], s->h, s->router_logits, s->router_counter, s->router_scores,
+                                         reinterpret_cast<int64_t*>(s->router_idx), flags);
+    if (st != MUI_OK) return st;
+    if (tp)
+      st = mui_parallel_moe_mlp_forward(s->comm, stream, c.dtype, c4.num_shared, c4.num_experts, c4.top_k, I, H,
+                                        s->ln2[l], c.rms_eps, s->gate[l], s->up[l], s->down[l], s->h, s->h,
+                                        s->router_scores, reinterpret_cast<const int64_t*>(s->router_idx), s->t, s->h,
+                                        flags);
+    else
+      st = mui_moe_mlp_forward(stream, c.dtype, c4.num_shared, c4.num_experts, c4.top_k, I, H, s->ln2[l], c.rms_eps,
+                               s->gate[l], s->up[l], s->down[l], s->h, s->h, s->router_scores,
+                               reinterpret_cast<const int64_t*>(s->router_idx), s->t, s->h, flags);
+    if (st != MUI_OK) return st;
+  }
+  if (s->layers_only) return MUI_OK;
+  st = mui_linear_forward(stream, c.dtype, 1, c.vocab, H, s->final_norm, c.rms_eps, s->lm_head, MUI_ACT_IDENTITY,
+                          nullptr, nullptr, nullptr, s->h, s->logits, flags);
+  if (st != MUI_OK) return st;
+  return mui_launch_argmax_advance(stream, c.dtype, s->logits, c.vocab, 1, s->state, s->seq_len32, s->out_tokens,
+                                   s->out_capacity, s->argmax_work, pdl, tp ? &s->comm_dev : nullptr, c.vocab_offset);
+}
+
 mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags) {
+  if (s->l4) return launch_step_l4(s, stream, flags);
   const mui_llama_config_t& c = s->cfg;
   const int B = c.batch, H = c.hidden, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim;
   const int qkv_n = (Hq + 2 * Hkv) * D;
@@ -337,6 +515,15 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
   s->graph_flags = 0;
   s->comm = nullptr;
   s->attn_mask = nullptr;
+  s->l4 = false;
+  s->k_rot = nullptr;
+  s->freqs = nullptr;
+  s->router_logits = nullptr;
+  s->router_counter = nullptr;
+  s->router_scores = nullptr;
+  s->router_idx = nullptr;
+  s->chunk_row = nullptr;
+  s->chunk_len32 = nullptr;
   {
     const int qkv_rows = (cfg->heads + 2 * cfg->kv_heads) * cfg->head_dim;
     const int od = cfg->heads * cfg->head_dim;
@@ -352,6 +539,103 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
     const long mb = (e && *e) ? atol(e) : 24;  // measured on the 8B decode step: 8-48 MB within 1 %, none -2 %, 96 MB -3 %
     s->prefetch_window = mb > 0 ? (size_t)mb << 20 : 0;
   }
+  *out = s;
+  return MUI_OK;
+}
+
+int mui_llama4_stack_cache_rows(const mui_llama4_config_t* cfg, int use_rope) {
+  if (cfg == nullptr) return 0;
+  return l4_cache_rows(*cfg, use_rope);
+}
+
+size_t mui_llama4_stack_scratch_bytes(const mui_llama4_config_t* cfg) {
+  if (validate_cfg_l4(cfg) != MUI_OK) return 0;
+  const mui_llama_config_t c = common_cfg(*cfg);
+  if (validate_cfg(&c) != MUI_OK) return 0;
+  return scratch_layout(c, cfg->num_shared + cfg->top_k, cfg->num_experts).total;
+}
+
+mui_status_t mui_llama4_stack_create(const mui_llama4_config_t* cfg4, const mui_llama4_weights_t* w, void* scratch,
+                                     size_t scratch_bytes, mui_llama_stack_t** out) {
+  if (mui_status_t st = validate_cfg_l4(cfg4)) return st;
+  const mui_llama_config_t cfg = common_cfg(*cfg4);
+  if (mui_status_t st = validate_cfg(&cfg)) return st;
+  MUI_REQUIRE(w && scratch && out, MUI_ERR_INVALID_ARG, "weights, scratch and out must be non-null");
+  MUI_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255) == 0, MUI_ERR_INVALID_ARG, "scratch must be 256-byte aligned");
+  const ScratchLayout lay = scratch_layout(cfg, cfg4->num_shared + cfg4->top_k, cfg4->num_experts);
+  MUI_REQUIRE(scratch_bytes >= lay.total, MUI_ERR_INVALID_ARG, "scratch too small: %zu < %zu", scratch_bytes, lay.total);
+  MUI_REQUIRE(w->embed && w->final_norm && w->lm_head && w->freqs && w->use_rope, MUI_ERR_INVALID_ARG,
+              "embed, final_norm, lm_head, freqs and use_rope must be non-null");
+  MUI_REQUIRE(w->qkv && w->o && w->router && w->gate && w->up && w->down && w->ln1 && w->ln2 && w->k_cache &&
+                  w->v_cache,
+              MUI_ERR_INVALID_ARG, "per-layer pointer arrays must be non-null");
+  MUI_REQUIRE((reinterpret_cast<uintptr_t>(w->freqs) & 15) == 0, MUI_ERR_INVALID_ARG, "freqs must be 16-byte aligned");
+  mui_llama_stack* s = new (std::nothrow) mui_llama_stack();
+  MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "out of host memory");
+  s->cfg = cfg;
+  s->l4 = true;
+  s->l4cfg = *cfg4;
+  for (int l = 0; l < cfg.layers; ++l) {
+    const void* ptrs[] = {w->qkv[l], w->o[l], w->router[l], w->gate[l], w->up[l], w->down[l], w->ln1[l], w->ln2[l],
+                          w->k_cache[l], w->v_cache[l]};
+    for (const void* p : ptrs) {
+      if (p == nullptr) {
+        delete s;
+        mui_set_error("layer %d has a null weight or cache pointer", l);
+        return MUI_ERR_INVALID_ARG;
+      }
+    }
+    s->qkv.push_back(w->qkv[l]);
+    s->o.push_back(w->o[l]);
+    s->router.push_back(w->router[l]);
+    s->gate.push_back(w->gate[l]);
+    s->up.push_back(w->up[l]);
+    s->down.push_back(w->down[l]);
+    s->ln1.push_back(w->ln1[l]);
+    s->ln2.push_back(w->ln2[l]);
+    s->k_cache.push_back(w->k_cache[l]);
+    s->v_cache.push_back(w->v_cache[l]);
+    s->use_rope.push_back(w->use_rope[l] ? 1 : 0);
+    s->cache_rows.push_back(l4_cache_rows(*cfg4, w->use_rope[l]));
+  }
+  s->embed = w->embed;
+  s->final_norm = w->final_norm;
+  s->lm_head = w->lm_head;
+  s->cos_t = s->sin_t = nullptr;
+  s->freqs = w->freqs;
+  unsigned char* base = reinterpret_cast<unsigned char*>(scratch);
+  s->scratch = base;
+  s->state = reinterpret_cast<long long*>(base + lay.state);
+  s->seq_len32 = reinterpret_cast<int32_t*>(base + lay.seq_len);
+  s->h = base + lay.h;
+  s->qkv_out = base + lay.qkv;
+  s->q_rot = base + lay.q_rot;
+  s->k_rot = base + lay.k_rot;
+  s->attn = base + lay.attn;
+  s->t = base + lay.t;
+  s->logits = base + lay.logits;
+  s->fd_ws = base + lay.fd_ws;
+  s->fd_ws_bytes = lay.fd_ws_bytes;
+  s->argmax_work = base + lay.argmax_work;
+  s->router_counter = reinterpret_cast<unsigned int*>(base + lay.router);
+  s->chunk_row = reinterpret_cast<long long*>(base + lay.router + 64);
+  s->chunk_len32 = reinterpret_cast<int32_t*>(base + lay.router + 72);
+  s->router_idx = reinterpret_cast<long long*>(base + lay.router + 128);   // up to 8 indices
+  s->router_scores = base + lay.router + 192;                              // up to 8 16-bit scores
+  s->router_logits = reinterpret_cast<float*>(base + lay.router + 256);
+  s->out_tokens = nullptr;
+  s->out_capacity = 0;
+  s->s_upper = cfg.max_seq;
+  s->host_pos = 0;
+  s->capturing = false;
+  s->graph_short = false;
+  s->layers_only = false;
+  s->skip_embedding = false;
+  s->graph_exec = nullptr;
+  s->graph_flags = 0;
+  s->comm = nullptr;
+  s->attn_mask = nullptr;
+  s->prefetch_window = 0;
   *out = s;
   return MUI_OK;
 }
@@ -406,6 +690,7 @@ mui_status_t mui_llama_stack_reset(mui_llama_stack_t* s, void* stream, int posit
   // flash-decoding and arg-max arrival counters start at zero
   MUI_CUDA_CHECK(cudaMemsetAsync(s->fd_ws, 0, 4096, cs));
   MUI_CUDA_CHECK(cudaMemsetAsync(s->argmax_work, 0, 64, cs));
+  if (s->l4) MUI_CUDA_CHECK(cudaMemsetAsync(s->router_counter, 0, 64, cs));
   s->out_tokens = reinterpret_cast<long long*>(out_tokens_dev);
   s->out_capacity = out_tokens_dev ? out_capacity : 0;
   // the caller's token buffer bounds how far this run decodes; without one assume the whole cache
@@ -436,6 +721,7 @@ mui_status_t mui_llama_stack_set_position_ids(mui_llama_stack_t* s, void* stream
 
 mui_status_t mui_llama_stack_set_attention_mask(mui_llama_stack_t* s, const void* mask_dev) {
   MUI_REQUIRE(s != nullptr, MUI_ERR_INVALID_ARG, "stack is null");
+  MUI_REQUIRE(!s->l4 || mask_dev == nullptr, MUI_ERR_UNSUPPORTED, "the Llama-4 stack decodes one sequence: no mask");
   if (mask_dev != s->attn_mask && s->graph_exec) {  // a captured step holds the old attention launches
     cudaGraphExecDestroy(s->graph_exec);
     s->graph_exec = nullptr;

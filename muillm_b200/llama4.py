@@ -11,11 +11,18 @@ Per layer and token, six launches:
 Chunked attention needs neither a ring buffer nor a mask here: every layer keeps a plain [1, Hkv, max_seq, D] cache and
 a chunked layer hands flash decoding the strided view of the rows of the current chunk.
 
-Each launch is one Python call (there is no whole-step C stack for this architecture yet).
+`Llama4DecodeRunner` makes one Python call per launch (kept as the kernel-by-kernel cross-check); `Llama4DecodeStack`
+runs the whole step as one call into the C decode stack (mui_llama4_stack_*): six launches per layer, ring caches for
+the chunked layers, token and position on the device, replayable as a CUDA graph.
 """
+import ctypes
+import math
+from ctypes import c_int, c_void_p
+
 import torch
 
-from . import ops
+from . import capi, ops
+from .decoder_stack import LlamaDecodeStack
 
 
 def llama4_config_from_hf(c):
@@ -252,3 +259,80 @@ class Llama4DecodeRunner:
             if len(out) < new_tokens:
                 logits = self.step(nxt)
         return torch.tensor(out, dtype=torch.int64, device=self.device)
+
+
+def llama4_freqs(max_pos, head_dim, theta, device):
+    """[max_pos, head_dim/2, 2] fp32 (cos, sin) of the interleaved-pair rotation angles: what HF's
+    Llama4TextRotaryEmbedding returns as complex numbers (freqs_cis)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
+    return torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(device).contiguous()
+
+
+class Llama4DecodeStack(LlamaDecodeStack):
+    """Greedy batch-1 decoding of a Llama-4 text model through the C decode stack: same weights dict and cfg as
+    Llama4DecodeRunner (packed experts, shared expert first; with `comm` this rank's shard from
+    shard_llama4_weights(..., shard_lm_head=True) or llama4_bench.local_weights). The methods of LlamaDecodeStack
+    (reset, set_tokens, step, capture, replay, prefill, greedy, logits, next_tokens) apply unchanged.
+
+    The per-token path the reference runs through MuiLLMParallelLlama4DecoderStack
+    (csrc/modules/parallel_llama4_decoder_stack.cpp:18-60)."""
+
+    def __init__(self, weights, cfg, max_seq, max_new_tokens=4096, flags=0, comm=None):
+        self.lib = capi.lib()
+        self.cfg = dict(cfg)
+        self.w = weights
+        dev, dt = weights["embed"].device, weights["embed"].dtype
+        self.device, self.dtype = dev, dt
+        self.batch, self.max_seq, self.flags = 1, max_seq, flags
+        L, Hkv, D = cfg["layers"], cfg["kv_heads"], cfg["head_dim"]
+        c = capi.Llama4Config(
+            capi.MUI_F16 if dt == torch.float16 else capi.MUI_BF16, L, cfg["hidden"], cfg["expert_intermediate"],
+            cfg["heads"], Hkv, D, weights["lm_head"].shape[0], max_seq, int(cfg.get("chunk") or 0), cfg["experts"],
+            cfg["top_k"], 1, float(cfg["eps"]), 1.0 / math.sqrt(D), int(bool(cfg["use_qk_norm"])),
+            int(bool(cfg["temperature_tuning"])), float(cfg["attn_scale"]), float(cfg["floor_scale"]),
+            int(weights["embed"].shape[0]) if comm is not None else 0, int(cfg.get("vocab_offset", 0)))
+        self._c = c
+        self.cfg["vocab"] = int(weights["lm_head"].shape[0])  # rows of this rank's lm_head (logits view)
+        use_rope = [int(bool(v)) for v in cfg["use_rope"]]
+        rows = [self.lib.mui_llama4_stack_cache_rows(ctypes.byref(c), r) for r in use_rope]
+        self.k_cache = [torch.zeros(1, Hkv, n, D, dtype=dt, device=dev) for n in rows]
+        self.v_cache = [torch.zeros(1, Hkv, n, D, dtype=dt, device=dev) for n in rows]
+        self.freqs = llama4_freqs(max_seq, D, cfg["rope_theta"], dev)
+        nbytes = self.lib.mui_llama4_stack_scratch_bytes(ctypes.byref(c))
+        if nbytes == 0:
+            raise RuntimeError("muillm_b200: " + self.lib.mui_last_error().decode())
+        self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        self.out_tokens = torch.zeros(max_new_tokens, 1, dtype=torch.int64, device=dev)
+
+        def arr(tensors):
+            for t in tensors:
+                assert t.is_cuda and t.is_contiguous() and t.dtype == dt
+            return (c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+        self._arrays = {k: arr(weights[k]) for k in ("qkv", "o", "router", "gate", "up", "down", "ln1", "ln2")}
+        self._arrays["k_cache"] = arr(self.k_cache)
+        self._arrays["v_cache"] = arr(self.v_cache)
+        self._use_rope = (c_int * L)(*use_rope)
+        w = capi.Llama4Weights(
+            weights["embed"].data_ptr(), weights["norm"].data_ptr(), weights["lm_head"].data_ptr(),
+            self.freqs.data_ptr(), self._use_rope,
+            self._arrays["qkv"], self._arrays["o"], self._arrays["router"], self._arrays["gate"], self._arrays["up"],
+            self._arrays["down"], self._arrays["ln1"], self._arrays["ln2"], self._arrays["k_cache"],
+            self._arrays["v_cache"])
+        h = c_void_p()
+        capi.check(self.lib.mui_llama4_stack_create(ctypes.byref(c), ctypes.byref(w), self.scratch.data_ptr(),
+                                                    self.scratch.numel(), ctypes.byref(h)))
+        self._h = h
+        self._captured = False
+        self.comm = comm
+        if comm is not None:
+            capi.check(self.lib.mui_llama_stack_set_comm(h, comm.handle))
+        self.reset(0)
+
+    @property
+    def launches_per_step(self):
+        """embedding, per layer {QKV, attention, o_proj, router + top-k, expert gate/up, expert down}, lm_head,
+        arg-max; head dims other than 128 run the attention as prologue + cache write + flash decoding."""
+        fused = self.cfg["head_dim"] == 128 and not (self.flags & capi.MUI_FLAG_FORCE_GENERIC)
+        return 3 + (6 if fused else 8) * self.cfg["layers"]

@@ -1,5 +1,5 @@
 """Generates the golden fixtures under tests/golden/ (run once in the authoring container; needs the reference
-checkout, whose location is REF below or $MUILLM_REFERENCE, and transformers). Committed beside the fixtures it made.
+checkout, whose location is $MUILLM_REFERENCE, and transformers). Committed beside the fixtures it made.
 
 Sources of truth, in order of authority:
  * the reference's own Python, imported unmodified with a stub `muillm_ext` (the CPU branches never call it):
@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("MUILLM_REFERENCE", "/root/reference")
+REF = os.environ.get("MUILLM_REFERENCE")  # checkout of the reference; required for the fixtures made from it
 
 
 class _Stub(types.ModuleType):
@@ -236,7 +236,7 @@ LLAMA4_TINY = dict(vocab_size=256, hidden_size=128, intermediate_size=64, interm
                    bos_token_id=1, eos_token_id=2)
 
 
-def hf_llama4_model_fixture(out):
+def hf_llama4_model_fixture(out, head_dim=None):
     """A whole HF Llama-4 text model (MoE with a shared expert and top-1 sigmoid routing in every layer, chunked
     attention of 8 tokens with rope + QK L2 norm in layers 0-2, full attention with temperature tuning and no rope
     in layer 3): fp16-representable weights, a 12-token prompt and the 24 tokens generate(do_sample=False) produced in
@@ -244,8 +244,11 @@ def hf_llama4_model_fixture(out):
     24 steps exceeds 0.05, which keeps a 16-bit implementation on the same tokens."""
     from transformers import Llama4ForCausalLM, Llama4TextConfig
 
-    cfg = Llama4TextConfig(attn_implementation="eager", **LLAMA4_TINY)
-    for seed in range(40, 80):
+    kw = dict(LLAMA4_TINY)
+    if head_dim is not None:  # the same model at another head size (128: the size the fused attention kernels serve)
+        kw["head_dim"] = head_dim
+    cfg = Llama4TextConfig(attn_implementation="eager", **kw)
+    for seed in range(40, 80 if head_dim is None else 400):
         g = torch.Generator().manual_seed(seed)
         model = Llama4ForCausalLM(cfg).eval()
         with torch.no_grad():
@@ -284,6 +287,13 @@ def main():
         np.savez_compressed(os.path.join(HERE, "hf_llama4_model.npz"), **d)
         print("hf_llama4_model.npz", os.path.getsize(os.path.join(HERE, "hf_llama4_model.npz")) // 1024, "KiB",
               "seed", int(d["seed"]), "min margin", float(d["margins"].min()), "no_rope_layers", d["no_rope_layers"])
+        return
+    if sys.argv[1:] == ["llama4_model_d128"]:
+        d = {}
+        hf_llama4_model_fixture(d, head_dim=128)
+        np.savez_compressed(os.path.join(HERE, "hf_llama4_model_d128.npz"), **d)
+        print("hf_llama4_model_d128.npz", os.path.getsize(os.path.join(HERE, "hf_llama4_model_d128.npz")) // 1024,
+              "KiB", "seed", int(d["seed"]), "min margin", float(d["margins"].min()))
         return
     if sys.argv[1:] == ["llama4"]:
         l4 = {}
