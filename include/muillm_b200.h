@@ -90,14 +90,6 @@ MUI_API mui_status_t mui_device_status(unsigned* code, int clear);
 MUI_API mui_status_t mui_trace_enable(void* stream, void* device_buffer, int max_records);
 MUI_API int mui_trace_count(int* tags_out, int max_tags);
 
-/* L2 prefetch hint: up to 3 weight matrices ([rows][row_bytes], 16-byte aligned) of the kernels that FOLLOW the
- * next GEMV / gate-up launch of this host thread on its stream. Once their own copies are issued, that launch's
- * producer warps pull into L2 the first frac1024/1024 of the row range each CTA index will own in the consuming
- * kernel, so HBM keeps streaming through the kernel tail, the launch gap and short latency-bound kernels in
- * between. Consumed (and cleared) by the next pipeline GEMV launch; harmless otherwise. */
-MUI_API mui_status_t mui_prefetch_hint(const void* const* ptrs, const int* rows, const int* row_bytes,
-                                       const int* frac1024, int n);
-
 /* ---- (a1) linear / GEMV --------------------------------------------------------------------------
  * y[b, n] = act( sum_k W[n,k] * xn[b,k] ) * mul_bias[n] + add_bias[n] + residual[b, n]
  * xn = x                                   when norm_weights == NULL

@@ -108,7 +108,6 @@ PROTOTYPES = {
     "mui_version": (c_int, []),
     "mui_device_props": (c_int, [c_int, POINTER(DeviceProps)]),
     "mui_device_status": (c_int, [POINTER(c_uint), c_int]),
-    "mui_prefetch_hint": (c_int, [POINTER(c_void_p), POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]),
     "mui_trace_enable": (c_int, [c_void_p, c_void_p, c_int]),
     "mui_trace_count": (c_int, [POINTER(c_int), c_int]),
     "mui_linear_forward": (

@@ -37,44 +37,6 @@ unsigned long long* mui_trace_next_record(int kernel_tag) {
   return tls_trace_buf + 8 * (size_t)(tls_trace_next++);
 }
 
-// ---- L2 prefetch hint (per host thread) ----
-static thread_local const void* tls_pf_ptr[3] = {nullptr, nullptr, nullptr};
-static thread_local int tls_pf_rows[3] = {0, 0, 0}, tls_pf_row_bytes[3] = {0, 0, 0}, tls_pf_frac[3] = {0, 0, 0};
-
-// Number of SMs the next GEMV launch of this thread leaves free (for a small kernel that should become resident
-// beside it); consumed by that launch.
-static thread_local int tls_reserve_sms = 0;
-void mui_set_gemv_reserve_sms(int n) { tls_reserve_sms = n > 0 ? n : 0; }
-int mui_take_gemv_reserve_sms() {
-  const int n = tls_reserve_sms;
-  tls_reserve_sms = 0;
-  return n;
-}
-
-// Bytes at the head of each CTA's range of a hinted matrix that the prefetch leaves out (the consuming kernel's own
-// ring fetches them as soon as it is resident); set together with the hint, consumed with it.
-static thread_local int tls_pf_skip[3] = {0, 0, 0};
-void mui_set_prefetch_skip(const int* skip_bytes, int n) {
-  for (int i = 0; i < 3; ++i) tls_pf_skip[i] = (i < n && skip_bytes[i] > 0) ? skip_bytes[i] : 0;
-}
-void mui_take_prefetch_skip(int* skip_bytes) {
-  for (int i = 0; i < 3; ++i) {
-    skip_bytes[i] = tls_pf_skip[i];
-    tls_pf_skip[i] = 0;
-  }
-}
-
-void mui_take_prefetch_hint(const void** ptrs, int* rows, int* row_bytes, int* frac1024) {
-  for (int i = 0; i < 3; ++i) {
-    ptrs[i] = tls_pf_ptr[i];
-    rows[i] = tls_pf_rows[i];
-    row_bytes[i] = tls_pf_row_bytes[i];
-    frac1024[i] = tls_pf_frac[i];
-    tls_pf_ptr[i] = nullptr;
-    tls_pf_frac[i] = 0;
-  }
-}
-
 const MuiDeviceInfo* mui_current_device_info() {
   static MuiDeviceInfo infos[64];
   static bool valid[64] = {false};
@@ -108,8 +70,18 @@ const MuiDeviceInfo* mui_current_device_info() {
   return &infos[dev];
 }
 
-// defined in gemv.cu / gemv_w8.cu
+// defined in gemv.cu
 mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode, const GemvArgs& a, unsigned flags);
+// the public entry points plus launch hints (decode stack)
+mui_status_t mui_linear_forward_hinted(void* stream, mui_dtype_t dtype, int B, int N, int K,
+                                       const void* norm_weights, float epsilon, const void* weights,
+                                       mui_activation_t activ, const void* mul_bias, const void* add_bias,
+                                       const void* residual, const void* x, void* y, unsigned flags,
+                                       const GemvHints* hints);
+mui_status_t mui_gateup_silu_forward_hinted(void* stream, mui_dtype_t dtype, int B, int I, int H,
+                                            const void* norm_weights, float epsilon, const void* gate_weights,
+                                            const void* up_weights, const void* x, void* t, unsigned flags,
+                                            const GemvHints* hints);
 
 extern "C" {
 
@@ -169,20 +141,6 @@ mui_status_t mui_trace_enable(void* stream, void* device_buffer, int max_records
   return MUI_OK;
 }
 
-mui_status_t mui_prefetch_hint(const void* const* ptrs, const int* rows, const int* row_bytes, const int* frac1024,
-                               int n) {
-  MUI_REQUIRE(n >= 0 && n <= 3, MUI_ERR_INVALID_ARG, "at most 3 prefetch ranges");
-  for (int i = 0; i < 3; ++i) {
-    const bool on = i < n && ptrs[i] != nullptr && (reinterpret_cast<uintptr_t>(ptrs[i]) & 15) == 0 && rows[i] > 0 &&
-                    row_bytes[i] > 0 && (row_bytes[i] & 15) == 0 && frac1024[i] > 0;
-    tls_pf_ptr[i] = on ? ptrs[i] : nullptr;
-    tls_pf_rows[i] = on ? rows[i] : 0;
-    tls_pf_row_bytes[i] = on ? row_bytes[i] : 0;
-    tls_pf_frac[i] = on ? std::min(frac1024[i], 1024) : 0;
-  }
-  return MUI_OK;
-}
-
 int mui_trace_count(int* tags_out, int max_tags) {
   const int n = tls_trace_next;
   for (int i = 0; i < n && i < max_tags; ++i) tags_out[i] = tls_trace_tags[i];
@@ -197,6 +155,24 @@ static mui_status_t check_dtype(mui_dtype_t d) {
 mui_status_t mui_linear_forward(void* stream, mui_dtype_t dtype, int B, int N, int K, const void* norm_weights,
                                 float epsilon, const void* weights, mui_activation_t activ, const void* mul_bias,
                                 const void* add_bias, const void* residual, const void* x, void* y, unsigned flags) {
+  return mui_linear_forward_hinted(stream, dtype, B, N, K, norm_weights, epsilon, weights, activ, mul_bias, add_bias,
+                                   residual, x, y, flags, nullptr);
+}
+
+mui_status_t mui_gateup_silu_forward(void* stream, mui_dtype_t dtype, int B, int I, int H, const void* norm_weights,
+                                     float epsilon, const void* gate_weights, const void* up_weights, const void* x,
+                                     void* t, unsigned flags) {
+  return mui_gateup_silu_forward_hinted(stream, dtype, B, I, H, norm_weights, epsilon, gate_weights, up_weights, x, t,
+                                        flags, nullptr);
+}
+
+}  // extern "C"
+
+mui_status_t mui_linear_forward_hinted(void* stream, mui_dtype_t dtype, int B, int N, int K,
+                                       const void* norm_weights, float epsilon, const void* weights,
+                                       mui_activation_t activ, const void* mul_bias, const void* add_bias,
+                                       const void* residual, const void* x, void* y, unsigned flags,
+                                       const GemvHints* hints) {
   if (mui_status_t s = check_dtype(dtype)) return s;
   MUI_REQUIRE(weights && x && y, MUI_ERR_INVALID_ARG, "weights, x and y must be non-null");
   MUI_REQUIRE(B >= 1 && B <= 8, MUI_ERR_UNSUPPORTED, "B=%d outside 1..8 (larger batches belong to a GEMM)", B);
@@ -221,12 +197,14 @@ mui_status_t mui_linear_forward(void* stream, mui_dtype_t dtype, int B, int N, i
   a.moe_mode = GEMV_MOE_NONE;
   a.slots = 1;
   a.w8_fmt = -1;
+  gemv_apply_hints(a, hints);
   return mui_launch_gemv16((cudaStream_t)stream, dtype, 0, a, flags);
 }
 
-mui_status_t mui_gateup_silu_forward(void* stream, mui_dtype_t dtype, int B, int I, int H, const void* norm_weights,
-                                     float epsilon, const void* gate_weights, const void* up_weights, const void* x,
-                                     void* t, unsigned flags) {
+mui_status_t mui_gateup_silu_forward_hinted(void* stream, mui_dtype_t dtype, int B, int I, int H,
+                                            const void* norm_weights, float epsilon, const void* gate_weights,
+                                            const void* up_weights, const void* x, void* t, unsigned flags,
+                                            const GemvHints* hints) {
   if (mui_status_t s = check_dtype(dtype)) return s;
   MUI_REQUIRE(gate_weights && up_weights && x && t, MUI_ERR_INVALID_ARG,
               "gate_weights, up_weights, x and t must be non-null");
@@ -247,8 +225,11 @@ mui_status_t mui_gateup_silu_forward(void* stream, mui_dtype_t dtype, int B, int
   a.moe_mode = GEMV_MOE_NONE;
   a.slots = 1;
   a.w8_fmt = -1;
+  gemv_apply_hints(a, hints);
   return mui_launch_gemv16((cudaStream_t)stream, dtype, 1, a, flags);
 }
+
+extern "C" {
 
 mui_status_t mui_gateupdown_forward(void* stream, mui_dtype_t dtype, int B, int I, int H, const void* norm_weights,
                                     float epsilon, const void* gate_weights, const void* up_weights,

@@ -26,6 +26,10 @@
 MUI_STATUS_ACCESSOR(comm)
 
 mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode, const GemvArgs& a, unsigned flags);
+mui_status_t mui_parallel_linear_forward_hinted(mui_comm_t* c, void* stream, mui_dtype_t dtype, int B, int N, int K,
+                                                const void* norm_weights, float epsilon, const void* weights,
+                                                const void* mul_bias, const void* add_bias, const void* residual,
+                                                const void* x, void* y, unsigned flags, const GemvHints* hints);
 
 struct mui_comm {
   int rank, world, device;
@@ -420,6 +424,16 @@ mui_status_t mui_parallel_linear_forward(mui_comm_t* c, void* stream, mui_dtype_
                                          const void* norm_weights, float epsilon, const void* weights,
                                          const void* mul_bias, const void* add_bias, const void* residual,
                                          const void* x, void* y, unsigned flags) {
+  return mui_parallel_linear_forward_hinted(c, stream, dtype, B, N, K, norm_weights, epsilon, weights, mul_bias,
+                                            add_bias, residual, x, y, flags, nullptr);
+}
+
+}  // extern "C"
+
+mui_status_t mui_parallel_linear_forward_hinted(mui_comm_t* c, void* stream, mui_dtype_t dtype, int B, int N, int K,
+                                                const void* norm_weights, float epsilon, const void* weights,
+                                                const void* mul_bias, const void* add_bias, const void* residual,
+                                                const void* x, void* y, unsigned flags, const GemvHints* hints) {
   if (mui_status_t s = check_ready(c)) return s;
   MUI_REQUIRE(dtype == MUI_F16 || dtype == MUI_BF16, MUI_ERR_UNSUPPORTED, "dtype %d unsupported", (int)dtype);
   MUI_REQUIRE(weights && x && y, MUI_ERR_INVALID_ARG, "weights, x and y must be non-null");
@@ -449,8 +463,11 @@ mui_status_t mui_parallel_linear_forward(mui_comm_t* c, void* stream, mui_dtype_
   a.w8_fmt = -1;
   a.use_comm = 1;
   fill_dev(c, &a.comm);
+  gemv_apply_hints(a, hints);
   return mui_launch_gemv16((cudaStream_t)stream, dtype, 0, a, flags);
 }
+
+extern "C" {
 
 mui_status_t mui_parallel_gateupdown_forward(mui_comm_t* c, void* stream, mui_dtype_t dtype, int B, int I_local, int H,
                                              const void* norm_weights, float epsilon, const void* gate_weights,

@@ -79,13 +79,6 @@ __device__ __forceinline__ void trace_end(unsigned long long* rec) {
     atomicMin(rec + 1, ~t);
   }
 }
-// Prefetch hint of the calling host thread: up to 3 matrices the NEXT GEMV launch should start pulling into L2
-// after issuing its own copies; taking the hint clears it.
-void mui_take_prefetch_hint(const void** ptrs, int* rows, int* row_bytes, int* frac1024);
-void mui_set_prefetch_skip(const int* skip_bytes, int n);
-void mui_take_prefetch_skip(int* skip_bytes);
-void mui_set_gemv_reserve_sms(int n);
-int mui_take_gemv_reserve_sms();
 // optional extra stamps of a record (words 2 and 3): earliest moment a CTA got past its wait for the previous
 // kernel, and (complemented) latest moment a CTA had its activations staged
 __device__ __forceinline__ void trace_mark(unsigned long long* rec, int word, bool complement) {

@@ -18,30 +18,8 @@
 #include "gemv_common.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 
 MUI_STATUS_ACCESSOR(gemv)
-
-// Tuning knobs of the pipeline kernel, read once from the environment (for benchmarking only):
-//   MUI_PIPE_KC      row-chunk length in elements: 2048 (default) or 1024
-//   MUI_PIPE_CTAS    CTAs per SM the grid is sized for: 1 (default) or 2
-//   MUI_PIPE_SMEM_KB shared-memory budget per CTA in KiB (default 226 of the 227 a block may have)
-static int env_int(const char* name, int dflt) {
-  const char* e = getenv(name);
-  return (e && *e) ? atoi(e) : dflt;
-}
-static int mui_pipe_kc() {
-  static int v = env_int("MUI_PIPE_KC", 2048);
-  return v;
-}
-static int mui_pipe_ctas() {
-  static int v = env_int("MUI_PIPE_CTAS", 1);
-  return v;
-}
-static int mui_pipe_smem_kb() {
-  static int v = env_int("MUI_PIPE_SMEM_KB", 226);
-  return v;
-}
 
 namespace {
 
@@ -545,11 +523,6 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
 // =============================================================================================
 // host dispatch
 // =============================================================================================
-static int mui_pipe_producers() {
-  static int v = env_int("MUI_PIPE_PRODUCERS", 1);
-  return v;
-}
-
 template <typename T, int NB, int MODE, int KC, int WB>
 mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int total_rows, int x_rows,
                          const MuiDeviceInfo* dev, bool* applicable) {
@@ -557,15 +530,10 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   // One CTA per SM with (nearly) all of its shared memory: ~190 KiB of copies in flight per SM is what keeps
   // HBM busy; with half of that the kernel runs ~25 % slower.
   // 226 KiB: with K = 14336 the staged activations (28 KiB) and three 64.25 KiB stages need 222.8 KiB
-  const int budget_small = std::min(mui_pipe_smem_kb(), 226) * 1024, budget_full = 226 * 1024;
+  // (two CTAs per SM with half-size stages measured +5 % on 8-bit weights and -3 % on 16-bit ones: not used)
+  const int budget = 226 * 1024;
   const int fixed = pipe_layout(G::STAGE_BYTES, 0, x_rows, a.Kp, NB).total;
-  int ctas_per_sm = std::max(1, std::min(2, mui_pipe_ctas()));
-  int stages = (budget_small - fixed) / G::STAGE_BYTES;
-  if (stages < 2) {
-    ctas_per_sm = 1;
-    stages = (budget_full - fixed) / G::STAGE_BYTES;
-  }
-  stages = std::min(stages, PIPE_MAX_STAGES);
+  const int stages = std::min((budget - fixed) / G::STAGE_BYTES, PIPE_MAX_STAGES);
   if (stages < 2) {
     *applicable = false;
     return MUI_OK;
@@ -574,21 +542,19 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   const PipeLayout lay = pipe_layout(G::STAGE_BYTES, stages, x_rows, a.Kp, NB);
   const int units = (total_rows + 7) / 8;  // at least one row block per CTA
   const int sms = std::max(1, dev->sm_count - std::min(a.reserve_sms, dev->sm_count / 4));
-  const int grid = std::max(1, std::min(units, sms * ctas_per_sm));
-  auto launch = [&](auto kern, int threads, bool* configured) -> mui_status_t {
-    if (!*configured) {
-      MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-      MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                          cudaSharedmemCarveoutMaxShared));
-      *configured = true;
-    }
-    MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(threads), (size_t)lay.total, stream, pdl, a, stages));
-    return MUI_OK;
-  };
-  static bool configured1 = false, configured2 = false;  // per instantiation
-  if (mui_pipe_producers() >= 2)
-    return launch(gemv_pipe_kernel<T, NB, MODE, KC, WB, 2>, GEMV_CONSUMER_THREADS + 64, &configured2);
-  return launch(gemv_pipe_kernel<T, NB, MODE, KC, WB, 1>, GEMV_CONSUMER_THREADS + 32, &configured1);
+  const int grid = std::max(1, std::min(units, sms));
+  // one producer warp: a second one doubles the issue rate of 4 KiB copies but measured no faster end to end
+  auto kern = gemv_pipe_kernel<T, NB, MODE, KC, WB, 1>;
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared));
+    configured = true;
+  }
+  MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(GEMV_CONSUMER_THREADS + 32), (size_t)lay.total, stream, pdl, a,
+                            stages));
+  return MUI_OK;
 }
 
 template <typename T, int NB, int MODE, int WB>
@@ -608,12 +574,9 @@ mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flag
   if (use_pipe) {
     bool applicable = false;
     mui_status_t st;
-    const int kc = mui_pipe_kc();
     // row chunks of 4 KiB: 2048 16-bit or 4096 8-bit weights
-    if (kc >= 2048) {
-      st = launch_pipe<T, NB, MODE, 2048 * (16 / WB), WB>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
-      if (st != MUI_OK || applicable) return st;
-    }
+    st = launch_pipe<T, NB, MODE, 2048 * (16 / WB), WB>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
+    if (st != MUI_OK || applicable) return st;
     // smaller stages when the staged activations leave no room for two 64 KiB ones
     st = launch_pipe<T, NB, MODE, 1024 * (16 / WB), WB>(stream, a, pdl, total_rows, x_rows, dev, &applicable);
     if (st != MUI_OK || applicable) return st;
@@ -668,9 +631,6 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
   if (!dev) return MUI_ERR_CUDA;
   GemvArgs a = a_in;
   if (a.trace == nullptr) a.trace = mui_trace_next_record(mode == 0 ? 1 : 2);
-  mui_take_prefetch_hint(a.pf_ptr, a.pf_rows, a.pf_row_bytes, a.pf_frac);
-  mui_take_prefetch_skip(a.pf_skip);
-  a.reserve_sms = mui_take_gemv_reserve_sms();
   const int nb = a.B <= 1 ? 1 : (a.B <= 2 ? 2 : (a.B <= 4 ? 4 : 8));
   // Activations of all batch rows are staged in shared memory; when they cannot fit (large K with B > 1), run
   // the batch in two halves (the weights are then streamed twice).

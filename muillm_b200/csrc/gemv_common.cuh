@@ -51,6 +51,30 @@ struct GemvArgs {
   CommDev comm;
 };
 
+// What a caller that knows the rest of the stream (the decode stack) tells one GEMV launch: the weight matrices of
+// the kernels that follow (pulled into L2 once the launch's own copies are issued) and how many SMs to leave free
+// for a small dependent kernel. Travels in the argument block of that launch only.
+struct GemvHints {
+  const void* pf_ptr[3];
+  int pf_rows[3];
+  int pf_row_bytes[3];
+  int pf_frac[3];  // of 1024
+  int reserve_sms;
+};
+inline void gemv_apply_hints(GemvArgs& a, const GemvHints* h) {
+  if (h == nullptr) return;
+  for (int i = 0; i < 3; ++i) {
+    const bool on = h->pf_ptr[i] != nullptr && (reinterpret_cast<uintptr_t>(h->pf_ptr[i]) & 15) == 0 &&
+                    h->pf_rows[i] > 0 && h->pf_row_bytes[i] > 0 && (h->pf_row_bytes[i] & 15) == 0 && h->pf_frac[i] > 0;
+    a.pf_ptr[i] = on ? h->pf_ptr[i] : nullptr;
+    a.pf_rows[i] = on ? h->pf_rows[i] : 0;
+    a.pf_row_bytes[i] = on ? h->pf_row_bytes[i] : 0;
+    a.pf_frac[i] = on ? (h->pf_frac[i] < 1024 ? h->pf_frac[i] : 1024) : 0;
+    a.pf_skip[i] = 0;
+  }
+  a.reserve_sms = h->reserve_sms > 0 ? h->reserve_sms : 0;
+}
+
 // expert whose weights serve computed slot `slot`
 __device__ __forceinline__ int gemv_slot_expert(const GemvArgs& a, int slot) {
   if (slot < a.num_shared) return slot;

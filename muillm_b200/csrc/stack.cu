@@ -12,7 +12,6 @@
 #include "gemv_common.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -24,6 +23,19 @@ mui_status_t mui_launch_argmax_advance(cudaStream_t stream, mui_dtype_t dtype, c
                                        void* work, int pdl, const CommDev* comm, int index_offset);
 mui_status_t mui_comm_device_view(mui_comm_t* c, CommDev* out);
 size_t mui_argmax_work_bytes(int B);
+mui_status_t mui_linear_forward_hinted(void* stream, mui_dtype_t dtype, int B, int N, int K,
+                                       const void* norm_weights, float epsilon, const void* weights,
+                                       mui_activation_t activ, const void* mul_bias, const void* add_bias,
+                                       const void* residual, const void* x, void* y, unsigned flags,
+                                       const GemvHints* hints);
+mui_status_t mui_gateup_silu_forward_hinted(void* stream, mui_dtype_t dtype, int B, int I, int H,
+                                            const void* norm_weights, float epsilon, const void* gate_weights,
+                                            const void* up_weights, const void* x, void* t, unsigned flags,
+                                            const GemvHints* hints);
+mui_status_t mui_parallel_linear_forward_hinted(mui_comm_t* c, void* stream, mui_dtype_t dtype, int B, int N, int K,
+                                                const void* norm_weights, float epsilon, const void* weights,
+                                                const void* mul_bias, const void* add_bias, const void* residual,
+                                                const void* x, void* y, unsigned flags, const GemvHints* hints);
 mui_status_t mui_llama4_qk_prologue_indexed(cudaStream_t stream, mui_dtype_t dtype, int B, int T, int Hq, int Hk, int D,
                                             const float* freqs_table, const int64_t* position_ids, int use_rope,
                                             int use_qk_norm, float norm_eps, const int64_t* cache_position,
@@ -195,27 +207,15 @@ __global__ void set_decode_state_kernel(long long* state, int32_t* seq_len32, co
   }
 }
 
-bool oproj_reserve_enabled() {
-  static const int v = [] {
-    const char* e = getenv("MUI_OPROJ_RESERVE");
-    return e ? atoi(e) : 1;  // measured on the 8B decode step: +1.6 % tokens/s
-  }();
-  return v != 0;
-}
+// Hints for the GEMV about to be launched: the weight matrices that follow it in execution order, up to `window`
+// bytes in total (a gate/up pair shares its part of the window evenly, since the kernel consumes both in step), and
+// the SMs it leaves free. 24 MB measured best on the 8B decode step (8-48 MB within 1 %, none -2 %, 96 MB -3 %).
+constexpr size_t PREFETCH_WINDOW_BYTES = (size_t)24 << 20;
 
-bool short_context_enabled() {
-  static const int v = [] {
-    const char* e = getenv("MUI_SHORT_CONTEXT");
-    return e ? atoi(e) : 1;
-  }();
-  return v != 0;
-}
-
-// Hint for the GEMV about to be launched: the weight matrices that follow it in execution order, up to `window`
-// bytes in total (a gate/up pair shares its part of the window evenly, since the kernel consumes both in step).
-void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t window) {
-  const void* ptrs[3] = {nullptr, nullptr, nullptr};
-  int rows[3] = {0, 0, 0}, rbytes[3] = {0, 0, 0}, frac[3] = {0, 0, 0};
+GemvHints make_hints(const std::vector<WeightRef>& order, size_t first, size_t window, int reserve_sms) {
+  GemvHints h;
+  memset(&h, 0, sizeof(h));
+  h.reserve_sms = reserve_sms;
   int n = 0;
   for (size_t i = first; i < order.size() && n < 3 && window > 0; ++i) {
     const size_t full = (size_t)order[i].rows * order[i].row_bytes;
@@ -224,34 +224,25 @@ void hint_prefetch(const std::vector<WeightRef>& order, size_t first, size_t win
       const size_t take = std::min(2 * full, window);
       const int f = (int)std::min<size_t>(1024, take * 1024 / (2 * full));
       for (int j = 0; j < 2; ++j) {
-        ptrs[n] = order[i + j].ptr;
-        rows[n] = order[i + j].rows;
-        rbytes[n] = order[i + j].row_bytes;
-        frac[n] = f;
+        h.pf_ptr[n] = order[i + j].ptr;
+        h.pf_rows[n] = order[i + j].rows;
+        h.pf_row_bytes[n] = order[i + j].row_bytes;
+        h.pf_frac[n] = f;
         ++n;
       }
       window -= take;
       ++i;
     } else {
       const size_t take = std::min(full, window);
-      ptrs[n] = order[i].ptr;
-      rows[n] = order[i].rows;
-      rbytes[n] = order[i].row_bytes;
-      frac[n] = (int)std::min<size_t>(1024, take * 1024 / full);
+      h.pf_ptr[n] = order[i].ptr;
+      h.pf_rows[n] = order[i].rows;
+      h.pf_row_bytes[n] = order[i].row_bytes;
+      h.pf_frac[n] = (int)std::min<size_t>(1024, take * 1024 / full);
       window -= take;
       ++n;
     }
   }
-  mui_prefetch_hint(ptrs, rows, rbytes, frac, n);
-  // the consumer's own ring (three 64 KiB stages per CTA) fetches the head of each CTA range the moment it is
-  // resident: the hint covers what comes after it. A gate/up pair shares one ring.
-  static const int skip_kb = [] {
-    const char* e = getenv("MUI_PREFETCH_SKIP_KB");
-    return e ? atoi(e) : 0;
-  }();
-  int skip[3] = {0, 0, 0};
-  for (int j = 0; j < n; ++j) skip[j] = skip_kb * 1024 / ((n >= 2 && rows[0] == rows[1] && j < 2) ? 2 : 1);
-  mui_set_prefetch_skip(skip, n);
+  return h;
 }
 
 // One decode step of a Llama-4 text model (batch 1): six launches per layer on the fused path.
@@ -288,11 +279,14 @@ mui_status_t launch_step_l4(mui_llama_stack* s, cudaStream_t stream, unsigned fl
     const int chunk = (rope && c4.chunk > 0) ? c4.chunk : 0;
     // the one-CTA-per-KV-head attention kernel serves up to 384 attended rows: always enough for a short chunk
     const int layer_attended = chunk > 0 ? std::min(attended, chunk) : attended;
-    const bool short_ctx = fused_attn && pdl && short_context_enabled() && layer_attended <= 384 && Hkv <= 16;
+    const bool short_ctx = fused_attn && pdl && layer_attended <= 384 && Hkv <= 16;
     if (s->capturing && short_ctx && !(chunk > 0 && chunk <= 384)) s->graph_short = true;
-    if (short_ctx) mui_set_gemv_reserve_sms(Hkv);
-    st = mui_linear_forward(stream, c.dtype, 1, qkv_n, H, s->ln1[l], c.rms_eps, s->qkv[l], MUI_ACT_IDENTITY, nullptr,
-                            nullptr, nullptr, s->h, s->qkv_out, flags);
+    // the attention CTAs (one per KV head) move in beside the QKV projection and are still there when o_proj starts
+    GemvHints reserve;
+    memset(&reserve, 0, sizeof(reserve));
+    reserve.reserve_sms = short_ctx ? Hkv : 0;
+    st = mui_linear_forward_hinted(stream, c.dtype, 1, qkv_n, H, s->ln1[l], c.rms_eps, s->qkv[l], MUI_ACT_IDENTITY,
+                                   nullptr, nullptr, nullptr, s->h, s->qkv_out, flags, &reserve);
     if (st != MUI_OK) return st;
     if (fused_attn) {
       st = mui_llama4_rope_flash_decode(stream, c.dtype, 1, Hq, Hkv, D, rows, c.max_seq, s->qkv_out, s->freqs,
@@ -327,13 +321,12 @@ mui_status_t launch_step_l4(mui_llama_stack* s, cudaStream_t stream, unsigned fl
                             s->v_cache[l], kvs, nullptr, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
       if (st != MUI_OK) return st;
     }
-    if (short_ctx && oproj_reserve_enabled()) mui_set_gemv_reserve_sms(Hkv);
     if (tp)
-      st = mui_parallel_linear_forward(s->comm, stream, c.dtype, 1, H, Hq * D, nullptr, 0.f, s->o[l], nullptr, nullptr,
-                                       s->h, s->attn, s->h, flags);
+      st = mui_parallel_linear_forward_hinted(s->comm, stream, c.dtype, 1, H, Hq * D, nullptr, 0.f, s->o[l], nullptr,
+                                              nullptr, s->h, s->attn, s->h, flags, &reserve);
     else
-      st = mui_linear_forward(stream, c.dtype, 1, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr, nullptr,
-                              s->h, s->attn, s->h, flags);
+      st = mui_linear_forward_hinted(stream, c.dtype, 1, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr,
+                                     nullptr, s->h, s->attn, s->h, flags, &reserve);
     if (st != MUI_OK) return st;
     st = mui_router_topk_sigmoid_forward(stream, c.dtype, c4.num_experts, H, c4.top_k, s->ln2[l], c.rms_eps,
                                          s->router[l], s->h, s->router_logits, s->router_counter, s->router_scores,
@@ -379,18 +372,19 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
   const mui_strides3_t qs = {(int64_t)qkv_n, (int64_t)D, (int64_t)qkv_n};
   const mui_strides3_t kvs = {(int64_t)Hkv * c.max_seq * D, (int64_t)c.max_seq * D, (int64_t)D};
   const size_t e = 2;
+  const size_t win = pf ? s->prefetch_window : 0;
   for (int l = 0; l < c.layers; ++l) {
-    if (pf) hint_prefetch(s->order, 5 * (size_t)l + 1, s->prefetch_window);
     // a masked (left-padded) batch takes RoPE + cache write and split-KV flash decoding as two launches
     const bool fused_attn = D == 128 && Hq / Hkv <= 8 && !(flags & MUI_FLAG_FORCE_GENERIC) && s->attn_mask == nullptr;
     // short histories: one CTA per KV head that moves in beside the QKV projection (which leaves it the SMs) and
     // has the K/V rows in shared memory by the time q arrives
     const int attended = s->capturing ? s->s_upper : s->host_pos + 1;
-    const bool short_ctx = fused_attn && pdl && short_context_enabled() && attended <= 384 && Hkv * B <= 16;
+    const bool short_ctx = fused_attn && pdl && attended <= 384 && Hkv * B <= 16;
     if (s->capturing) s->graph_short = short_ctx;
-    if (short_ctx) mui_set_gemv_reserve_sms(Hkv * B);
-    st = mui_linear_forward(stream, c.dtype, B, qkv_n, H, s->ln1[l], c.rms_eps, s->qkv[l], MUI_ACT_IDENTITY, nullptr,
-                            nullptr, nullptr, s->h, s->qkv_out, flags);
+    const int reserve = short_ctx ? Hkv * B : 0;
+    GemvHints hints = make_hints(s->order, 5 * (size_t)l + 1, win, reserve);
+    st = mui_linear_forward_hinted(stream, c.dtype, B, qkv_n, H, s->ln1[l], c.rms_eps, s->qkv[l], MUI_ACT_IDENTITY,
+                                   nullptr, nullptr, nullptr, s->h, s->qkv_out, flags, &hints);
     if (st != MUI_OK) return st;
     if (fused_attn) {
       // one launch: RoPE + cache write + attention
@@ -409,28 +403,27 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
                             s->k_cache[l], s->v_cache[l], kvs, s->attn_mask, s->attn, s->fd_ws, s->fd_ws_bytes, flags);
       if (st != MUI_OK) return st;
     }
-    if (pf) hint_prefetch(s->order, 5 * (size_t)l + 2, s->prefetch_window);
     // the attention CTAs still hold their SMs when o_proj's CTAs are placed: a full-width grid would leave its last
-    // CTAs waiting for them
-    if (short_ctx && oproj_reserve_enabled()) mui_set_gemv_reserve_sms(Hkv * B);
+    // CTAs waiting for them (measured on the 8B decode step: +1.6 % tokens/s)
+    hints = make_hints(s->order, 5 * (size_t)l + 2, win, reserve);
     if (tp)
-      st = mui_parallel_linear_forward(s->comm, stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], nullptr, nullptr,
-                                       s->h, s->attn, s->h, flags);
+      st = mui_parallel_linear_forward_hinted(s->comm, stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], nullptr,
+                                              nullptr, s->h, s->attn, s->h, flags, &hints);
     else
-      st = mui_linear_forward(stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr,
-                              nullptr, s->h, s->attn, s->h, flags);
+      st = mui_linear_forward_hinted(stream, c.dtype, B, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr,
+                                     nullptr, s->h, s->attn, s->h, flags, &hints);
     if (st != MUI_OK) return st;
-    if (pf) hint_prefetch(s->order, 5 * (size_t)l + 4, s->prefetch_window);
-    st = mui_gateup_silu_forward(stream, c.dtype, B, c.intermediate, H, s->ln2[l], c.rms_eps, s->gate[l], s->up[l],
-                                 s->h, s->t, flags);
+    hints = make_hints(s->order, 5 * (size_t)l + 4, win, 0);
+    st = mui_gateup_silu_forward_hinted(stream, c.dtype, B, c.intermediate, H, s->ln2[l], c.rms_eps, s->gate[l],
+                                        s->up[l], s->h, s->t, flags, &hints);
     if (st != MUI_OK) return st;
-    if (pf) hint_prefetch(s->order, 5 * (size_t)l + 5, s->prefetch_window);
+    hints = make_hints(s->order, 5 * (size_t)l + 5, win, 0);
     if (tp)
-      st = mui_parallel_linear_forward(s->comm, stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l],
-                                       nullptr, nullptr, s->h, s->t, s->h, flags);
+      st = mui_parallel_linear_forward_hinted(s->comm, stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l],
+                                              nullptr, nullptr, s->h, s->t, s->h, flags, &hints);
     else
-      st = mui_linear_forward(stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l], MUI_ACT_IDENTITY,
-                              nullptr, nullptr, s->h, s->t, s->h, flags);
+      st = mui_linear_forward_hinted(stream, c.dtype, B, H, c.intermediate, nullptr, 0.f, s->down[l],
+                                     MUI_ACT_IDENTITY, nullptr, nullptr, s->h, s->t, s->h, flags, &hints);
     if (st != MUI_OK) return st;
   }
   if (s->layers_only) return MUI_OK;
@@ -535,9 +528,7 @@ mui_status_t mui_llama_stack_create(const mui_llama_config_t* cfg, const mui_lla
       s->order.push_back(WeightRef{w->down[l], cfg->hidden, cfg->intermediate * 2});
     }
     s->order.push_back(WeightRef{w->lm_head, cfg->vocab, cfg->hidden * 2});
-    const char* e = getenv("MUI_PREFETCH_MB");
-    const long mb = (e && *e) ? atol(e) : 24;  // measured on the 8B decode step: 8-48 MB within 1 %, none -2 %, 96 MB -3 %
-    s->prefetch_window = mb > 0 ? (size_t)mb << 20 : 0;
+    s->prefetch_window = PREFETCH_WINDOW_BYTES;
   }
   *out = s;
   return MUI_OK;

@@ -58,19 +58,50 @@ def test_prompt_logits_close_to_hf_fp32(head_dim):
 
 def test_stack_equals_kernel_by_kernel_runner_past_the_short_context_limit():
     """400 positions (beyond the 384 rows of the one-CTA-per-KV-head attention kernel, with a chunk of 96 that the
-    ring wraps four times): the stack's tokens against the runner that chains the stand-alone kernels from Python
-    over plain caches, bf16."""
-    d, cfg, w = _load(128, dtype=torch.bfloat16)
+    ring wraps four times): the stack, stepped eagerly over the prompt and then by graph replay, against the runner
+    that chains the stand-alone kernels from Python over plain caches. Both are fed the runner's greedy tokens, so
+    every position is compared: logits within tolerance, and the same arg-max unless the runner's own logits hold the
+    two candidates within the same tolerance. A handful of steps may miss the tolerance: where two router logits of a
+    layer are one rounding step apart, the attention kernels' different summation orders can route that token to
+    another expert (seen at one step in 24 in bf16); such a step stands alone, an error in the caches would not."""
+    d, cfg, w = _load(128, dtype=torch.float16)
     cfg = dict(cfg, chunk=96)
     prompt = torch.randint(3, 256, (1, 40), generator=torch.Generator().manual_seed(5))
-    want = Llama4DecodeRunner(w, cfg, max_seq=512).greedy(prompt[0], 360).cpu()
+    steps = 400
     for flags in (0, capi.MUI_FLAG_PDL):
+        run = Llama4DecodeRunner(w, cfg, max_seq=512)
         stack = Llama4DecodeStack(w, cfg, max_seq=512, max_new_tokens=512, flags=flags)
-        got = stack.greedy(prompt, 360, use_graph=True).cpu()[0]
-        same = int((got == want).long().cumprod(0).sum().item())
-        # the fused kernel sums the scores in another order than split-KV flash decoding: a late flip of a near-tie is
-        # possible in a random-weight model, an early one is not
-        assert same >= 64, f"flags {flags}: tokens equal the runner's for only {same} positions"
+        stack.reset(0)
+        side = torch.cuda.Stream()
+        tok = int(prompt[0, 0])
+        flips, outliers = 0, []
+        for t in range(steps):
+            ref = run.step(tok).float()
+            tt = torch.tensor([tok], dtype=torch.int64)
+            if t < prompt.shape[1]:
+                stack.set_tokens(tt)
+                stack.step()
+            else:
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    if t == prompt.shape[1]:
+                        stack.capture()
+                    stack.set_tokens(tt)
+                    stack.replay(1)
+                torch.cuda.current_stream().wait_stream(side)
+            got = stack.logits().float()
+            err = float((got - ref).abs().max())
+            a, b = int(torch.argmax(ref)), int(stack.next_tokens()[0].item())
+            if err > 3e-2:
+                outliers.append((t, round(err, 3)))
+            elif a != b:
+                assert float(ref[0, a] - ref[0, b]) < 3e-2, f"flags {flags} step {t}: runner {a}, stack {b}"
+                flips += 1
+            tok = int(prompt[0, t + 1]) if t + 1 < prompt.shape[1] else a
+        assert len(outliers) <= 6, f"flags {flags}: logits off at steps {outliers}"
+        assert all(t2 - t1 > 1 for (t1, _), (t2, _) in zip(outliers, outliers[1:])), \
+            f"flags {flags}: consecutive steps off: {outliers}"
+        assert flips <= 8, f"flags {flags}: {flips} arg-max flips in {steps} steps"
     assert capi.device_status() == 0
 
 
