@@ -205,7 +205,6 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS) gemv_generic_kernel(con
 // stage costs each consumer warp a few dozen instructions; at the end of a row block the warps' partial
 // tiles are summed through shared memory in a fixed order.
 constexpr int PIPE_ROWS = 16;
-constexpr int PIPE_MAX_PRODUCERS = 2;
 constexpr int PIPE_MAX_STAGES = 8;
 constexpr int PIPE_XPAD = 8;  // elements of padding per staged activation row (bank spread for ldmatrix)
 
@@ -231,6 +230,8 @@ __host__ __device__ inline PipeLayout pipe_layout(int stage_bytes, int stages, i
   l.total = l.abort_off + 16;
   return l;
 }
+
+#include "gemv_xchunk.cuh"
 
 template <typename T, int NB, int MODE, int KC, int WB, int NPROD>
 __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_kernel(const GemvArgs a,
@@ -325,21 +326,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
       }
     }
     if (ok && prod == 0) {
-      // L2 prefetch of what comes next on the stream: for each hinted matrix the head of the row range this CTA
-      // index owns in the kernel that will consume it (same even row split), 8 KiB per request
-#pragma unroll
-      for (int sgm = 0; sgm < 3; ++sgm) {
-        if (a.pf_ptr[sgm] == nullptr || a.pf_frac[sgm] <= 0) continue;
-        const long long rows = a.pf_rows[sgm], rbytes = a.pf_row_bytes[sgm];
-        const long long pr0 = rows * blockIdx.x / gridDim.x, pr1 = rows * (blockIdx.x + 1) / gridDim.x;
-        const long long total = (pr1 - pr0) * rbytes;
-        const long long skip = min(static_cast<long long>(a.pf_skip[sgm]) & ~15ll, total);
-        const long long b0 = pr0 * rbytes + skip;
-        const long long nb = min((total * a.pf_frac[sgm] / 1024) & ~15ll, total - skip);
-        const unsigned char* base = reinterpret_cast<const unsigned char*>(a.pf_ptr[sgm]) + b0;
-        for (long long off = (long long)lane * 8192; off < nb; off += 32 * 8192)
-          bulk_prefetch_l2(base + off, static_cast<uint32_t>(min(8192ll, nb - off)));
-      }
+      pipe_prefetch_next(a, lane);
     }
     if (!ok && lane == 0 && prod == 0) {
       // leave no copy in flight behind: wait (bounded) for every stage that was armed
@@ -557,6 +544,30 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   return MUI_OK;
 }
 
+// Chunk-staged batched variant (gemv_xchunk.cuh)
+template <typename T, int NB, int MODE, int WB>
+mui_status_t launch_xchunk(cudaStream_t stream, const GemvArgs& a, int pdl, const MuiDeviceInfo* dev) {
+  using G = XcGeom<WB>;
+  const int budget = 226 * 1024;
+  const int fixed = xc_layout(G::STAGE_BYTES, 0, NB).total;
+  const int stages = std::min((budget - fixed) / G::STAGE_BYTES, PIPE_MAX_STAGES);
+  const XcLayout lay = xc_layout(G::STAGE_BYTES, stages, NB);
+  const int units = (a.N + 7) / 8;
+  const int sms = std::max(1, dev->sm_count - std::min(a.reserve_sms, dev->sm_count / 4));
+  const int grid = std::max(1, std::min(units, sms));
+  auto kern = gemv_pipe_xchunk_kernel<T, NB, MODE, WB>;
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared));
+    configured = true;
+  }
+  MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(GEMV_CONSUMER_THREADS + 32), (size_t)lay.total, stream, pdl, a,
+                            stages));
+  return MUI_OK;
+}
+
 template <typename T, int NB, int MODE, int WB>
 mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flags, const MuiDeviceInfo* dev) {
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
@@ -571,6 +582,20 @@ mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flag
                        (MODE == 0 || (reinterpret_cast<uintptr_t>(a.W2) & 15) == 0) &&
                        (WB == 16 || a.w8_fmt == MUI_W8_SYM_ROW);
   bool use_pipe = aligned && !(flags & MUI_FLAG_FORCE_GENERIC);
+  if constexpr (NB >= 2) {
+    if (use_pipe && a.moe_mode == GEMV_MOE_NONE && ((a.K & 7) == 0) &&
+        ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) &&
+        (a.norm_w == nullptr || (reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0)) {
+      // batches: stage the activations chunk by chunk whenever whole rows would leave the weight ring fewer than
+      // three full stages (16-bit weights) or fewer than two (8-bit weights: their chunked row copies are 2 KiB,
+      // which the copy engine ingests more slowly; measured at the Llama-3-8B MLP shape, two whole-row stages
+      // still win there)
+      using G = PipeGeom<2048 * (16 / WB), WB>;
+      const int fixed = pipe_layout(G::STAGE_BYTES, 0, x_rows, a.Kp, NB).total;
+      if ((226 * 1024 - fixed) / G::STAGE_BYTES < (WB == 16 ? 3 : 2))
+        return launch_xchunk<T, NB, MODE, WB>(stream, a, pdl, dev);
+    }
+  }
   if (use_pipe) {
     bool applicable = false;
     mui_status_t st;
@@ -632,9 +657,17 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
   GemvArgs a = a_in;
   if (a.trace == nullptr) a.trace = mui_trace_next_record(mode == 0 ? 1 : 2);
   const int nb = a.B <= 1 ? 1 : (a.B <= 2 ? 2 : (a.B <= 4 ? 4 : 8));
-  // Activations of all batch rows are staged in shared memory; when they cannot fit (large K with B > 1), run
-  // the batch in two halves (the weights are then streamed twice).
-  if (a.B > 1 && a.moe_mode == GEMV_MOE_NONE && (size_t)nb * (a.Kp + 8) * 2 > 150 * 1024) {
+  // The pipeline stages a batch's activations chunk by chunk. The plain-load kernel (odd K, unaligned pointers, the
+  // per-group 8-bit format, or when forced) stages whole rows: when those cannot fit, it runs the batch in two
+  // halves (the weights are then streamed twice).
+  const int kstep = (a.w8_fmt < 0) ? 16 : 32;
+  const bool pipeline_ok = !(flags & MUI_FLAG_FORCE_GENERIC) && (a.K % kstep) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(a.W) & 15) == 0) &&
+                           (mode == 0 || (reinterpret_cast<uintptr_t>(a.W2) & 15) == 0) &&
+                           (a.w8_fmt < 0 || a.w8_fmt == MUI_W8_SYM_ROW) &&
+                           ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) &&
+                           (a.norm_w == nullptr || (reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0);
+  if (a.B > 1 && a.moe_mode == GEMV_MOE_NONE && !pipeline_ok && (size_t)nb * (a.Kp + 8) * 2 > 150 * 1024) {
     const int h = a.B / 2;
     GemvArgs lo = a, hi = a;
     lo.trace = hi.trace = nullptr;

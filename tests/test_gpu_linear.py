@@ -158,3 +158,46 @@ def test_linear_full_size_linearity():
     rows = torch.randint(0, N, (64,), generator=g)
     want = oracle.linear(x1.cpu(), W[rows.cuda()].cpu())
     _close(y1[:, rows.cuda()].to(dtype), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,N,K,norm", [
+    (8, 8192, 14336, False),   # down projection of the 70B architecture cut in two: did not fit whole-row staging
+    (8, 2560, 8192, True),     # QKV of the 70B architecture cut in four, fused norm
+    (3, 4096, 2064, False),    # ragged last chunk (2064 = 2048 + 16)
+    (2, 40000, 2048, True),    # 271 rows per CTA: 17 row blocks, two groups of accumulators
+    (5, 515, 4096, True),      # rows not a multiple of the tile, batch padded to 8
+])
+def test_linear_batches_staged_chunk_by_chunk(dtype, B, N, K, norm):
+    """Batches whose activations the pipeline stages one 2048-element chunk at a time (whole rows would leave the
+    weight ring less than three stages): every epilogue term, with and without the fused norm, with dependent launch."""
+    g = _gen(B + N)
+    x = torch.randn(B, K, generator=g).to(dtype)
+    W = _mk((N, K), g, 0.02, dtype)
+    nw = (1 + 0.01 * torch.randn(K, generator=g)).to(dtype) if norm else None
+    res = _mk((B, N), g, 1.0, dtype)
+    ab = _mk((N,), g, 0.5, dtype)
+    want = oracle.linear(x, W, norm_weights=nw, eps=1e-5, add_bias=ab, residual=res)
+    for flags in (capi.MUI_FLAG_FORCE_PIPELINE, capi.MUI_FLAG_FORCE_PIPELINE | capi.MUI_FLAG_PDL):
+        got = ops.muillm_linear_forward(None, x.cuda(), W.cuda(), norm_weights=None if nw is None else nw.cuda(),
+                                        epsilon=1e-5, add_bias=ab.cuda(), residual=res.cuda(), flags=flags)
+        _close(got, want)
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,I,H", [(8, 14336, 8192), (4, 20000, 4096), (2, 1000, 8192)])
+def test_gateup_batches_staged_chunk_by_chunk(dtype, B, I, H):
+    """Gate/up + SiLU for batches at the 70B shard shape (97 gate rows per CTA: 13 row blocks) and with more row blocks
+    per CTA than one group of accumulators holds (136 rows: 17 blocks)."""
+    g = _gen(I + B)
+    x = torch.randn(B, H, generator=g).to(dtype)
+    nw = (1 + 0.01 * torch.randn(H, generator=g)).to(dtype)
+    G = _mk((I, H), g, 0.02, dtype)
+    U = _mk((I, H), g, 0.02, dtype)
+    want = oracle.gateup_silu(x, G, U, norm_weights=nw, eps=1e-5)
+    Gc, Uc = G.cuda(), U.cuda()
+    for flags in (capi.MUI_FLAG_FORCE_PIPELINE, capi.MUI_FLAG_FORCE_PIPELINE | capi.MUI_FLAG_PDL):
+        got = ops.gateup_silu(x.cuda(), Gc, Uc, norm_weights=nw.cuda(), epsilon=1e-5, flags=flags)
+        _close(got, want)
+    assert capi.device_status() == 0

@@ -72,7 +72,8 @@ def _case_all_reduce_and_broadcast(rank, world, comm):
 
 def _case_parallel_linear(rank, world, comm):
     for dtype in (torch.float16, torch.bfloat16):
-        for (B, N, K) in ((1, 4096, 4096), (1, 8192, 1024 * world), (4, 515, 256 * world), (1, 128, 8 * world)):
+        for (B, N, K) in ((1, 4096, 4096), (1, 8192, 1024 * world), (4, 515, 256 * world), (1, 128, 8 * world),
+                          (8, 2048, 4096 * world)):  # the last one: activations staged chunk by chunk
             g = torch.Generator().manual_seed(N + K + B)
             W = (torch.randn(N, K, generator=g) * 0.02).to(dtype)
             x = torch.randn(B, K, generator=g).to(dtype)
