@@ -516,6 +516,11 @@ MUI_API int mui_llama4_stack_cache_rows(const mui_llama4_config_t* cfg, int use_
 MUI_API size_t mui_llama4_stack_scratch_bytes(const mui_llama4_config_t* cfg);
 MUI_API mui_status_t mui_llama4_stack_create(const mui_llama4_config_t* cfg, const mui_llama4_weights_t* weights,
                                              void* scratch, size_t scratch_bytes, mui_llama_stack_t** out);
+/* Device pointers of the last step's router outputs: logits [layers, num_experts] (fp32, rounded to the model
+ * dtype) and the chosen experts [layers, 8] (int64, the first top_k of each row). Routing is the one discontinuous
+ * step of the model; two runs whose tokens differ can be compared layer by layer with these. */
+MUI_API mui_status_t mui_llama4_stack_router_state(mui_llama_stack_t* stack, float** logits_dev,
+                                                   int64_t** indices_dev);
 /* Tensor-parallel decode: with a communicator of world > 1 attached, the weights are this rank's shards — QKV and
  * gate/up by output rows (whole heads per rank), o_proj and down by input columns with the all-reduce fused into
  * their GEMV (residual on rank 0), lm_head by rows with the arg-max finished by exchanging each rank's best

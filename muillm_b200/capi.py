@@ -242,6 +242,7 @@ PROTOTYPES = {
     "mui_llama4_stack_scratch_bytes": (c_size_t, [POINTER(Llama4Config)]),
     "mui_llama4_stack_create": (
         c_int, [POINTER(Llama4Config), POINTER(Llama4Weights), c_void_p, c_size_t, POINTER(c_void_p)]),
+    "mui_llama4_stack_router_state": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p)]),
     "mui_llama4_rope_flash_decode": (
         c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                 c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_uint]),

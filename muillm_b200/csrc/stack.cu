@@ -83,10 +83,11 @@ struct mui_llama_stack {
   std::vector<const void*> router;
   std::vector<int> use_rope, cache_rows;
   const float* freqs;
-  float* router_logits;           // [num_experts]
+  // router outputs of the last step, kept per layer (the caller can read them back, mui_llama4_stack_router_state)
+  float* router_logits;           // [layers][num_experts]
   unsigned int* router_counter;   // arrival counter of the router kernel (zero between launches)
-  void* router_scores;            // [top_k] 16-bit
-  long long* router_idx;          // [top_k]
+  unsigned char* router_scores;   // [layers][8] 16-bit
+  long long* router_idx;          // [layers][8]
   long long* chunk_row;           // separate-launch attention path: cache row and attended length of the chunked
   int32_t* chunk_len32;           //   layers for the current step
 };
@@ -102,6 +103,7 @@ struct ScratchLayout {
 // t_rows: rows of the MLP intermediate (1 for a dense MLP, computed experts for MoE); router_experts > 0 adds the
 // router scratch and the rotated-key row of the separate-launch Llama-4 attention path
 ScratchLayout scratch_layout(const mui_llama_config_t& c, int t_rows = 1, int router_experts = 0) {
+  const size_t L = c.layers;
   ScratchLayout l;
   const size_t B = c.batch, e = 2;
   size_t off = 0;
@@ -123,8 +125,9 @@ ScratchLayout scratch_layout(const mui_llama_config_t& c, int t_rows = 1, int ro
   l.argmax_work = take(mui_argmax_work_bytes(c.batch));
   l.router = l.k_rot = 0;
   if (router_experts > 0) {
-    // [0,64): counter; [64,128): chunk row (int64) + chunk length (int32); [256, ...): logits fp32, scores, indices
-    l.router = take(256 + (size_t)router_experts * 4 + 64 * 2 + 64 * 8);
+    // [0,64): counter; [64,128): chunk row (int64) + chunk length (int32); [256, ...): per layer 8 indices (int64),
+    // then per layer 8 scores (16 bytes), then per layer the logits (fp32)
+    l.router = take(256 + L * 64 + L * 16 + L * (size_t)router_experts * 4);
     l.k_rot = take(B * (size_t)c.kv_heads * c.head_dim * e);
   }
   l.total = off;
@@ -328,19 +331,20 @@ mui_status_t launch_step_l4(mui_llama_stack* s, cudaStream_t stream, unsigned fl
       st = mui_linear_forward_hinted(stream, c.dtype, 1, H, Hq * D, nullptr, 0.f, s->o[l], MUI_ACT_IDENTITY, nullptr,
                                      nullptr, s->h, s->attn, s->h, flags, &reserve);
     if (st != MUI_OK) return st;
+    float* r_logits = s->router_logits + (size_t)l * c4.num_experts;
+    void* r_scores = s->router_scores + (size_t)l * 16;
+    int64_t* r_idx = reinterpret_cast<int64_t*>(s->router_idx + (size_t)l * 8);
     st = mui_router_topk_sigmoid_forward(stream, c.dtype, c4.num_experts, H, c4.top_k, s->ln2[l], c.rms_eps,
-                                         s->router[l], s->h, s->router_logits, s->router_counter, s->router_scores,
-                                         reinterpret_cast<int64_t*>(s->router_idx), flags);
+                                         s->router[l], s->h, r_logits, s->router_counter, r_scores, r_idx, flags);
     if (st != MUI_OK) return st;
     if (tp)
       st = mui_parallel_moe_mlp_forward(s->comm, stream, c.dtype, c4.num_shared, c4.num_experts, c4.top_k, I, H,
                                         s->ln2[l], c.rms_eps, s->gate[l], s->up[l], s->down[l], s->h, s->h,
-                                        s->router_scores, reinterpret_cast<const int64_t*>(s->router_idx), s->t, s->h,
+                                        r_scores, r_idx, s->t, s->h,
                                         flags);
     else
       st = mui_moe_mlp_forward(stream, c.dtype, c4.num_shared, c4.num_experts, c4.top_k, I, H, s->ln2[l], c.rms_eps,
-                               s->gate[l], s->up[l], s->down[l], s->h, s->h, s->router_scores,
-                               reinterpret_cast<const int64_t*>(s->router_idx), s->t, s->h, flags);
+                               s->gate[l], s->up[l], s->down[l], s->h, s->h, r_scores, r_idx, s->t, s->h, flags);
     if (st != MUI_OK) return st;
   }
   if (s->layers_only) return MUI_OK;
@@ -611,9 +615,9 @@ mui_status_t mui_llama4_stack_create(const mui_llama4_config_t* cfg4, const mui_
   s->router_counter = reinterpret_cast<unsigned int*>(base + lay.router);
   s->chunk_row = reinterpret_cast<long long*>(base + lay.router + 64);
   s->chunk_len32 = reinterpret_cast<int32_t*>(base + lay.router + 72);
-  s->router_idx = reinterpret_cast<long long*>(base + lay.router + 128);   // up to 8 indices
-  s->router_scores = base + lay.router + 192;                              // up to 8 16-bit scores
-  s->router_logits = reinterpret_cast<float*>(base + lay.router + 256);
+  s->router_idx = reinterpret_cast<long long*>(base + lay.router + 256);
+  s->router_scores = base + lay.router + 256 + (size_t)cfg.layers * 64;
+  s->router_logits = reinterpret_cast<float*>(base + lay.router + 256 + (size_t)cfg.layers * 80);
   s->out_tokens = nullptr;
   s->out_capacity = 0;
   s->s_upper = cfg.max_seq;
@@ -628,6 +632,13 @@ mui_status_t mui_llama4_stack_create(const mui_llama4_config_t* cfg4, const mui_
   s->attn_mask = nullptr;
   s->prefetch_window = 0;
   *out = s;
+  return MUI_OK;
+}
+
+mui_status_t mui_llama4_stack_router_state(mui_llama_stack_t* s, float** logits_dev, int64_t** indices_dev) {
+  MUI_REQUIRE(s != nullptr && s->l4, MUI_ERR_INVALID_ARG, "not a Llama-4 stack");
+  if (logits_dev) *logits_dev = s->router_logits;
+  if (indices_dev) *indices_dev = reinterpret_cast<int64_t*>(s->router_idx);
   return MUI_OK;
 }
 

@@ -330,6 +330,18 @@ class Llama4DecodeStack(LlamaDecodeStack):
             capi.check(self.lib.mui_llama_stack_set_comm(h, comm.handle))
         self.reset(0)
 
+    def router_state(self):
+        """Views of the last step's router outputs: logits [layers, experts] (fp32) and chosen experts
+        [layers, top_k] (int64)."""
+        lp, ip = c_void_p(), c_void_p()
+        capi.check(self.lib.mui_llama4_stack_router_state(self._h, ctypes.byref(lp), ctypes.byref(ip)))
+        L, E = self.cfg["layers"], self.cfg["experts"]
+        lo = lp.value - self.scratch.data_ptr()
+        io = ip.value - self.scratch.data_ptr()
+        logits = self.scratch[lo: lo + 4 * L * E].view(torch.float32).view(L, E)
+        idx = self.scratch[io: io + 8 * L * 8].view(torch.int64).view(L, 8)[:, : self.cfg["top_k"]]
+        return logits, idx
+
     @property
     def launches_per_step(self):
         """embedding, per layer {QKV, attention, o_proj, router + top-k, expert gate/up, expert down}, lm_head,
