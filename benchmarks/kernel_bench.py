@@ -96,7 +96,7 @@ def case_down_w8(name, H, I, B, dtype, dev, g, flags):
     return name, _time_graph(fns, 4 * L), nbytes
 
 
-def case_attention(name, S, dtype, dev, g, flags, short=False):
+def case_attention(name, S, dtype, dev, g, flags, short=False, split=False):
     B, Hq, Hkv, D, max_T = 1, 32, 8, 128, 4096
     L = 12
     qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device=dev, generator=g).to(dtype)
@@ -107,9 +107,14 @@ def case_attention(name, S, dtype, dev, g, flags, short=False):
     pos = torch.full((B,), S - 1, dtype=torch.int64, device=dev)
     cpos = torch.tensor([S - 1], dtype=torch.int64, device=dev)
     sl = torch.tensor([S], dtype=torch.int32, device=dev)
+    ws = None
     if short:
         flags = flags | capi.MUI_FLAG_SHORT_CONTEXT
-    fns = [(lambda kc=kc, vc=vc: ops.rope_flash_decode(qkv, cos, sin, pos, cpos, sl, kc, vc, Hq, flags=flags))
+    if split:
+        flags = flags | capi.MUI_FLAG_SPLIT_CONTEXT
+        ws = torch.zeros(capi.lib().mui_flash_decode_workspace_bytes(B, Hq, Hkv, D, max_T), dtype=torch.uint8, device=dev)
+    fns = [(lambda kc=kc, vc=vc: ops.rope_flash_decode(qkv, cos, sin, pos, cpos, sl, kc, vc, Hq, flags=flags,
+                                                       workspace=ws, max_attended=S))
            for kc, vc in caches]
     nbytes = 2 * B * Hkv * S * D * 2 + (Hq + 2 * Hkv) * D * 2 + Hq * D * 2
     return name, _time_graph(fns, 4 * L), nbytes
@@ -162,6 +167,8 @@ def run(dtype=torch.float16):
         add(case_attention(f"rope+cache+attention 32q/8kv d128, S={S}", S, dtype, dev, g, flags))
     for S in (64, 256, 384):
         add(case_attention(f"rope+cache+attention, one CTA per KV head, S={S}", S, dtype, dev, g, flags, short=True))
+    for S in (1024, 2048, 4096):
+        add(case_attention(f"rope+cache+attention, tokens split over CTAs, S={S}", S, dtype, dev, g, flags, split=True))
     add(case_moe("MoE MLP shared+top-1 of 16, H=5120 I=2048, bf16", 5120, 2048, 1, 16, torch.bfloat16, dev, g, flags))
     assert capi.device_status() == 0
     return rows
@@ -170,11 +177,17 @@ def run(dtype=torch.float16):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
+    ap.add_argument("--md", default=None, help="also write the table as markdown rows")
     args = ap.parse_args()
     rows = run()
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)
+    if args.md:
+        with open(args.md, "w") as f:
+            f.write("| case | us per launch | GB/s | of 8 TB/s |\n|---|---|---|---|\n")
+            for r in rows:
+                f.write(f"| {r['case']} | {r['us']:.2f} | {r['gbs']:.1f} | {r['of_8tbs']:.3f} |\n")
 
 
 if __name__ == "__main__":

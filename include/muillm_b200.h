@@ -50,6 +50,9 @@ typedef enum { MUI_W8_SYM_ROW = 0, MUI_W8_GROUP_MIN = 1 } mui_w8_format_t;
                                     of this kernel with the tail of the previous kernel on the stream) */
 #define MUI_FLAG_FORCE_GENERIC 2u /* use the plain-load kernel even where the bulk-copy pipeline applies */
 #define MUI_FLAG_FORCE_PIPELINE 4u /* fail with MUI_ERR_UNSUPPORTED instead of falling back to the plain-load kernel */
+#define MUI_FLAG_SPLIT_CONTEXT 32u  /* fused decode attention with a workspace: the tokens in view are split over several
+                                      CTAs per KV head (about 256 each), each running the tensor-core kernel of
+                                      MUI_FLAG_SHORT_CONTEXT on its part; the last one to arrive merges the parts */
 #define MUI_FLAG_SHORT_CONTEXT 16u  /* mui_rope_flash_decode / decode stack: at most a few hundred tokens are attended;
                                       one CTA per KV head stages the whole K/V history in shared memory (up to 384 rows
                                       per round) before the QKV projection has finished. Correct for any length. */
@@ -117,6 +120,21 @@ MUI_API mui_status_t mui_gateupdown_forward(void* stream, mui_dtype_t dtype, int
                                             const void* norm_weights, float epsilon, const void* gate_weights,
                                             const void* up_weights, const void* down_weights, const void* residual,
                                             const void* x, void* scratch_t, void* y, unsigned flags);
+
+/* ---- prefill / batched rows (more than 8) on the tcgen05 tensor cores --------------------------------
+ * Same math as mui_linear_forward (without the fused norm: normalise with mui_rmsnorm_forward first) and
+ * mui_gateup_silu_forward for M rows of x [M, K] (prompt tokens): one kernel, weights streamed once per 256 rows,
+ * TMA tile loads into 128-byte-swizzled shared-memory stages, tcgen05.mma with fp32 accumulators in tensor memory.
+ * K % 8 == 0; weights, x 16-byte aligned. The call builds the tensor maps of its operands on the host (a few
+ * microseconds). Stands where the reference falls back to at::linear for more than one token
+ * (csrc/modules/linear_module.cpp:61-77, csrc/modules/parallel_linear_module.cpp:73-83). */
+MUI_API mui_status_t mui_prefill_linear_forward(void* stream, mui_dtype_t dtype, int M, int N, int K,
+                                                const void* weights, mui_activation_t activ, const void* mul_bias,
+                                                const void* add_bias, const void* residual, const void* x, void* y,
+                                                unsigned flags);
+MUI_API mui_status_t mui_prefill_gateup_silu_forward(void* stream, mui_dtype_t dtype, int M, int I, int H,
+                                                     const void* gate_weights, const void* up_weights, const void* x,
+                                                     void* t, unsigned flags);
 
 /* ---- (a3/a5) weight-only 8-bit GEMV and gate/up ---------------------------------------------------
  * Same math as mui_linear_forward / mui_gateup_silu_forward on de-quantised weights.
@@ -204,6 +222,20 @@ MUI_API mui_status_t mui_rope_flash_decode(void* stream, mui_dtype_t dtype, int 
                                            const int32_t* seq_len_dev, float scale, void* k_cache, void* v_cache,
                                            void* out, unsigned flags);
 
+/* mui_rope_flash_decode with a workspace (mui_flash_decode_workspace_bytes bytes, first 4 KiB zero before the first
+ * call) and an upper bound `max_attended` of the tokens the launch (or every replay of it in a CUDA graph) will
+ * attend. With MUI_FLAG_SPLIT_CONTEXT the tokens are split over ceil(max_attended / 256) CTAs per (KV head, sequence)
+ * (at most 64, i.e. 16384 tokens; beyond that the cluster kernel runs): each stages its tokens in shared memory and
+ * runs QK^T and PV on the tensor cores, the last one to arrive merges the partial (max, denominator, output) triples
+ * by log-sum-exp. For a few thousand tokens this is three to four times faster than the cluster kernel, which keeps
+ * one cluster per KV head whatever the length. */
+MUI_API mui_status_t mui_rope_flash_decode_ws(void* stream, mui_dtype_t dtype, int B, int Hq, int Hkv, int D,
+                                              int max_seq, const void* qkv, const void* cos_table,
+                                              const void* sin_table, const int64_t* position_ids,
+                                              const int64_t* cache_position, const int32_t* seq_len_dev, float scale,
+                                              void* k_cache, void* v_cache, void* out, void* workspace,
+                                              size_t workspace_bytes, int max_attended, unsigned flags);
+
 /* The same fused launch for a Llama-4 attention layer: instead of the rotate-half RoPE, q and the new k go through
  * the Llama-4 prologue — interleaved-pair rotation by freqs[position] ([max_pos, D/2, 2] fp32 (cos, sin); use_rope),
  * L2 norm over the head dim (use_qk_norm, norm_eps), and for q the temperature scale
@@ -212,7 +244,8 @@ MUI_API mui_status_t mui_rope_flash_decode(void* stream, mui_dtype_t dtype, int 
  * the layer's caches [B, Hkv, cache_rows, D] are a ring indexed by cache_position % chunk and the token attends the
  * rows of its own chunk, rows 0 .. cache_position % chunk (chunked attention; cache_rows >= min(chunk, longest
  * sequence)); with chunk == 0 the cache is plain and rows 0 .. cache_position are attended. cache_position [1] is the
- * absolute position of the new token. D == 128, Hq / Hkv <= 8. One launch where the reference's
+ * absolute position of the new token. D == 128, Hq / Hkv <= 8. workspace / workspace_bytes / max_attended as in
+ * mui_rope_flash_decode_ws (workspace may be NULL without MUI_FLAG_SPLIT_CONTEXT). One launch where the reference's
  * MuiLLMParallelLlama4Attention::forward chains rope, QK norm, temperature tuning, the hybrid chunked cache update and
  * flash decoding (csrc/modules/parallel_llama4_attention_module.cpp:66-147,
  * csrc/modules/hybrid_chunked_kvcache.cpp:23-77). */
@@ -222,6 +255,7 @@ MUI_API mui_status_t mui_llama4_rope_flash_decode(void* stream, mui_dtype_t dtyp
                                                   int use_rope, int use_qk_norm, float norm_eps,
                                                   int temperature_tuning, float attn_scale, float floor_scale,
                                                   int chunk, float scale, void* k_cache, void* v_cache, void* out,
+                                                  void* workspace, size_t workspace_bytes, int max_attended,
                                                   unsigned flags);
 
 /* Flash decoding for callers that may not allocate device memory. No counterpart in the reference (there,

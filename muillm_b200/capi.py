@@ -34,6 +34,7 @@ MUI_FLAG_PDL = 1
 MUI_FLAG_FORCE_GENERIC = 2
 MUI_FLAG_FORCE_PIPELINE = 4
 MUI_FLAG_SHORT_CONTEXT = 16
+MUI_FLAG_SPLIT_CONTEXT = 32
 
 
 class Strides3(Structure):
@@ -157,6 +158,11 @@ PROTOTYPES = {
         [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_uint],
     ),
+    "mui_rope_flash_decode_ws": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_uint],
+    ),
     "mui_flash_decode_static_scratch": (
         c_int,
         [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
@@ -242,10 +248,16 @@ PROTOTYPES = {
     "mui_llama4_stack_scratch_bytes": (c_size_t, [POINTER(Llama4Config)]),
     "mui_llama4_stack_create": (
         c_int, [POINTER(Llama4Config), POINTER(Llama4Weights), c_void_p, c_size_t, POINTER(c_void_p)]),
+    "mui_prefill_linear_forward": (
+        c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_uint]),
+    "mui_prefill_gateup_silu_forward": (
+        c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_uint]),
     "mui_llama4_stack_router_state": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p)]),
     "mui_llama4_rope_flash_decode": (
         c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_uint]),
+                c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_size_t, c_int, c_uint]),
     "mui_router_topk_sigmoid_forward": (
         c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                 c_void_p, c_void_p, c_uint]),

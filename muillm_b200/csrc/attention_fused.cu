@@ -45,6 +45,11 @@ struct FaArgs {
   // indexed by position % chunk and the token attends the rows of its own chunk only.
   const float* freqs;  // [max_pos, D/2, 2] (cos, sin)
   int max_pos;         // rows of the rotary table
+  // token-split variant of the one-CTA-per-KV-head kernel (gridDim.z > 1): arrival counters [B * Hkv] (zero between
+  // launches) and fp32 partials [B, Hq, max_splits, D + 2] = (max, denominator, unnormalised output)
+  unsigned int* counters;
+  float* partials;
+  int max_splits;
   int l4, chunk;
   float eps, attn_scale, floor_scale;
 };
@@ -423,13 +428,26 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(
   const long long pos_id = __ldcg(a.position_ids + b);
   const long long abs_pos = __ldcg(a.cache_position);
   const long long cache_pos = (a.l4 && a.chunk > 0) ? abs_pos % a.chunk : abs_pos;
-  const int S = a.l4 ? static_cast<int>(min(cache_pos + 1, (long long)a.max_seq))
-                     : min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
+  const int S_all = a.l4 ? static_cast<int>(min(cache_pos + 1, (long long)a.max_seq))
+                         : min(max(__ldcg(a.seq_len_dev), 1), a.max_seq);
+  // Token split (gridDim.z > 1): this CTA attends tokens [tok_begin, tok_begin + S) of the S_all in view; the CTA
+  // whose range ends the sequence holds the new token. Chunks are multiples of 16 tokens and at least 64, so short
+  // sequences use few of the launched CTAs.
+  const int split = blockIdx.z;
+  int chunk = S_all, n_active = 1;
+  if (gridDim.z > 1) {
+    chunk = max(64, ((S_all + (int)gridDim.z - 1) / (int)gridDim.z + 15) & ~15);
+    n_active = (S_all + chunk - 1) / chunk;
+  }
+  if (split >= n_active) return;
+  const int tok_begin = split * chunk;
+  const int S = min(S_all, tok_begin + chunk) - tok_begin;  // rows of this CTA, the new token included if it owns it
+  const bool own_new = (split == n_active - 1);
   if (S > RA_ROWS || abs_pos < 0 || cache_pos >= a.max_seq || pos_id < 0 || pos_id >= a.max_pos) {
-    if (tid == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(S));
+    if (tid == 0) mui_dev_set_status(MUI_DEV_BAD_LENGTH, static_cast<unsigned>(S_all));
     return;
   }
-  const int cached = S - 1;
+  const int cached = own_new ? S - 1 : S;  // rows that come from the cache
   T* kc = reinterpret_cast<T*>(a.k_cache) + ((size_t)b * a.Hkv + kvh) * a.max_seq * FA_D;
   T* vc = reinterpret_cast<T*>(a.v_cache) + ((size_t)b * a.Hkv + kvh) * a.max_seq * FA_D;
   // 16-byte asynchronous copies (cp.async): each lands at its padded position; a bulk copy could not pad, and one
@@ -440,7 +458,7 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(
     for (int i = tid; i < pieces; i += FA_THREADS) {
       const int r = i >> 4, c = (i & 15) * 8;
       const uint32_t so = static_cast<uint32_t>((r * RA_PITCH + c) * 2);
-      const size_t go = (size_t)r * FA_D + c;
+      const size_t go = (size_t)(tok_begin + r) * FA_D + c;
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks_u + so), "l"(kc + go) : "memory");
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs_u + so), "l"(vc + go) : "memory");
     }
@@ -492,10 +510,10 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(
     const uint4 rot = pack8<T>(x);
     if (slot < G) {
       *reinterpret_cast<uint4*>(Qs + (size_t)slot * FA_D + d0) = rot;
-    } else if (slot == G) {
+    } else if (slot == G && own_new) {
       *reinterpret_cast<uint4*>(Ks + (size_t)cached * RA_PITCH + d0) = rot;
       *reinterpret_cast<uint4*>(kc + (size_t)cache_pos * FA_D + d0) = rot;
-    } else if (slot == G + 1) {
+    } else if (slot == G + 1 && own_new) {
       *reinterpret_cast<uint4*>(Vs + (size_t)cached * RA_PITCH + d0) = raw;
       *reinterpret_cast<uint4*>(vc + (size_t)cache_pos * FA_D + d0) = raw;
     }
@@ -608,40 +626,127 @@ __global__ void __launch_bounds__(FA_THREADS) rope_flash_decode_resident_kernel(
   }
   __syncthreads();
   if (tid == 0) trace_mark(a.trace, 3, true);
-  {
-    T* out = reinterpret_cast<T*>(a.out) + ((size_t)b * a.Hq + (size_t)kvh * G) * FA_D;
-    for (int idx = tid; idx < G * FA_D; idx += FA_THREADS) {
-      const int g = idx / FA_D, d = idx - g * FA_D;
-      float v = 0.f, l = 0.f;
+  T* out = reinterpret_cast<T*>(a.out) + ((size_t)b * a.Hq + (size_t)kvh * G) * FA_D;
+  for (int idx = tid; idx < G * FA_D; idx += FA_THREADS) {
+    const int g = idx / FA_D, d = idx - g * FA_D;
+    float v = 0.f, l = 0.f, mh = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < FA_WARPS; ++w) {
-        v += red[((size_t)w * GP + g) * FA_D + d];
-        l += wsum[w * GP + g];
-      }
+    for (int w = 0; w < FA_WARPS; ++w) {
+      v += red[((size_t)w * GP + g) * FA_D + d];
+      l += wsum[w * GP + g];
+      mh = fmaxf(mh, wmax[w * GP + g]);
+    }
+    if (n_active == 1) {
       out[idx] = Elt<T>::from_f32(l > 0.f ? v / l : 0.f);
+    } else {
+      float* p = a.partials + ((((size_t)b * a.Hq + (size_t)kvh * G + g) * a.max_splits) + split) * (FA_D + 2);
+      if (d == 0) {
+        p[0] = mh;
+        p[1] = l;
+      }
+      p[2 + d] = v;
     }
   }
-  if (tid == 0) trace_end(a.trace);
+  if (n_active == 1) {
+    if (tid == 0) trace_end(a.trace);
+    return;
+  }
+  // the last CTA of this (sequence, KV head) to arrive merges the splits by log-sum-exp
+  __shared__ int is_last_s;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(&a.counters[b * a.Hkv + kvh], 1u);
+    is_last_s = (prev == static_cast<unsigned>(n_active - 1)) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!is_last_s) {
+    if (tid == 0) trace_end(a.trace);
+    return;
+  }
+  __threadfence();
+  for (int idx = tid; idx < G * FA_D; idx += FA_THREADS) {
+    const int g = idx / FA_D, d = idx - g * FA_D;
+    const float* p = a.partials + (((size_t)b * a.Hq + (size_t)kvh * G + g) * a.max_splits) * (FA_D + 2);
+    float mm = -INFINITY, ll = 0.f, aa = 0.f;
+    for (int s0 = 0; s0 < n_active; s0 += 8) {  // loads of eight splits back to back, then the fold
+      float ms[8], ls[8], as[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float* ps = p + (size_t)min(s0 + i, n_active - 1) * (FA_D + 2);
+        ms[i] = __ldcg(ps);
+        ls[i] = __ldcg(ps + 1);
+        as[i] = __ldcg(ps + 2 + d);
+      }
+      float bm = mm;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (s0 + i < n_active) bm = fmaxf(bm, ms[i]);
+      if (bm == -INFINITY) continue;
+      const float c = (mm == -INFINITY) ? 0.f : exp2f(mm - bm);
+      ll *= c;
+      aa *= c;
+      mm = bm;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (s0 + i < n_active && ms[i] != -INFINITY) {
+          const float f = exp2f(ms[i] - bm);
+          ll = fmaf(ls[i], f, ll);
+          aa = fmaf(as[i], f, aa);
+        }
+      }
+    }
+    out[idx] = Elt<T>::from_f32(ll > 0.f ? aa / ll : 0.f);
+  }
+  if (tid == 0) {
+    a.counters[b * a.Hkv + kvh] = 0u;  // ready for the next launch
+    trace_end(a.trace);
+  }
 }
 
 template <typename T, int GP>
-mui_status_t launch_ra(cudaStream_t stream, const FaArgs& a, int pdl) {
+mui_status_t launch_ra(cudaStream_t stream, const FaArgs& a, int pdl, int splits) {
   static bool configured = false;  // per instantiation
   auto kern = rope_flash_decode_resident_kernel<T, GP>;
   if (!configured) {
     MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ra_smem_bytes<GP>()));
     configured = true;
   }
-  MUI_CUDA_CHECK(mui_launch(kern, dim3(a.Hkv, a.B), dim3(FA_THREADS), ra_smem_bytes<GP>(), stream, pdl, a));
+  MUI_CUDA_CHECK(mui_launch(kern, dim3(a.Hkv, a.B, splits), dim3(FA_THREADS), ra_smem_bytes<GP>(), stream, pdl, a));
   return MUI_OK;
 }
 
 template <typename T>
-mui_status_t launch_ra_g(cudaStream_t stream, const FaArgs& a, int pdl) {
-  if (a.G <= 1) return launch_ra<T, 1>(stream, a, pdl);
-  if (a.G <= 2) return launch_ra<T, 2>(stream, a, pdl);
-  if (a.G <= 4) return launch_ra<T, 4>(stream, a, pdl);
-  return launch_ra<T, 8>(stream, a, pdl);
+mui_status_t launch_ra_g(cudaStream_t stream, const FaArgs& a, int pdl, int splits = 1) {
+  if (a.G <= 1) return launch_ra<T, 1>(stream, a, pdl, splits);
+  if (a.G <= 2) return launch_ra<T, 2>(stream, a, pdl, splits);
+  if (a.G <= 4) return launch_ra<T, 4>(stream, a, pdl, splits);
+  return launch_ra<T, 8>(stream, a, pdl, splits);
+}
+
+// Workspace of the token-split variant: the layout of mui_flash_decode_workspace_bytes (4 KiB of arrival counters that
+// are zero between launches, then fp32 partials [B, Hq, 64, D + 2]).
+constexpr int RA_MAX_SPLITS = 64;
+constexpr int RA_SPLIT_ROWS = 256;  // tokens per CTA the split count is sized for (a CTA holds up to RA_ROWS)
+constexpr size_t RA_COUNTER_BYTES = 4096;
+
+// Picks the kernel variant for `max_attended` tokens: 0 = cluster kernel, 1 = one CTA per KV head, n > 1 = n-way
+// token split of the latter (needs the workspace).
+int ra_pick_splits(unsigned flags, int max_attended, int B, int Hq, int Hkv, const void* workspace,
+                   size_t workspace_bytes) {
+  if (flags & MUI_FLAG_SHORT_CONTEXT) return 1;
+  if (!(flags & MUI_FLAG_SPLIT_CONTEXT) || workspace == nullptr) return 0;
+  const int splits = (max_attended + RA_SPLIT_ROWS - 1) / RA_SPLIT_ROWS;
+  const size_t need = RA_COUNTER_BYTES + (size_t)B * Hq * RA_MAX_SPLITS * (FA_D + 2) * sizeof(float);
+  if (splits <= 1) return 1;
+  if (splits > RA_MAX_SPLITS || workspace_bytes < need || (size_t)B * Hkv * 4 > RA_COUNTER_BYTES) return 0;
+  return splits;
+}
+void ra_bind_workspace(FaArgs& a, void* workspace) {
+  a.counters = reinterpret_cast<unsigned int*>(workspace);
+  a.partials = workspace ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + RA_COUNTER_BYTES)
+                         : nullptr;
+  a.max_splits = RA_MAX_SPLITS;
 }
 
 template <typename T, int GP, int U>
@@ -679,6 +784,18 @@ extern "C" mui_status_t mui_rope_flash_decode(void* stream, mui_dtype_t dtype, i
                                               const void* sin_table, const int64_t* position_ids,
                                               const int64_t* cache_position, const int32_t* seq_len_dev,
                                               float scale, void* k_cache, void* v_cache, void* out, unsigned flags) {
+  return mui_rope_flash_decode_ws(stream, dtype, B, Hq, Hkv, D, max_seq, qkv, cos_table, sin_table, position_ids,
+                                  cache_position, seq_len_dev, scale, k_cache, v_cache, out, nullptr, 0, max_seq,
+                                  flags & ~MUI_FLAG_SPLIT_CONTEXT);
+}
+
+extern "C" mui_status_t mui_rope_flash_decode_ws(void* stream, mui_dtype_t dtype, int B, int Hq, int Hkv, int D,
+                                                 int max_seq, const void* qkv, const void* cos_table,
+                                                 const void* sin_table, const int64_t* position_ids,
+                                                 const int64_t* cache_position, const int32_t* seq_len_dev,
+                                                 float scale, void* k_cache, void* v_cache, void* out,
+                                                 void* workspace, size_t workspace_bytes, int max_attended,
+                                                 unsigned flags) {
   MUI_REQUIRE(dtype == MUI_F16 || dtype == MUI_BF16, MUI_ERR_UNSUPPORTED, "dtype %d unsupported", (int)dtype);
   MUI_REQUIRE(D == FA_D, MUI_ERR_UNSUPPORTED, "head dim %d unsupported by the fused kernel (128)", D);
   MUI_REQUIRE(B >= 1 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && Hq / Hkv <= 8 && max_seq >= 1, MUI_ERR_INVALID_ARG,
@@ -712,10 +829,12 @@ extern "C" mui_status_t mui_rope_flash_decode(void* stream, mui_dtype_t dtype, i
   a.l4 = 0;
   a.chunk = 0;
   a.eps = a.attn_scale = a.floor_scale = 0.f;
+  ra_bind_workspace(a, workspace);
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
-  if (flags & MUI_FLAG_SHORT_CONTEXT) {
-    if (dtype == MUI_F16) return launch_ra_g<__half>((cudaStream_t)stream, a, pdl);
-    return launch_ra_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl);
+  const int splits = ra_pick_splits(flags, std::min(max_attended, max_seq), B, Hq, Hkv, workspace, workspace_bytes);
+  if (splits >= 1) {
+    if (dtype == MUI_F16) return launch_ra_g<__half>((cudaStream_t)stream, a, pdl, splits);
+    return launch_ra_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl, splits);
   }
   if (dtype == MUI_F16) return launch_fa_g<__half>((cudaStream_t)stream, a, pdl);
   return launch_fa_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl);
@@ -727,7 +846,8 @@ extern "C" mui_status_t mui_llama4_rope_flash_decode(void* stream, mui_dtype_t d
                                                      const int64_t* cache_position, int use_rope, int use_qk_norm,
                                                      float norm_eps, int temperature_tuning, float attn_scale,
                                                      float floor_scale, int chunk, float scale, void* k_cache,
-                                                     void* v_cache, void* out, unsigned flags) {
+                                                     void* v_cache, void* out, void* workspace,
+                                                     size_t workspace_bytes, int max_attended, unsigned flags) {
   MUI_REQUIRE(dtype == MUI_F16 || dtype == MUI_BF16, MUI_ERR_UNSUPPORTED, "dtype %d unsupported", (int)dtype);
   MUI_REQUIRE(D == FA_D, MUI_ERR_UNSUPPORTED, "head dim %d unsupported by the fused kernel (128)", D);
   MUI_REQUIRE(B >= 1 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && Hq / Hkv <= 8 && cache_rows >= 1 && max_pos >= 1,
@@ -765,10 +885,13 @@ extern "C" mui_status_t mui_llama4_rope_flash_decode(void* stream, mui_dtype_t d
   a.eps = norm_eps;
   a.attn_scale = attn_scale;
   a.floor_scale = floor_scale;
+  ra_bind_workspace(a, workspace);
   const int pdl = (flags & MUI_FLAG_PDL) ? 1 : 0;
-  if (flags & MUI_FLAG_SHORT_CONTEXT) {
-    if (dtype == MUI_F16) return launch_ra_g<__half>((cudaStream_t)stream, a, pdl);
-    return launch_ra_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl);
+  const int in_view = std::min(max_attended, chunk > 0 ? std::min(chunk, cache_rows) : cache_rows);
+  const int splits = ra_pick_splits(flags, in_view, B, Hq, Hkv, workspace, workspace_bytes);
+  if (splits >= 1) {
+    if (dtype == MUI_F16) return launch_ra_g<__half>((cudaStream_t)stream, a, pdl, splits);
+    return launch_ra_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl, splits);
   }
   if (dtype == MUI_F16) return launch_fa_g<__half>((cudaStream_t)stream, a, pdl);
   return launch_fa_g<__nv_bfloat16>((cudaStream_t)stream, a, pdl);

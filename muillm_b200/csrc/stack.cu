@@ -295,7 +295,8 @@ mui_status_t launch_step_l4(mui_llama_stack* s, cudaStream_t stream, unsigned fl
       st = mui_llama4_rope_flash_decode(stream, c.dtype, 1, Hq, Hkv, D, rows, c.max_seq, s->qkv_out, s->freqs,
                                         position_ids, cache_position, rope, norm, c.rms_eps, tune, c4.attn_scale,
                                         c4.floor_scale, chunk, c.attn_scale, s->k_cache[l], s->v_cache[l], s->attn,
-                                        flags | (short_ctx ? MUI_FLAG_SHORT_CONTEXT : 0u));
+                                        s->fd_ws, s->fd_ws_bytes, layer_attended,
+                                        flags | (short_ctx ? MUI_FLAG_SHORT_CONTEXT : MUI_FLAG_SPLIT_CONTEXT));
       if (st != MUI_OK) return st;
     } else {
       const unsigned char* qp = (const unsigned char*)s->qkv_out;
@@ -391,11 +392,13 @@ mui_status_t launch_step(mui_llama_stack* s, cudaStream_t stream, unsigned flags
                                    nullptr, nullptr, nullptr, s->h, s->qkv_out, flags, &hints);
     if (st != MUI_OK) return st;
     if (fused_attn) {
-      // one launch: RoPE + cache write + attention
-      st = mui_rope_flash_decode(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->qkv_out, s->cos_t, s->sin_t,
-                                 (const int64_t*)position_ids, (const int64_t*)cache_position, s->seq_len32,
-                                 c.attn_scale, s->k_cache[l], s->v_cache[l], s->attn,
-                                 flags | (short_ctx ? MUI_FLAG_SHORT_CONTEXT : 0u));
+      // one launch: RoPE + cache write + attention. Up to 384 tokens one CTA per KV head (resident beside the QKV
+      // projection); beyond, the same tensor-core kernel with the tokens split over several CTAs per KV head
+      st = mui_rope_flash_decode_ws(stream, c.dtype, B, Hq, Hkv, D, c.max_seq, s->qkv_out, s->cos_t, s->sin_t,
+                                    (const int64_t*)position_ids, (const int64_t*)cache_position, s->seq_len32,
+                                    c.attn_scale, s->k_cache[l], s->v_cache[l], s->attn, s->fd_ws, s->fd_ws_bytes,
+                                    attended,
+                                    flags | (short_ctx ? MUI_FLAG_SHORT_CONTEXT : MUI_FLAG_SPLIT_CONTEXT));
       if (st != MUI_OK) return st;
     } else {
       const unsigned char* qp = (const unsigned char*)s->qkv_out;

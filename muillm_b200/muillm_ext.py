@@ -48,12 +48,23 @@ def _rows(x):
     return x.numel() // x.shape[-1] if x.numel() else 0
 
 
+def _tensor_core_prefill_ok(x, *weights):
+    """The tcgen05 prefill GEMM takes 16-bit contiguous operands with rows that are multiples of 16 bytes."""
+    if x.dtype not in (torch.float16, torch.bfloat16) or x.shape[-1] % 8 or not x.is_contiguous():
+        return False
+    return all(w.is_contiguous() and w.dtype == x.dtype and w.data_ptr() % 16 == 0 for w in weights) and \
+        x.data_ptr() % 16 == 0
+
+
 def _linear_any_rows(x, weights, norm_weights=None, epsilon=0.0, mul_bias=None, add_bias=None, residual=None):
-    """Decode rows -> GEMV kernel; prefill -> RMSNorm kernel + torch GEMM (csrc/modules/linear_module.cpp:40-80)."""
+    """Decode rows -> GEMV kernel; prefill -> RMSNorm kernel + the tcgen05 GEMM with the epilogue fused (the reference
+    calls at::linear there, csrc/modules/linear_module.cpp:40-80); other dtypes / layouts -> torch GEMM."""
     if _rows(x) <= _MAX_GEMV_ROWS:
         return ops.muillm_linear_forward(None, x, weights, norm_weights=norm_weights, epsilon=epsilon,
                                          mul_bias=mul_bias, add_bias=add_bias, residual=residual)
     xn = ops.muillm_rmsnorm_forward(norm_weights, x.contiguous(), epsilon) if norm_weights is not None else x
+    if _tensor_core_prefill_ok(xn, weights) and (residual is None or residual.is_contiguous()):
+        return ops.prefill_linear(xn, weights, mul_bias=mul_bias, add_bias=add_bias, residual=residual)
     y = F.linear(xn, weights)
     if mul_bias is not None:
         y = y * mul_bias
@@ -74,6 +85,10 @@ def _mlp_any_rows(norm_weights, epsilon, gate_weights, up_weights, down_weights,
         return ops.muillm_gateupsilu_forward(None, norm_weights, epsilon, gate_weights, up_weights, down_weights,
                                              residual, x)
     xn = ops.muillm_rmsnorm_forward(norm_weights, x.contiguous(), epsilon) if norm_weights is not None else x
+    if _tensor_core_prefill_ok(xn, gate_weights, up_weights, down_weights) and \
+            (residual is None or residual.is_contiguous()):
+        t = ops.prefill_gateup_silu(xn, gate_weights, up_weights)
+        return ops.prefill_linear(t, down_weights, residual=residual)
     y = F.linear(F.silu(F.linear(xn, gate_weights)) * F.linear(xn, up_weights), down_weights)
     return y + residual if residual is not None else y
 
@@ -93,23 +108,22 @@ def muillm_gateupsilumoe_forward(engine, num_shared_experts, num_dynamic_experts
                                             router_indices)
 
 
-_PACK_SPLITS = {}  # (data_ptr, shape) of a packed gate/up tensor -> its split halves, made once
-
-
 def _split_gateup_pack(gate_up_weights, gate_up_scales_min_vals, group_size_shift):
     """The reference packs gate and up element-interleaved, [I, H, 2] uint8 with [I*G, 2, 2] (gate/up, scale/min) pairs
     (muillm/modules/quantized/int8gateupdownmlp.py:211-230); the kernels stream two plain matrices, so the pack is
-    split once per tensor and the halves are kept."""
-    key = (gate_up_weights.data_ptr(), tuple(gate_up_weights.shape), gate_up_scales_min_vals.data_ptr())
-    hit = _PACK_SPLITS.get(key)
-    if hit is None:
+    split once per tensor. The halves live on the packed tensor object itself (they go when it goes) and are redone
+    when either tensor was written in place since (torch's version counters)."""
+    key = (gate_up_weights._version, gate_up_scales_min_vals._version, gate_up_scales_min_vals.data_ptr(),
+           group_size_shift)
+    hit = getattr(gate_up_weights, "_mui_split_halves", None)
+    if hit is None or hit[0] != key:
         I, H, _ = gate_up_weights.shape
         G = H >> group_size_shift
         sm = gate_up_scales_min_vals.reshape(I * G, 2, 2)
-        hit = (gate_up_weights[:, :, 0].contiguous(), sm[:, 0, :].contiguous(),
-               gate_up_weights[:, :, 1].contiguous(), sm[:, 1, :].contiguous())
-        _PACK_SPLITS[key] = hit
-    return hit
+        hit = (key, (gate_up_weights[:, :, 0].contiguous(), sm[:, 0, :].contiguous(),
+                     gate_up_weights[:, :, 1].contiguous(), sm[:, 1, :].contiguous()))
+        gate_up_weights._mui_split_halves = hit
+    return hit[1]
 
 
 def muillm_int8_gateupsilu_dequantize_forward(gate_up_weights, gate_up_scales_min_vals, group_size_shift):

@@ -96,6 +96,35 @@ def gateup_silu(x, gate_weights, up_weights, norm_weights=None, epsilon=0.0, fla
     return out
 
 
+def prefill_linear(x, weights, mul_bias=None, add_bias=None, residual=None, activation=capi.MUI_ACT_IDENTITY, flags=0):
+    """y = act(x W^T) * mul_bias + add_bias + residual for any number of rows (x [..., K], weights [N, K]) on the
+    tcgen05 tensor cores: the prefill / batched counterpart of muillm_linear_forward."""
+    for t, n in ((x, "x"), (weights, "weights"), (mul_bias, "mul_bias"), (add_bias, "add_bias"),
+                 (residual, "residual")):
+        _check_input(t, n)
+    N, K = weights.shape
+    if x.shape[-1] != K:
+        raise RuntimeError(f"x last dim {x.shape[-1]} != K {K}")
+    M = x.numel() // K
+    y = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_prefill_linear_forward(
+        _stream(), _dtype_code(x), M, N, K, _ptr(weights), int(activation), _ptr(mul_bias), _ptr(add_bias),
+        _ptr(residual), _ptr(x), _ptr(y), flags))
+    return y
+
+
+def prefill_gateup_silu(x, gate_weights, up_weights, flags=0):
+    """t = silu(x G^T) * (x U^T) for any number of rows on the tcgen05 tensor cores (no fused norm)."""
+    for t, n in ((x, "x"), (gate_weights, "gate_weights"), (up_weights, "up_weights")):
+        _check_input(t, n)
+    I, H = gate_weights.shape
+    M = x.numel() // H
+    out = torch.empty(x.shape[:-1] + (I,), dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_prefill_gateup_silu_forward(
+        _stream(), _dtype_code(x), M, I, H, _ptr(gate_weights), _ptr(up_weights), _ptr(x), _ptr(out), flags))
+    return out
+
+
 def muillm_rmsnorm_forward(weights, x, epsilon, flags=0):
     """RMSNorm over the last dim (csrc/module.cpp:251, csrc/norm/rmsnorm.cu:31-84). weights may be None (L2 norm)."""
     _check_input(x, "x")
@@ -312,21 +341,24 @@ def muillm_int8_dequantize_forward(weights, scales_min_vals, group_size_shift, d
 
 
 def rope_flash_decode(qkv, cos_table, sin_table, position_ids, cache_position, seq_len, k_cache, v_cache, num_q_heads,
-                      flags=0):
+                      flags=0, workspace=None, max_attended=None):
     """Fused decode attention for one new token per sequence: RoPE on q and the new k, K/V cache write at
     cache_position, attention over the first `seq_len` cache rows (the new one included). qkv is the packed QKV
     projection output [B, (Hq + 2*Hkv) * D]; position_ids [B] int64, cache_position [1] int64 and seq_len [1] int32
     are device tensors. Returns [B, 1, Hq * D]. One launch in place of muillm_rope_forward_static_cache +
-    muillm_causal_transformer_decoding_no_mask."""
+    muillm_causal_transformer_decoding_no_mask. With `workspace` (uint8 tensor of flash_decode_workspace_bytes, first
+    4 KiB zero) and MUI_FLAG_SPLIT_CONTEXT the tokens are split over several CTAs per KV head, sized for
+    `max_attended` tokens (default: the cache length)."""
     for t, n in ((qkv, "qkv"), (cos_table, "cos_table"), (sin_table, "sin_table"), (position_ids, "position_ids"),
                  (cache_position, "cache_position"), (seq_len, "seq_len"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _check_input(t, n)
     B, Hkv, max_seq, D = k_cache.shape
     out = torch.empty((B, 1, num_q_heads * D), dtype=qkv.dtype, device=qkv.device)
-    capi.check(capi.lib().mui_rope_flash_decode(
+    capi.check(capi.lib().mui_rope_flash_decode_ws(
         _stream(), _dtype_code(qkv), B, num_q_heads, Hkv, D, max_seq, _ptr(qkv), _ptr(cos_table), _ptr(sin_table),
         _ptr(position_ids), _ptr(cache_position), _ptr(seq_len), 1.0 / math.sqrt(D), _ptr(k_cache), _ptr(v_cache),
-        _ptr(out), flags))
+        _ptr(out), _ptr(workspace), 0 if workspace is None else workspace.numel(),
+        max_seq if max_attended is None else int(max_attended), flags))
     return out
 
 

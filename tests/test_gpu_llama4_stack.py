@@ -106,7 +106,7 @@ def test_stack_equals_kernel_by_kernel_runner_past_the_short_context_limit():
 
 
 def _fused_attention(q, k, v, kc, vc, freqs, pos, rope, norm, tune, chunk, flags, eps=1e-5, attn_scale=0.1,
-                     floor_scale=4.0):
+                     floor_scale=4.0, ws=None):
     B, Hq, _, D = q.shape
     Hkv = k.shape[1]
     qkv = torch.cat([q.reshape(B, Hq * D), k.reshape(B, Hkv * D), v.reshape(B, Hkv * D)], dim=1).contiguous()
@@ -117,7 +117,8 @@ def _fused_attention(q, k, v, kc, vc, freqs, pos, rope, norm, tune, chunk, flags
         torch.cuda.current_stream().cuda_stream, capi.MUI_F16 if q.dtype == torch.float16 else capi.MUI_BF16, B, Hq,
         Hkv, D, kc.shape[2], freqs.shape[0], qkv.data_ptr(), freqs.data_ptr(), pid.data_ptr(), cp.data_ptr(),
         int(rope), int(norm), eps, int(tune), attn_scale, floor_scale, chunk, 1.0 / math.sqrt(D), kc.data_ptr(),
-        vc.data_ptr(), out.data_ptr(), flags))
+        vc.data_ptr(), out.data_ptr(), None if ws is None else ws.data_ptr(), 0 if ws is None else ws.numel(),
+        kc.shape[2], flags))
     return out
 
 
@@ -129,8 +130,10 @@ def _fused_attention(q, k, v, kc, vc, freqs, pos, rope, norm, tune, chunk, flags
     (1, 5, 1, 191, 64, 64, True, False, False),     # last row of a chunk
     (1, 5, 1, 192, 64, 64, True, True, False),      # first row of a chunk: attends itself only
     (2, 8, 2, 300, 0, 512, False, False, True),     # no-rope layer with temperature tuning, two sequences
-    (1, 8, 8, 600, 0, 1024, True, True, True),      # beyond the short-context limit (cluster kernel only)
-], ids=["tp4", "ring22", "ring-last", "ring-first", "nope-b2", "long"])
+    (1, 8, 8, 600, 0, 1024, True, True, True),      # beyond the one-CTA limit: cluster kernel and 4-way token split
+    (1, 32, 8, 4000, 0, 4096, True, True, False),   # 16-way token split, 4 query heads per KV head
+    (2, 5, 1, 2047, 2048, 2048, True, True, False),  # last row of a 2048-row ring, 8-way split, two sequences
+], ids=["tp4", "ring22", "ring-last", "ring-first", "nope-b2", "long", "split16", "ring2048"])
 def test_fused_llama4_attention_matches_oracle(dtype, case):
     B, Hq, Hkv, pos, chunk, rows, rope, norm, tune = case
     D = 128
@@ -140,7 +143,7 @@ def test_fused_llama4_attention_matches_oracle(dtype, case):
     v = torch.randn(B, Hkv, 1, D, generator=g).to(dtype)
     kc = torch.randn(B, Hkv, rows, D, generator=g).to(dtype)
     vc = torch.randn(B, Hkv, rows, D, generator=g).to(dtype)
-    freqs = llama4_freqs(1024, D, 500000.0, "cpu")
+    freqs = llama4_freqs(4096, D, 500000.0, "cpu")
     # oracle: the three prologue stages, the cache write at the ring / plain row, attention over the rows in view
     pe = freqs[pos: pos + 1].unsqueeze(0).expand(B, 1, D // 2, 2)
     cpos = torch.tensor([pos], dtype=torch.int64)
@@ -156,10 +159,16 @@ def test_fused_llama4_attention_matches_oracle(dtype, case):
     kc_ref[:, :, row] = ko[:, :, 0]
     vc_ref[:, :, row] = v[:, :, 0]
     want = oracle.decode_attention(qo, kc_ref[:, :, : row + 1], vc_ref[:, :, : row + 1]).reshape(B, Hq * D)
-    variants = [0] if row + 1 > 384 else [0, capi.MUI_FLAG_SHORT_CONTEXT]
+    # cluster kernel; token-split tensor-core kernel (twice: the second call finds the counters back at zero);
+    # one CTA per KV head where the rows fit
+    variants = [0, capi.MUI_FLAG_SPLIT_CONTEXT, capi.MUI_FLAG_SPLIT_CONTEXT]
+    if row + 1 <= 384:
+        variants.append(capi.MUI_FLAG_SHORT_CONTEXT)
+    ws = torch.zeros(capi.lib().mui_flash_decode_workspace_bytes(B, Hq, Hkv, D, rows), dtype=torch.uint8, device="cuda")
     for flags in variants:
         kd, vd = kc.cuda(), vc.cuda()
-        got = _fused_attention(q.cuda(), k.cuda(), v.cuda(), kd, vd, freqs.cuda(), pos, rope, norm, tune, chunk, flags)
+        got = _fused_attention(q.cuda(), k.cuda(), v.cuda(), kd, vd, freqs.cuda(), pos, rope, norm, tune, chunk, flags,
+                               ws=ws)
         torch.cuda.synchronize()
         torch.testing.assert_close(got.float().cpu(), want.float(), rtol=1e-2, atol=2e-3)
         # the new row was written where the ring says, bit for bit what the stand-alone prologue kernel gives; every

@@ -155,11 +155,14 @@ def test_flash_decode_softmax_shift_invariance():
                                         (1, 32, 8, 513),
                                         (2, 8, 1, 2000), (3, 4, 4, 65), (1, 8, 8, 4096), (2, 8, 1, 300), (2, 4, 2, 384),
                                         (1, 16, 2, 97)])
-@pytest.mark.parametrize("variant", [0, capi.MUI_FLAG_SHORT_CONTEXT, capi.MUI_FLAG_SHORT_CONTEXT | capi.MUI_FLAG_PDL])
+@pytest.mark.parametrize("variant", [0, capi.MUI_FLAG_SHORT_CONTEXT, capi.MUI_FLAG_SHORT_CONTEXT | capi.MUI_FLAG_PDL,
+                                     capi.MUI_FLAG_SPLIT_CONTEXT, capi.MUI_FLAG_SPLIT_CONTEXT | capi.MUI_FLAG_PDL])
 def test_fused_rope_cache_write_attention(dtype, B, Hq, Hkv, S, variant):
-    """One launch = RoPE(q, k_new) + cache write + attention over S tokens (the new one last): the cluster kernel, and
-    the one-CTA-per-head tensor-core kernel that stages the history in shared memory (at most 384 tokens; a longer
-    sequence must be refused through the device status word, not computed wrongly)."""
+    """One launch = RoPE(q, k_new) + cache write + attention over S tokens (the new one last): the cluster kernel, the
+    one-CTA-per-head tensor-core kernel that stages the history in shared memory (at most 384 tokens; a longer
+    sequence must be refused through the device status word, not computed wrongly), and the same kernel with the
+    tokens split over several CTAs per KV head (sized for the whole 4096-row cache: 16 CTAs, of which a short sequence
+    uses few) whose last arriver merges the parts."""
     D, max_T = 128, 4096
     g = _gen(S + B + Hq)
     qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
@@ -178,8 +181,13 @@ def test_fused_rope_cache_write_attention(dtype, B, Hq, Hkv, S, variant):
     q_rot, ks, vs = oracle.rope_write_static_cache(q, k, v, cos, sin, position_ids, kc_ref, vc_ref, cache_position, S)
     want = oracle.decode_attention(q_rot, ks, vs)
     kc_g, vc_g = kc.cuda(), vc.cuda()
+    ws = None
+    if variant & capi.MUI_FLAG_SPLIT_CONTEXT:
+        ws = torch.zeros(capi.lib().mui_flash_decode_workspace_bytes(B, Hq, Hkv, D, max_T), dtype=torch.uint8,
+                         device="cuda")
     got = ops.rope_flash_decode(qkv.cuda(), cos.cuda(), sin.cuda(), position_ids.view(-1).cuda(), cache_position.cuda(),
-                                torch.tensor([S], dtype=torch.int32, device="cuda"), kc_g, vc_g, Hq, flags=variant)
+                                torch.tensor([S], dtype=torch.int32, device="cuda"), kc_g, vc_g, Hq, flags=variant,
+                                workspace=ws)
     if (variant & capi.MUI_FLAG_SHORT_CONTEXT) and S > 384:
         torch.cuda.synchronize()
         status = capi.device_status(clear=True)
@@ -193,3 +201,5 @@ def test_fused_rope_cache_write_attention(dtype, B, Hq, Hkv, S, variant):
     keep = torch.ones(max_T, dtype=torch.bool)
     keep[pos] = False
     assert torch.equal(kc_g.cpu()[:, :, keep], kc[:, :, keep])
+    if ws is not None:
+        assert int(ws[:4096].view(torch.int32).abs().sum()) == 0, "the arrival counters must be back at zero"

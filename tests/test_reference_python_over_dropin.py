@@ -1,4 +1,4 @@
-"""Where the reference checkout is present (the authoring container), its own Python modules are imported with the
+"""Where a checkout of the reference is given in $MUILLM_REFERENCE, its own Python modules are imported with the
 drop-in registered as `muillm_ext` and built the way `init_engine` builds them, which goes through the drop-in's
 engine / module-handle life cycle (no GPU here, so nothing is computed). Skipped elsewhere."""
 import importlib
@@ -8,8 +8,9 @@ import sys
 import pytest
 import torch
 
-REF = os.environ.get("MUILLM_REFERENCE", "/root/reference")
-pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "muillm")), reason="reference checkout absent")
+REF = os.environ.get("MUILLM_REFERENCE", "")
+pytestmark = pytest.mark.skipif(not (REF and os.path.isdir(os.path.join(REF, "muillm"))),
+                                reason="no reference checkout at $MUILLM_REFERENCE")
 
 
 @pytest.fixture(scope="module")
