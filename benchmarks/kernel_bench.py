@@ -138,6 +138,20 @@ def case_moe(name, H, I, shared, routed, dtype, dev, g, flags):
     return name + " (2 launches)", _time_graph(fns, 2 * len(fns)), nbytes
 
 
+def case_prefill(M, N, K, dtype, dev, g):
+    """The tcgen05 prefill GEMM beside torch's (cuBLAS) at the same shape: microseconds and dense TFLOP/s."""
+    import torch.nn.functional as F
+
+    L = _sets_for(N * K * 2)
+    ws = [_randw(N, K, dtype, g, dev) for _ in range(L)]
+    x = torch.randn(M, K, device=dev, generator=g).to(dtype)
+    ours = _time_graph([(lambda w=w: ops.prefill_linear(x, w)) for w in ws], 4 * L)
+    blas = _time_graph([(lambda w=w: F.linear(x, w)) for w in ws], 4 * L)
+    flops = 2.0 * M * N * K
+    return {"case": f"prefill GEMM M={M} N={N} K={K}", "us": ours * 1e6, "tflops": flops / ours / 1e12,
+            "cublas_us": blas * 1e6, "cublas_tflops": flops / blas / 1e12, "weight_gbs": N * K * 2 / ours / 1e9}
+
+
 def run(dtype=torch.float16):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -170,6 +184,13 @@ def run(dtype=torch.float16):
     for S in (1024, 2048, 4096):
         add(case_attention(f"rope+cache+attention, tokens split over CTAs, S={S}", S, dtype, dev, g, flags, split=True))
     add(case_moe("MoE MLP shared+top-1 of 16, H=5120 I=2048, bf16", 5120, 2048, 1, 16, torch.bfloat16, dev, g, flags))
+    for (M, N, K) in ((16, 6144, 4096), (64, 6144, 4096), (256, 6144, 4096), (256, 14336, 4096), (1024, 6144, 4096),
+                      (2048, 4096, 14336)):
+        r = case_prefill(M, N, K, dtype, dev, g)
+        rows.append(r)
+        print(f"{r['case']:58s} {r['us']:8.2f} us {r['tflops']:7.1f} TFLOP/s (torch/cuBLAS {r['cublas_us']:8.2f} us "
+              f"{r['cublas_tflops']:7.1f} TFLOP/s); weights at {r['weight_gbs']:.0f} GB/s", flush=True)
+        torch.cuda.empty_cache()
     assert capi.device_status() == 0
     return rows
 
@@ -187,7 +208,13 @@ def main():
         with open(args.md, "w") as f:
             f.write("| case | us per launch | GB/s | of 8 TB/s |\n|---|---|---|---|\n")
             for r in rows:
-                f.write(f"| {r['case']} | {r['us']:.2f} | {r['gbs']:.1f} | {r['of_8tbs']:.3f} |\n")
+                if "gbs" in r:
+                    f.write(f"| {r['case']} | {r['us']:.2f} | {r['gbs']:.1f} | {r['of_8tbs']:.3f} |\n")
+            f.write("\n| prefill case | us | TFLOP/s | torch (cuBLAS) us | torch TFLOP/s |\n|---|---|---|---|---|\n")
+            for r in rows:
+                if "tflops" in r:
+                    f.write(f"| {r['case']} | {r['us']:.2f} | {r['tflops']:.1f} | {r['cublas_us']:.2f} | "
+                            f"{r['cublas_tflops']:.1f} |\n")
 
 
 if __name__ == "__main__":

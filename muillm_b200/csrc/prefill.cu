@@ -34,7 +34,10 @@ constexpr int PF_UMMA_K = 16;                               // K of one tcgen05.
 constexpr int PF_W_TILE_BYTES = PF_TILE_N * PF_BLOCK_K * 2;  // 16 KiB
 constexpr int PF_MAX_STAGES = 8;
 constexpr int PF_MAX_MT = 256;                              // tokens per CTA tile = UMMA N
-constexpr int PF_THREADS = 192;                             // warp 0: TMA, warp 1: tensor memory + MMA, warps 2-5: epilogue
+// Two warpgroups: warp 0 issues the TMA loads, warp 1 owns the tensor memory and issues the MMAs, warps 2-3 idle,
+// warps 4-7 (tensor-memory lanes 32 * (warp % 4)) run the epilogue.
+constexpr int PF_THREADS = 256;
+constexpr int PF_EPI_WARP0 = 4;
 
 struct PfArgs {
   int M, N, K;
@@ -52,9 +55,6 @@ struct PfArgs {
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
-}
 // 2-D tile load global -> this CTA's shared memory; x = element coordinate along K (a multiple of 64 here, so the
 // 16-byte rule holds), y = row; completion is counted in bytes on `bar`
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* m, int x, int y, uint64_t* bar) {
@@ -136,15 +136,17 @@ __device__ __forceinline__ void pf_store(const PfArgs& a, int tok, int n, float 
     v = silu_f32(g) * u;
   } else {
     if (a.activ == MUI_ACT_SILU) v = silu_f32(v);
-    if (a.mul_bias != nullptr) v *= Elt<T>::to_f32(__ldg(reinterpret_cast<const T*>(a.mul_bias) + n));
-    if (a.add_bias != nullptr) v += Elt<T>::to_f32(__ldg(reinterpret_cast<const T*>(a.add_bias) + n));
+    // plain loads: the 16-bit __ldg overloads are non-volatile inline asm, which the compiler is free to hoist above
+    // the null checks (it did: the first versions of this kernel read address n * 2 when no bias was given)
+    if (a.mul_bias != nullptr) v *= Elt<T>::to_f32(reinterpret_cast<const T*>(a.mul_bias)[n]);
+    if (a.add_bias != nullptr) v += Elt<T>::to_f32(reinterpret_cast<const T*>(a.add_bias)[n]);
     if (a.residual != nullptr)
       v += ld_act_f32<T>(reinterpret_cast<const T*>(a.residual) + static_cast<size_t>(tok) * a.N + n);
   }
   reinterpret_cast<T*>(a.y)[static_cast<size_t>(tok) * a.N + n] = Elt<T>::from_f32(v);
 }
 
-// grid = (weight tiles of 128 rows, token chunks of mt); block = 192 threads
+// grid = (weight tiles of 128 rows, token chunks of mt); block = 256 threads
 template <typename T, int NMAT>
 __global__ void __launch_bounds__(PF_THREADS, 1)
     prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_u,
@@ -187,9 +189,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tm_w);
-      if (NMAT == 2) tma_prefetch_desc(&tm_u);
-      tma_prefetch_desc(&tm_x);
       pdl_wait_prior_grid();  // the activations are the previous kernel's output
       int issued = 0;
       bool ok = true;
@@ -252,8 +251,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
       }
     }
     __syncwarp();
-  } else {
-    // ------------------------------ epilogue: warps 2-5 own tensor-memory lanes 32 * (warp % 4) ... ------------------------------
+  } else if (warp >= PF_EPI_WARP0) {
+    // ------------------------------ epilogue: warps 4-7 own tensor-memory lanes 32 * (warp % 4) ... ------------------------------
     const int q = warp & 3;
     const int row = q * 32 + lane;  // weight row inside the tile = tensor-memory lane
     const int n = n0 + row;
