@@ -138,6 +138,75 @@ def time_dominant_kernel(w, cfg, flags):
     return seconds, algo_bytes
 
 
+def time_plugin_e2e(w, cfg, prompt, K, W, max_seq):
+    """The same decode loop through the reference-facing plugin surface (`muillm_ext` module handles, the calls the
+    reference's Python makes: csrc/module.cpp:280-431): per token one `muillm_parallel_decoder_stack_forward`, the
+    final-norm lm_head through `muillm_linear_forward`, arg-max in torch as the reference samples; the token id is
+    copied host->device from pinned memory and the arg-max device->host every step. Returns tokens/s."""
+    import torch
+
+    from muillm_b200 import muillm_ext as ext
+    from muillm_b200.decoder_stack import rope_tables
+
+    Hq, Hkv, D, L = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["layers"]
+    dev, dt = w["embed"].device, w["embed"].dtype
+    engine = ext.muillm_engine_init()
+    comm = ext.muillm_comm_init(engine, 1, 1, 0, 0)
+    cos, sin = rope_tables(max_seq, D, cfg["rope_theta"], dt, dev)
+    embed = ext.muillm_embedding_module_init(engine, w["embed"])
+    stack_rotary = ext.muillm_rotary_embedding_module_init(engine, 0, cos, sin)
+    keep, decoders = [], []
+    for l in range(L):
+        qkv_lin = ext.muillm_parallel_linear_module_init(engine, comm, w["qkv"][l], norm_weights=w["ln1"][l],
+                                                         epsilon=cfg["eps"], sharding_dim=0)
+        slices = [(0, Hq * D), (Hq * D, (Hq + Hkv) * D), ((Hq + Hkv) * D, (Hq + 2 * Hkv) * D)]
+        multilinear = ext.muillm_parallel_multilinear_module_init(engine, comm, qkv_lin, slices, 0)
+        rotary = ext.muillm_rotary_embedding_module_init(engine, l, cos, sin)
+        o_proj = ext.muillm_parallel_linear_module_init(engine, comm, w["o"][l], sharding_dim=1)
+        attention = ext.muillm_parallel_attention_module_init(engine, comm, rotary, o_proj, Hq, Hkv, D)
+        mlp = ext.muillm_parallel_gateupdownmlp_module_init(engine, comm, ext.GATEUPSILU_FUSED, w["ln2"][l],
+                                                            w["gate"][l], w["up"][l], w["down"][l], cfg["eps"])
+        decoders.append(ext.muillm_parallel_decoder_module_init(engine, comm, multilinear, attention, mlp))
+        keep += [qkv_lin, multilinear, rotary, o_proj, attention, mlp]
+    stack = ext.muillm_parallel_decoder_stack_init(engine, comm, embed, stack_rotary, decoders)
+    kc = [torch.zeros(1, Hkv, max_seq, D, dtype=dt, device=dev) for _ in range(L)]
+    vc = [torch.zeros(1, Hkv, max_seq, D, dtype=dt, device=dev) for _ in range(L)]
+    cache = ext.muillm_static_kvcache_module_init(engine, kc, vc, 0)
+    tok_in = torch.zeros(1, 1, dtype=torch.int64).pin_memory()
+    tok_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+    pos_h = torch.zeros(1, 1, dtype=torch.int64).pin_memory()
+
+    def step(t):
+        pos_h[0, 0] = t
+        ids = tok_in.to(dev, non_blocking=True)
+        pos = pos_h.to(dev, non_blocking=True)
+        h = ext.muillm_parallel_decoder_stack_forward(stack, cache, ids, None, None, pos, pos.view(1))
+        logits = ext.muillm_linear_forward(engine, h, w["lm_head"], norm_weights=w["norm"], epsilon=cfg["eps"])
+        tok_out.copy_(torch.argmax(logits.view(1, -1), dim=-1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        tok_in[0, 0] = tok_out[0]
+
+    t = 0
+    for i in range(prompt.shape[1]):
+        tok_in[0, 0] = prompt[0, i]
+        step(t)
+        t += 1
+    for _ in range(W):
+        step(t)
+        t += 1
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        step(t)
+        t += 1
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    ext.muillm_parallel_decoder_stack_deinit(stack)
+    for m in keep + decoders + [embed, stack_rotary]:
+        m.release()
+    return K / seconds
+
+
 def cpu_decode_sample(cfg, seconds_budget=20.0, sample_layers=2, tokens=3):
     """Times the CPU oracle (PyTorch fp32, all host threads) on `sample_layers` decoder layers + the lm_head for
     `tokens` decode steps at sequence length ~PROMPT_LEN and scales the layer time to the full depth."""
@@ -290,6 +359,10 @@ def run_gpu(args):
                 stream.synchronize()
         barrier()
         e2e_seconds = time.perf_counter() - t0
+    plugin_tok_s = None
+    if world == 1:
+        with torch.cuda.stream(stream):
+            plugin_tok_s = time_plugin_e2e(w, cfg, prompt, K, W, MAX_SEQ)
     with torch.cuda.stream(stream):
         k_seconds, k_bytes = time_dominant_kernel(w, local_cfg, flags)
     status = capi.device_status()
@@ -345,6 +418,11 @@ def run_gpu(args):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if plugin_tok_s is not None:
+        # the same metric through the muillm_ext module handles the reference's Python would call (one decoder-stack
+        # call per token, lm_head and arg-max issued from Python): what a drop-in user of the reference gets
+        line["e2e_plugin"] = {"value": plugin_tok_s, "unit": "tokens/s", "api": "muillm_ext module handles",
+                              "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 8}
     if parity is not None:
         line["parity"] = parity
     print(json.dumps(line), flush=True)
