@@ -359,10 +359,13 @@ def run_gpu(args):
                 stream.synchronize()
         barrier()
         e2e_seconds = time.perf_counter() - t0
-    plugin_tok_s = None
+    plugin_tok_s, plugin_error = None, None
     if world == 1:
-        with torch.cuda.stream(stream):
-            plugin_tok_s = time_plugin_e2e(w, cfg, prompt, K, W, MAX_SEQ)
+        try:
+            with torch.cuda.stream(stream):
+                plugin_tok_s = time_plugin_e2e(w, cfg, prompt, K, W, MAX_SEQ)
+        except Exception as e:  # the headline numbers above do not depend on this leg: report it instead of dying
+            plugin_error = f"{type(e).__name__}: {e}"
     with torch.cuda.stream(stream):
         k_seconds, k_bytes = time_dominant_kernel(w, local_cfg, flags)
     status = capi.device_status()
@@ -423,6 +426,8 @@ def run_gpu(args):
         # call per token, lm_head and arg-max issued from Python): what a drop-in user of the reference gets
         line["e2e_plugin"] = {"value": plugin_tok_s, "unit": "tokens/s", "api": "muillm_ext module handles",
                               "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 8}
+    elif plugin_error is not None:
+        line["e2e_plugin"] = {"error": plugin_error}
     if parity is not None:
         line["parity"] = parity
     print(json.dumps(line), flush=True)

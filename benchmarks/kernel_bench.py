@@ -96,6 +96,45 @@ def case_down_w8(name, H, I, B, dtype, dev, g, flags):
     return name, _time_graph(fns, 4 * L), nbytes
 
 
+def _q8_group(w, shift=7):
+    """The reference's per-group format: uint8 q and {scale, min} pairs (muillm/quantization/rtnquantizer.py:48-88)."""
+    gs = 1 << shift
+    t = w.float().reshape(-1, gs)
+    mx, mn = t.amax(dim=1, keepdim=True), t.amin(dim=1, keepdim=True)
+    rng = (mx - mn).clamp(min=1e-6)
+    mn = (mn + mx) * 0.5 - rng * 0.5
+    sc = rng / 255
+    q = t.sub(mn).div(sc).clamp(0, 255).round().to(torch.uint8).reshape_as(w)
+    return q, torch.cat([sc, mn], dim=-1).to(w.dtype)
+
+
+def case_group_gateup_packed(name, I, H, B, dtype, dev, g, flags, shift=7):
+    """gate/up on the reference's interleaved [I, H, 2] pack with [I * G, 2, 2] {scale, min} pairs."""
+    L = _sets_for(2 * I * H)
+    x = torch.randn(B, H, device=dev, generator=g).to(dtype)
+    nw = torch.ones(H, device=dev, dtype=dtype)
+    fns = []
+    for _ in range(L):
+        (gq, gsm), (uq, usm) = _q8_group(_randw(I, H, dtype, g, dev), shift), _q8_group(_randw(I, H, dtype, g, dev), shift)
+        pack = torch.stack([gq, uq], dim=-1).contiguous()
+        sm = torch.stack([gsm, usm], dim=1).contiguous()
+        del gq, uq
+        fns.append(lambda pack=pack, sm=sm: ops.int8_gateup_silu_packed(x, pack, sm, shift, norm_weights=nw,
+                                                                        epsilon=1e-5, flags=flags))
+    nbytes = 2 * I * H + 2 * I * (H >> shift) * 4 + B * H * 2 + H * 2 + B * I * 2
+    return name, _time_graph(fns, 4 * L), nbytes
+
+
+def case_group_down(name, H, I, B, dtype, dev, g, flags, shift=7):
+    L = _sets_for(H * I)
+    qs = [_q8_group(_randw(H, I, dtype, g, dev), shift) for _ in range(L)]
+    t = torch.randn(B, I, device=dev, generator=g).to(dtype)
+    res = torch.randn(B, H, device=dev, generator=g).to(dtype)
+    fns = [(lambda q=q, s=s: ops.muillm_int8_linear_forward(t, q, s, shift, residual=res, flags=flags)) for q, s in qs]
+    nbytes = H * I + H * (I >> shift) * 4 + B * I * 2 + 2 * B * H * 2
+    return name, _time_graph(fns, 4 * L), nbytes
+
+
 def case_attention(name, S, dtype, dev, g, flags, short=False, split=False):
     B, Hq, Hkv, D, max_T = 1, 32, 8, 128, 4096
     L = 12
@@ -170,6 +209,10 @@ def run(dtype=torch.float16):
     for B in (1, 2, 4, 8):
         add(case_gateup(f"int8 gate/up+SiLU 2x14336x4096, B={B}", 14336, 4096, B, dtype, dev, g, flags, w8=True))
         add(case_down_w8(f"int8 down 4096x14336 + residual, B={B}", 4096, 14336, B, dtype, dev, g, flags))
+    for B in (1, 4):
+        add(case_group_gateup_packed(f"uint8 group-128 packed gate/up+SiLU 14336x4096x2, B={B}", 14336, 4096, B, dtype,
+                                     dev, g, flags))
+        add(case_group_down(f"uint8 group-128 down 4096x14336 + residual, B={B}", 4096, 14336, B, dtype, dev, g, flags))
     add(case_linear("o_proj 4096x4096 + residual, fp16", 4096, 4096, 1, dtype, False, True, dev, g, flags))
     add(case_gateup("gate/up+SiLU 2x14336x4096, fp16", 14336, 4096, 1, dtype, dev, g, flags))
     for B in (2, 8):

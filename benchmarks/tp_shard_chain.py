@@ -1,17 +1,23 @@
 """One rank's share of a tensor-parallel decode step WITHOUT the collectives, on a single GPU:
 
-  python -m benchmarks.tp_shard_chain [--arch 8b|70b] [--worlds 1,2,4,8] [--steps 64]
+  python -m benchmarks.tp_shard_chain [--arch 8b|70b] [--worlds 1,2,4,8] [--steps 64] [--timeline]
 
 Builds the decode stack at the per-rank shapes of a world-N tensor-parallel run (heads, KV heads, intermediate and
 vocabulary divided by N; random weights) and times CUDA-graph replays of its decode step. The result is the floor a
 rank's step time would have if the all-reduces were free: weight streaming plus the chain of dependent launches. The
 gap between the measured N-GPU step and this figure is what the collectives (and the skew between ranks) cost.
+
+--timeline adds the device-side timeline of one middle layer of the replayed graph, from the records the kernels
+write themselves (%globaltimer; mui_trace_enable): per launch the first CTA's start relative to the previous launch's
+last CTA end, how long until the first CTA got past its wait for the previous kernel, until the last CTA had its
+activations staged, and the whole launch.
 """
 import argparse
 import json
 
 import torch
 
+from benchmarks.timing import read_trace
 from muillm_b200 import capi
 from muillm_b200.decoder_stack import LlamaDecodeStack
 
@@ -54,6 +60,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=16)
+    ap.add_argument("--timeline", action="store_true")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -68,10 +75,16 @@ def main():
                                  flags=capi.MUI_FLAG_PDL)
         prompt = torch.randint(0, cfg["vocab"], (args.batch, args.prompt), generator=torch.Generator().manual_seed(1))
         st = torch.cuda.Stream()
+        nrec = stack.launches_per_step + 8
+        tbuf = torch.empty(nrec * 64, dtype=torch.uint8, device=dev).fill_(255)
         with torch.cuda.stream(st):
             stack.reset(0)
             stack.prefill(prompt)
+            if args.timeline:  # records are bound to launches at capture time and rewritten on every replay
+                capi.check(capi.lib().mui_trace_enable(st.cuda_stream, tbuf.data_ptr(), nrec))
             stack.capture()
+            if args.timeline:
+                capi.check(capi.lib().mui_trace_enable(None, None, 0))
             stack.replay(args.steps)
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record(st)
@@ -84,6 +97,29 @@ def main():
                           "tokens_per_s": 1e3 / ms, "bytes_per_step": nbytes, "tbs": nbytes / ms / 1e9,
                           "launches": stack.launches_per_step, "us_per_launch": ms * 1e3 / stack.launches_per_step,
                           "device_status": capi.device_status()}), flush=True)
+        if args.timeline:
+            with torch.cuda.stream(st):
+                tbuf.fill_(255)
+                stack.replay(1)
+            torch.cuda.synchronize()
+            import ctypes
+            tags = (ctypes.c_int * nrec)()
+            n = min(capi.lib().mui_trace_count(tags, nrec), nrec)
+            recs = read_trace(tbuf, n)
+            names = {1: "linear", 2: "gate/up", 3: "attention", 4: "rope", 5: "all-reduce"}
+            per_layer = max(1, (stack.launches_per_step - 2) // cfg["layers"])
+            first = 1 + per_layer * (cfg["layers"] // 2)
+            rows = []
+            for i in range(first, min(first + per_layer + 1, n)):
+                r, prev = recs[i], recs[i - 1]
+                if None in (r["start"], r["end"], prev["end"]):
+                    continue
+                rows.append({"kernel": names.get(tags[i], str(tags[i])),
+                             "gap_after_prev_end_us": (r["start"] - prev["end"]) / 1e3,
+                             "start_to_past_wait_us": None if r["past_wait"] is None else (r["past_wait"] - r["start"]) / 1e3,
+                             "start_to_staged_us": None if r["staged"] is None else (r["staged"] - r["start"]) / 1e3,
+                             "launch_us": (r["end"] - r["start"]) / 1e3})
+            print(json.dumps({"emulated_world": world, "timeline_of_layer": cfg["layers"] // 2, "launches": rows}), flush=True)
         del stack, w
         torch.cuda.empty_cache()
 

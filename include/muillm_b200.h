@@ -140,11 +140,14 @@ MUI_API mui_status_t mui_prefill_gateup_silu_forward(void* stream, mui_dtype_t d
  * Same math as mui_linear_forward / mui_gateup_silu_forward on de-quantised weights.
  * scales: SYM_ROW -> [N] of dtype; GROUP_MIN -> [N * (K >> group_shift), 2] of dtype (scale, min).
  * Replaces muillm_int8_linear_activ_forward (csrc/int8_linear_kernels.cu:703-784) and
- * muillm_int8_gateupsilu_forward (csrc/int8_gateup_kernels.cu:871-940). Gate and up are separate [I, H]
- * matrices with separate scale arrays in both formats; the reference's interleaved [I, H, 2] pack with
- * [I, G, 2, 2] scale/min (muillm/modules/quantized/int8gateupdownmlp.py:211-230) is split once at load time
- * (gate = pack[:, :, 0], up = pack[:, :, 1]). SYM_ROW with K % 32 == 0 runs on the bulk-copy pipeline;
- * GROUP_MIN runs on the plain-load kernel. */
+ * muillm_int8_gateupsilu_forward (csrc/int8_gateup_kernels.cu:871-940). mui_gateup_silu_w8_forward takes gate and
+ * up as separate [I, H] matrices with separate scale arrays; mui_gateup_silu_w8_packed_forward takes the reference's
+ * own layout, the element-interleaved [I, H, 2] pack (gate, up) with [I, G, 2, 2] {scale, min} pairs
+ * (muillm/modules/quantized/int8gateupdownmlp.py:211-230), and splits the bytes in registers; it returns
+ * MUI_ERR_UNSUPPORTED for shapes the pipeline kernel does not serve (H % 16 != 0, groups outside 32..2048, or a
+ * batch whose staged activations leave no room for two weight stages). Both formats run on the bulk-copy pipeline
+ * when K % 32 == 0 (GROUP_MIN: groups of 32..2048) and the pointers are 16-byte aligned, else on the plain-load
+ * kernel. */
 MUI_API mui_status_t mui_linear_w8_forward(void* stream, mui_dtype_t dtype, mui_w8_format_t fmt, int group_shift,
                                            int B, int N, int K, const void* norm_weights, float epsilon,
                                            const void* qweights, const void* scales, mui_activation_t activ,
@@ -155,6 +158,10 @@ MUI_API mui_status_t mui_gateup_silu_w8_forward(void* stream, mui_dtype_t dtype,
                                                 float epsilon, const void* gate_q, const void* gate_scales,
                                                 const void* up_q, const void* up_scales, const void* x, void* t,
                                                 unsigned flags);
+MUI_API mui_status_t mui_gateup_silu_w8_packed_forward(void* stream, mui_dtype_t dtype, int group_shift, int B, int I,
+                                                       int H, const void* norm_weights, float epsilon,
+                                                       const void* gate_up_q, const void* gate_up_scales_min,
+                                                       const void* x, void* t, unsigned flags);
 /* Full de-quantisation to [N,K] of dtype (batched fallback of the reference,
  * csrc/int8_dequantization_kernel.cu:74). */
 MUI_API mui_status_t mui_w8_dequantize(void* stream, mui_dtype_t dtype, mui_w8_format_t fmt, int group_shift, int N,

@@ -135,6 +135,11 @@ PROTOTYPES = {
         [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_void_p, c_uint],
     ),
+    "mui_gateup_silu_w8_packed_forward": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_uint],
+    ),
     "mui_w8_dequantize": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "mui_rmsnorm_forward": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_uint]),
     "mui_rope_forward": (

@@ -21,6 +21,7 @@
 
 MUI_STATUS_ACCESSOR(gemv)
 
+
 namespace {
 
 // =============================================================================================
@@ -225,7 +226,7 @@ __host__ __device__ inline PipeLayout pipe_layout(int stage_bytes, int stages, i
   l.x_off = stages * stage_bytes;
   int x_bytes = ((x_rows * (Kp + PIPE_XPAD) * 2) + 15) & ~15;
   l.bar_off = l.x_off + x_bytes;
-  l.red_off = l.bar_off + 2 * stages * 8;
+  l.red_off = l.bar_off + (2 * stages + 4) * 8;  // + tile_full[2], tile_free[2] of the asynchronous epilogue
   l.abort_off = l.red_off + 2 * GEMV_CONSUMER_WARPS * PIPE_ROWS * nb * 4;
   l.total = l.abort_off + 16;
   return l;
@@ -233,10 +234,16 @@ __host__ __device__ inline PipeLayout pipe_layout(int stage_bytes, int stages, i
 
 #include "gemv_xchunk.cuh"
 
-template <typename T, int NB, int MODE, int KC, int WB, int NPROD>
-__global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_kernel(const GemvArgs a,
-                                                                                      const int num_stages) {
+// AE = 1 (8-bit weights): asynchronous epilogue. The tile loop on 8-bit weights is bound by the mma.sync issue rate
+// (one m16n8k16 occupies a sub-partition's tensor pipe for ~34 cycles on this part, and 8-bit weights need as many of
+// them per output as 16-bit ones for half the bytes), so every cycle the eight math warps spend at a row block's
+// barrier, in its cross-warp sum or in its epilogue is lost. With AE an extra warp owns the cross-warp sum and the
+// epilogue: the math warps drop their partial tiles into a double-buffered slot, arrive on an mbarrier and go on.
+template <typename T, int NB, int MODE, int KC, int WB, int NPROD, int AE>
+__global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * (NPROD + AE)) gemv_pipe_kernel(const GemvArgs a,
+                                                                                             const int num_stages) {
   using G = PipeGeom<KC, WB>;
+  constexpr int MW = GEMV_CONSUMER_WARPS;  // warps in the tile loop
   constexpr int EB = WB / 8;  // bytes per weight
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int x_rows = (a.moe_mode == GEMV_MOE_SEGMENTS) ? a.slots : NB;
@@ -245,6 +252,8 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
   T* x_s = reinterpret_cast<T*>(smem_raw + lay.x_off);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_raw + lay.bar_off);
   uint64_t* empty_bar = full_bar + num_stages;
+  uint64_t* tile_full = empty_bar + num_stages;  // [2] partial tiles of a row block written (AE)
+  uint64_t* tile_free = tile_full + 2;           // [2] slot drained by the epilogue warp (AE)
   float* red = reinterpret_cast<float*>(smem_raw + lay.red_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + lay.abort_off);
 
@@ -253,7 +262,11 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
   if (tid == 0) {
     for (int s = 0; s < num_stages; ++s) {
       mbar_init(full_bar + s, NPROD);
-      mbar_init(empty_bar + s, GEMV_CONSUMER_WARPS);
+      mbar_init(empty_bar + s, MW);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tile_full + s, MW);
+      mbar_init(tile_free + s, 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -274,22 +287,24 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
   const int cpb = nseg * nchunks;  // stage items per row block
   const int total_items = nblk * cpb;
 
-  if (warp >= GEMV_CONSUMER_WARPS) {
+  if (warp >= MW && warp < MW + NPROD) {
     // ------------------------------ producer warps ------------------------------
     // each of the NPROD warps issues the copies of its share of the 16 tile rows (the copy engine takes one
     // warp's copies one after the other; two issuing warps double the ingest rate of 4 KiB copies)
     constexpr int ROWS_PER_PROD = PIPE_ROWS / NPROD;
-    const int prod = warp - GEMV_CONSUMER_WARPS;
+    const int prod = warp - MW;
     if (a.moe_mode != GEMV_MOE_NONE) pdl_wait_prior_grid();  // expert ids come from the previous kernel
     const uint64_t policy = l2_policy_evict_first();
     const unsigned char* __restrict__ W = reinterpret_cast<const unsigned char*>(a.W);
     const unsigned char* __restrict__ W2 = reinterpret_cast<const unsigned char*>(a.W2);
     int issued = 0;
     bool ok = true;
-    int blk = 0, c = 0;  // item -> (row block, chunk) without divisions
+    int blk = 0, c = 0, seg = 0, kc = 0;  // item -> (row block, segment, chunk) without divisions
+    int s = -1;         // ring slot and its phase bit, advanced without divisions
+    uint32_t ph = 1;
     for (int it = 0; it < total_items; ++it) {
-      const int s = it % num_stages;
-      const uint32_t ph = (it / num_stages) & 1;
+      if (++s == num_stages) s = 0;
+      if (s == 0) ph ^= 1u;
       int w_ok = 1;
       if (lane == 0) w_ok = mbar_wait_bounded(empty_bar + s, ph ^ 1u, abort_flag) ? 1 : 0;
       w_ok = __shfl_sync(MUI_FULL_MASK, w_ok, 0);
@@ -301,7 +316,6 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
         ok = false;
         break;
       }
-      const int seg = c / nchunks, kc = c - seg * nchunks;
       const int rb = r_begin + blk * ROWS_PER_STAGE;
       const int kc_len = min(KC, K - kc * KC);
       const uint32_t bytes = static_cast<uint32_t>(kc_len) * EB;
@@ -320,8 +334,13 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
                      policy);
       }
       issued = it + 1;
+      if (++kc == nchunks) {
+        kc = 0;
+        ++seg;
+      }
       if (++c == cpb) {
         c = 0;
+        seg = 0;
         ++blk;
       }
     }
@@ -337,18 +356,79 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
           mui_dev_set_status(MUI_DEV_TIMEOUT_DRAIN, it % num_stages);
       }
     }
+  } else if (AE && warp == MW + NPROD) {
+    // ------------------------------ epilogue warp (AE) ------------------------------
+    // per row block: the eight warps' partial tiles are summed in a fixed order, then the epilogue; the operands of
+    // the epilogue (per-row scales, residual) are fetched before the wait for the tiles
+    pdl_wait_prior_grid();
+    constexpr int OUTS = ROWS_PER_STAGE * NB;       // outputs per row block
+    constexpr int PER_LANE = (OUTS + 31) / 32;
+    const bool sym = (WB == 8) && a.w8_fmt == MUI_W8_SYM_ROW && a.moe_mode == GEMV_MOE_NONE;
+    for (int blk = 0; blk < nblk; ++blk) {
+      const int rb = r_begin + blk * ROWS_PER_STAGE;
+      const int slot = blk & 1;
+      float pa[PER_LANE], pb[PER_LANE];
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        pa[i] = (MODE == 0) ? 0.f : 1.f;
+        pb[i] = 1.f;
+        const int o = lane + 32 * i, r = o / NB, b = o - r * NB, row = rb + r;
+        if (o < OUTS && row < r_end && b < a.B) {
+          if (MODE == 0) {
+            if (a.residual) pa[i] = ld_act_f32<T>(reinterpret_cast<const T*>(a.residual) + (size_t)b * a.N + row);
+            if (sym) pb[i] = Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[row]);
+          } else if (sym) {
+            pa[i] = Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales)[row]);
+            pb[i] = Elt<T>::to_f32(reinterpret_cast<const T*>(a.scales2)[row]);
+          }
+        }
+      }
+      if (!mbar_wait_bounded(tile_full + slot, (blk >> 1) & 1, abort_flag)) {
+        if (lane == 0 && !*abort_flag) {
+          mui_dev_set_status(MUI_DEV_TIMEOUT_FULL, 64 + slot);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      const float* rbuf = red + slot * (MW * PIPE_ROWS * NB);
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        const int o = lane + 32 * i, r = o / NB, b = o - r * NB, row = rb + r;
+        if (o < OUTS && row < r_end && b < a.B) {
+          if (MODE == 0) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < MW; ++w) v += rbuf[(w * PIPE_ROWS + r) * NB + b];
+            gemv_store_linear<T>(a, b, row, v, 0ull, true, pb[i], pa[i]);
+          } else {
+            float g = 0.f, u = 0.f;
+#pragma unroll
+            for (int w = 0; w < MW; ++w) {
+              g += rbuf[(w * PIPE_ROWS + r) * NB + b];
+              u += rbuf[(w * PIPE_ROWS + r + 8) * NB + b];
+            }
+            float score = 1.f;
+            if (a.moe_mode == GEMV_MOE_ROWS) score = gemv_slot_score<T>(a, row / a.N);
+            gemv_store_gateup<T>(a, b, row, total_rows, g, u, score, a.moe_mode == GEMV_MOE_NONE, pa[i], pb[i]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tile_free + slot);
+    }
+    if (lane == 0) trace_end(a.trace);
   } else {
     // ------------------------------ consumer warps ------------------------------
     GemvNormPre norm_pre;
+    norm_pre.have = false;
     if (a.moe_mode != GEMV_MOE_SEGMENTS) gemv_prefetch_norm<T, NB>(a, tid, norm_pre);
-    else norm_pre.have = false;
     pdl_wait_prior_grid();
     if (tid == 0) trace_mark(a.trace, 2, false);
     const unsigned long long comm_seq = (MODE == 0 && a.use_comm) ? comm_begin(a.comm) : 0ull;
     // Epilogue operands (residual, per-row 8-bit scales) of every row block this thread will finish, loaded now so
     // that their round trip overlaps the activation staging instead of stalling a row block's epilogue.
     constexpr int EPI_MAX = 16;
-    const bool epi_pre = nblk <= EPI_MAX;
+    const bool epi_pre = !AE && nblk <= EPI_MAX;
     float epi_a[EPI_MAX], epi_b[EPI_MAX];  // MODE 0: residual, scale; MODE 1: gate scale, up scale
 #pragma unroll
     for (int i = 0; i < EPI_MAX; ++i) {
@@ -390,10 +470,12 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
     const uint32_t stage_base = smem_u32(stage_mem);
     const uint32_t x_base = smem_u32(x_s);
 
-    int blk = 0, c = 0;
+    int blk = 0, c = 0, seg = 0, kc = 0;
+    int s = -1;         // ring slot and its phase bit, advanced without divisions
+    uint32_t ph = 1;
     for (int it = 0; it < total_items; ++it) {
-      const int s = it % num_stages;
-      const uint32_t ph = (it / num_stages) & 1;
+      if (++s == num_stages) s = 0;
+      if (s == 0) ph ^= 1u;
       if (!mbar_wait_bounded(full_bar + s, ph, abort_flag)) {
         if (lane == 0 && !*abort_flag) {
           mui_dev_set_status(MUI_DEV_TIMEOUT_FULL, s);
@@ -401,7 +483,6 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
         }
         break;
       }
-      const int seg = c / nchunks, kc = c - seg * nchunks;
       const int kc_len = min(KC, K - kc * KC);
       const uint32_t a_addr = stage_base + static_cast<uint32_t>(s) * G::STAGE_BYTES + a_lane_off;
       if (WB == 16) {
@@ -409,7 +490,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
         // MoE segments: segment `seg` multiplies activation row `seg` (NB == 1 there)
         const uint32_t b_addr = x_base + b_lane_off + static_cast<uint32_t>((seg * x_pitch + kc * KC) * 2);
 #pragma unroll 4
-        for (int j = warp; j < nsteps; j += GEMV_CONSUMER_WARPS) {
+        for (int j = warp; j < nsteps; j += MW) {
           uint32_t af[4], b0, b1;
           ldmatrix_x4(af, a_addr + j * 32);
           ldmatrix_x2(b0, b1, b_addr + j * 32);
@@ -426,7 +507,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
         const uint32_t xmask = sgn ? 0x80808080u : 0u, cbias = W8Cvt<T>::bias_for(sgn);
         const uint32_t x_addr = smem_u32(xrow);
 #pragma unroll 4
-        for (int j = warp; j < nsteps; j += GEMV_CONSUMER_WARPS) {
+        for (int j = warp; j < nsteps; j += MW) {
           uint32_t r[4];
           ldmatrix_x4(r, a_addr + j * 32);
           uint32_t xa0, xa1, xb0, xb1;
@@ -444,13 +525,28 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar + s);
 
+      if (++kc == nchunks) {
+        kc = 0;
+        ++seg;
+      }
       if (++c == cpb) {
         // row block complete: sum the eight warps' partial tiles in a fixed order, then the epilogue
         c = 0;
+        seg = 0;
         const int rb = r_begin + blk * ROWS_PER_STAGE;
-        float* rbuf = red + (blk & 1) * (GEMV_CONSUMER_WARPS * PIPE_ROWS * NB);
+        float* rbuf = red + (blk & 1) * (MW * PIPE_ROWS * NB);
         // this thread holds D[tile row lane/4 (+8)][batch (lane%4)*2 + {0,1}]
         const int trow = lane >> 2, n0 = (lane & 3) * 2;
+        if (AE && blk >= 2) {
+          // the slot's previous tiles (row block blk - 2) must have been drained by the epilogue warp
+          if (!mbar_wait_bounded(tile_free + (blk & 1), ((blk >> 1) - 1) & 1, abort_flag)) {
+            if (lane == 0 && !*abort_flag) {
+              mui_dev_set_status(MUI_DEV_TIMEOUT_EMPTY, 64 + (blk & 1));
+              *abort_flag = 1;
+            }
+            break;
+          }
+        }
         if (WB == 8) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -467,6 +563,12 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
           rbuf[(warp * PIPE_ROWS + trow + 8) * NB + n0 + 1] = d[3];
         }
         d[0] = d[1] = d[2] = d[3] = 0.f;
+        if (AE) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tile_full + (blk & 1));  // release: the tile stores above are visible to the waiter
+          ++blk;
+          continue;
+        }
         named_bar_sync(1, GEMV_CONSUMER_THREADS);
         if (tid < ROWS_PER_STAGE * NB) {
           const int r = tid / NB, b = tid - r * NB;
@@ -475,12 +577,12 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
             if (MODE == 0) {
               float v = 0.f;
 #pragma unroll
-              for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) v += rbuf[(w * PIPE_ROWS + r) * NB + b];
+              for (int w = 0; w < MW; ++w) v += rbuf[(w * PIPE_ROWS + r) * NB + b];
               gemv_store_linear<T>(a, b, row, v, comm_seq, epi_pre, epi_b[0], epi_a[0]);
             } else {
               float g = 0.f, u = 0.f;
 #pragma unroll
-              for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) {
+              for (int w = 0; w < MW; ++w) {
                 g += rbuf[(w * PIPE_ROWS + r) * NB + b];
                 u += rbuf[(w * PIPE_ROWS + r + 8) * NB + b];
               }
@@ -503,9 +605,11 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * NPROD) gemv_pipe_
     if (MODE == 0 && a.use_comm)
       gemv_comm_tail<T>(a, comm_seq, tid, GEMV_CONSUMER_THREADS, 1, r_end - r_begin,
                         [r_begin](int i) { return r_begin + i; });
-    if (tid == 0) trace_end(a.trace);
+    if (!AE && tid == 0) trace_end(a.trace);
   }
 }
+
+#include "gemv_w8g.cuh"
 
 // =============================================================================================
 // host dispatch
@@ -514,6 +618,9 @@ template <typename T, int NB, int MODE, int KC, int WB>
 mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int total_rows, int x_rows,
                          const MuiDeviceInfo* dev, bool* applicable) {
   using G = PipeGeom<KC, WB>;
+  // 8-bit weights: asynchronous epilogue warp (never combined with the fused all-reduce, whose tail runs on the
+  // consumer threads after their own pushes)
+  constexpr int AE = (WB == 8) ? 1 : 0;
   // One CTA per SM with (nearly) all of its shared memory: ~190 KiB of copies in flight per SM is what keeps
   // HBM busy; with half of that the kernel runs ~25 % slower.
   // 226 KiB: with K = 14336 the staged activations (28 KiB) and three 64.25 KiB stages need 222.8 KiB
@@ -531,7 +638,11 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   const int sms = std::max(1, dev->sm_count - std::min(a.reserve_sms, dev->sm_count / 4));
   const int grid = std::max(1, std::min(units, sms));
   // one producer warp: a second one doubles the issue rate of 4 KiB copies but measured no faster end to end
-  auto kern = gemv_pipe_kernel<T, NB, MODE, KC, WB, 1>;
+  if (AE && a.use_comm) {
+    mui_set_error("8-bit weights with the fused all-reduce are not supported");
+    return MUI_ERR_UNSUPPORTED;
+  }
+  auto kern = gemv_pipe_kernel<T, NB, MODE, KC, WB, 1, AE>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -539,8 +650,35 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
                                         cudaSharedmemCarveoutMaxShared));
     configured = true;
   }
-  MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(GEMV_CONSUMER_THREADS + 32), (size_t)lay.total, stream, pdl, a,
+  MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(GEMV_CONSUMER_THREADS + 32 * (1 + AE)), (size_t)lay.total, stream, pdl, a,
                             stages));
+  return MUI_OK;
+}
+
+// Per-group 8-bit format on the bulk-copy pipeline (gemv_w8g.cuh); *applicable = false when the activations leave no
+// room for two weight stages.
+template <typename T, int NB, int LAYOUT>
+mui_status_t launch_gm(cudaStream_t stream, const GemvArgs& a, int pdl, const MuiDeviceInfo* dev, bool* applicable) {
+  const int out_tile = (LAYOUT == 2) ? 32 : 16;
+  const int ngroups = a.K >> a.group_shift;
+  const int budget = 226 * 1024;
+  const int fixed = gm_layout(0, NB, a.Kp, ngroups, out_tile).total;
+  const int stages = std::min((budget - fixed) / GM_STAGE_BYTES, PIPE_MAX_STAGES);
+  *applicable = stages >= 2;
+  if (!*applicable) return MUI_OK;
+  const GmLayout lay = gm_layout(stages, NB, a.Kp, ngroups, out_tile);
+  const int units = (a.N + 7) / 8;
+  const int sms = std::max(1, dev->sm_count - std::min(a.reserve_sms, dev->sm_count / 4));
+  const int grid = std::max(1, std::min(units, sms));
+  auto kern = gemv_pipe_gm_kernel<T, NB, LAYOUT>;
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    MUI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared));
+    configured = true;
+  }
+  MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(32 * (GM_MW + 2)), (size_t)lay.total, stream, pdl, a, stages));
   return MUI_OK;
 }
 
@@ -582,6 +720,29 @@ mui_status_t launch_gemv_t(cudaStream_t stream, const GemvArgs& a, unsigned flag
                        (MODE == 0 || (reinterpret_cast<uintptr_t>(a.W2) & 15) == 0) &&
                        (WB == 16 || a.w8_fmt == MUI_W8_SYM_ROW);
   bool use_pipe = aligned && !(flags & MUI_FLAG_FORCE_GENERIC);
+  if constexpr (WB == 8) {
+    if (a.w8_fmt == MUI_W8_GROUP_MIN) {
+      // groups of 32..2048 weights, whole groups per stage, 16-byte aligned rows and tables
+      const bool gm_ok = a.group_shift >= 5 && a.group_shift <= 11 && (a.K % 16) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(a.W) & 15) == 0) &&
+                         (MODE == 0 || a.w8_pack || (reinterpret_cast<uintptr_t>(a.W2) & 15) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(a.scales) & 7) == 0) && a.moe_mode == GEMV_MOE_NONE &&
+                         !a.use_comm && !(flags & MUI_FLAG_FORCE_GENERIC);
+      if (gm_ok) {
+        bool applicable = false;
+        mui_status_t st;
+        if (MODE == 0) st = launch_gm<T, NB, 0>(stream, a, pdl, dev, &applicable);
+        else if (a.w8_pack) st = launch_gm<T, NB, 2>(stream, a, pdl, dev, &applicable);
+        else st = launch_gm<T, NB, 1>(stream, a, pdl, dev, &applicable);
+        if (st != MUI_OK || applicable) return st;
+      }
+      if (a.w8_pack) {
+        mui_set_error("packed 8-bit gate/up: shape not served by the pipeline kernel (H=%d, group 2^%d, batch %d)",
+                      a.K, a.group_shift, a.B);
+        return MUI_ERR_UNSUPPORTED;
+      }
+    }
+  }
   if constexpr (NB >= 2) {
     if (use_pipe && a.moe_mode == GEMV_MOE_NONE && ((a.K & 7) == 0) &&
         ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) &&

@@ -37,6 +37,7 @@ struct GemvArgs {
   int num_shared;  // shared experts among the slots
   int group_shift; // 8-bit GROUP_MIN: log2(group size)
   int w8_fmt;      // -1: 16-bit weights; else mui_w8_format_t of the 8-bit weights
+  int w8_pack;     // gate/up GROUP_MIN: W is the element-interleaved pack [N][K][2], scales [N][K/group][2][2]
   unsigned long long* trace;  // launch-trace record or null
   // weights of the kernels that follow on the stream: once its own copies are issued, the producer warp pulls
   // this CTA's slice of them into L2, so that HBM keeps streaming through this kernel's tail, the launch gap and

@@ -109,6 +109,34 @@ mui_status_t mui_gateup_silu_w8_forward(void* stream, mui_dtype_t dtype, mui_w8_
   return mui_launch_gemv16((cudaStream_t)stream, dtype, 1, a, flags);
 }
 
+mui_status_t mui_gateup_silu_w8_packed_forward(void* stream, mui_dtype_t dtype, int group_shift, int B, int I, int H,
+                                               const void* norm_weights, float epsilon, const void* gate_up_q,
+                                               const void* gate_up_scales_min, const void* x, void* t,
+                                               unsigned flags) {
+  if (mui_status_t s = check_w8(dtype, MUI_W8_GROUP_MIN, group_shift, H)) return s;
+  MUI_REQUIRE(gate_up_q && gate_up_scales_min && x && t, MUI_ERR_INVALID_ARG, "null pointer");
+  MUI_REQUIRE(B >= 1 && B <= 8, MUI_ERR_UNSUPPORTED, "B=%d outside 1..8 (larger batches de-quantise and use a GEMM)", B);
+  MUI_REQUIRE(I >= 1 && H >= 1, MUI_ERR_INVALID_ARG, "I=%d, H=%d must be positive", I, H);
+  GemvArgs a;
+  memset(&a, 0, sizeof(a));
+  a.W = gate_up_q;
+  a.scales = gate_up_scales_min;
+  a.x = x;
+  a.norm_w = norm_weights;
+  a.y = t;
+  a.eps = epsilon;
+  a.N = I;
+  a.K = H;
+  a.B = B;
+  a.Kp = (H + 7) & ~7;
+  a.moe_mode = GEMV_MOE_NONE;
+  a.slots = 1;
+  a.group_shift = group_shift;
+  a.w8_fmt = (int)MUI_W8_GROUP_MIN;
+  a.w8_pack = 1;
+  return mui_launch_gemv16((cudaStream_t)stream, dtype, 1, a, flags);
+}
+
 mui_status_t mui_w8_dequantize(void* stream, mui_dtype_t dtype, mui_w8_format_t fmt, int group_shift, int N, int K,
                                const void* qweights, const void* scales, void* out) {
   if (mui_status_t s = check_w8(dtype, fmt, group_shift, K)) return s;

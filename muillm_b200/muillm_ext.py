@@ -133,9 +133,26 @@ def muillm_int8_gateupsilu_dequantize_forward(gate_up_weights, gate_up_scales_mi
             ops.muillm_int8_dequantize_forward(uq, us, group_size_shift))
 
 
+def _packed_gateup_fits(rows, H, group_size_shift):
+    """Shared memory of the packed gate/up kernel: staged activations (rows rounded up to 1/2/4/8), group sums,
+    partial tiles and at least two 64.25 KiB weight stages inside 226 KiB (gemv_w8g.cuh, gm_layout)."""
+    nb = 1 if rows <= 1 else 2 if rows <= 2 else 4 if rows <= 4 else 8
+    fixed = nb * (H + 8) * 2 + (H >> group_size_shift) * 32 + 2 * 16 * 32 * nb * 4 + 256
+    return fixed + 2 * 16 * (4096 + 16) <= 226 * 1024
+
+
 def muillm_int8_gateupsilu_forward(norm_weights, epsilon, gate_up_weights, gate_up_scales_min_vals, group_size_shift,
                                    x):
-    """silu(G xn) * (U xn) on the reference's packed 8-bit weights (csrc/int8_gateup_kernels.cu:871-940)."""
+    """silu(G xn) * (U xn) on the reference's packed 8-bit weights (csrc/int8_gateup_kernels.cu:871-940). Decode rows
+    stream the pack as it is (the kernel splits the interleaved bytes in registers); shapes that kernel does not
+    serve (groups under 32 weights, unaligned rows, more than 8 rows) go through the split halves."""
+    rows = x.numel() // x.shape[-1]
+    if (rows <= 8 and 5 <= group_size_shift <= 11 and gate_up_weights.shape[1] % 16 == 0
+            and gate_up_weights.is_contiguous() and gate_up_scales_min_vals.is_contiguous()
+            and gate_up_weights.data_ptr() % 16 == 0 and gate_up_scales_min_vals.data_ptr() % 8 == 0
+            and _packed_gateup_fits(rows, gate_up_weights.shape[1], group_size_shift)):
+        return ops.int8_gateup_silu_packed(x, gate_up_weights, gate_up_scales_min_vals, group_size_shift,
+                                           norm_weights=norm_weights, epsilon=epsilon)
     gq, gs, uq, us = _split_gateup_pack(gate_up_weights, gate_up_scales_min_vals, group_size_shift)
     return ops.int8_gateup_silu(x, gq, gs, uq, us, group_size_shift=group_size_shift, norm_weights=norm_weights,
                                 epsilon=epsilon)

@@ -328,6 +328,26 @@ def int8_gateup_silu(x, gate_q, gate_scales, up_q, up_scales, group_size_shift=0
     return out
 
 
+def int8_gateup_silu_packed(x, gate_up_q, gate_up_scales_min, group_size_shift, norm_weights=None, epsilon=0.0,
+                            flags=0):
+    """t = silu(G xn) * (U xn) on the reference's own packed layout: gate_up_q [I, H, 2] uint8 (gate, up interleaved
+    element by element), gate_up_scales_min [I * G, 2, 2] (gate {scale, min}, up {scale, min}) as built by
+    muillm/modules/quantized/int8gateupdownmlp.py:211-230. Raises capi.MuiError (MUI_ERR_UNSUPPORTED) for shapes the
+    pipeline kernel does not serve."""
+    for t, n in ((x, "x"), (gate_up_q, "gate_up_q"), (gate_up_scales_min, "gate_up_scales_min"),
+                 (norm_weights, "norm_weights")):
+        _check_input(t, n)
+    I, H, two = gate_up_q.shape
+    if two != 2 or gate_up_q.dtype != torch.uint8:
+        raise ValueError("gate_up_q must be a uint8 [I, H, 2] tensor")
+    B = _rows(x)
+    out = torch.empty(x.shape[:-1] + (I,), dtype=x.dtype, device=x.device)
+    capi.check(capi.lib().mui_gateup_silu_w8_packed_forward(
+        _stream(), _dtype_code(x), int(group_size_shift), B, I, H, _ptr(norm_weights), float(epsilon),
+        _ptr(gate_up_q), _ptr(gate_up_scales_min), _ptr(x), _ptr(out), flags))
+    return out
+
+
 def muillm_int8_dequantize_forward(weights, scales_min_vals, group_size_shift, dtype=None):
     """Whole-matrix de-quantisation (csrc/module.cpp:180, csrc/int8_dequantization_kernel.cu:74)."""
     _check_input(weights, "weights")

@@ -30,7 +30,13 @@ def test_reference_test_files_pass_over_the_dropin():
     ref = os.path.abspath(REF)
     env = dict(os.environ)
     env["PYTHONPATH"] = os.pathsep.join([ROOT, HERE, ref, env.get("PYTHONPATH", "")])
-    files = [os.path.join("tests", f) for f in FILES if os.path.isfile(os.path.join(ref, "tests", f))]
+    import transformers.cache_utils as hf_cache
+
+    names = list(FILES)
+    if not hasattr(hf_cache, "HybridChunkedCache"):
+        # the installed transformers no longer has the class this file compares with (see tests/dropin_plugin.py)
+        names.remove("test_hybridchunked_kvcache.py")
+    files = [os.path.join("tests", f) for f in names if os.path.isfile(os.path.join(ref, "tests", f))]
     assert files, "the checkout has none of the expected test files"
     r = subprocess.run([sys.executable, "-m", "pytest", "-p", "dropin_plugin", "-p", "no:cacheprovider", "-q", "-rf",
                         *files], cwd=ref, env=env, capture_output=True, text=True, timeout=1500)

@@ -85,3 +85,66 @@ def test_quantised_weights_reach_the_kernel_bit_exact():
     q, s = oracle.rtn_symrow_quantize(W)
     deq = ops.muillm_int8_dequantize_forward(q.cuda(), s.cuda(), 0).cpu()
     assert torch.equal(deq, oracle.rtn_symrow_dequantize(q, s).to(torch.float16))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the reference's per-group {scale, min} format on the bulk-copy pipeline (groups of >= 32, K % 32 == 0) and on the
+# plain-load kernel, and its element-interleaved gate/up pack
+# ---------------------------------------------------------------------------------------------------------------
+def _group_pack(gq, gsm, uq, usm):
+    """gate/up -> the reference's pack: [I, H, 2] bytes and [I * G, 2, 2] {scale, min} pairs
+    (muillm/modules/quantized/int8gateupdownmlp.py:211-230)."""
+    pack = torch.stack([gq, uq], dim=-1).contiguous()
+    sm = torch.stack([gsm.reshape(-1, 2), usm.reshape(-1, 2)], dim=1).contiguous()
+    return pack, sm
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("path", list(PATHS))
+@pytest.mark.parametrize("N,K,B,shift", [(4096, 4096, 1, 7), (515, 6144, 3, 7), (1024, 14336, 1, 7), (130, 1024, 8, 5),
+                                         (256, 8192, 2, 9), (64, 4096, 4, 11)])
+def test_linear_group_min_both_kernels(dtype, path, N, K, B, shift):
+    g = _gen(N + K + shift + B)
+    W = (torch.randn(N, K, generator=g) * 0.02 + 0.003).to(dtype)
+    q, sm = oracle.rtn_group_quantize(W, group_shift=shift)
+    x = (torch.randn(B, K, generator=g) + 0.25).to(dtype)  # a non-zero mean exercises the min * sum(x) term
+    nw = (1 + 0.01 * torch.randn(K, generator=g)).to(dtype)
+    res = torch.randn(B, N, generator=g).to(dtype)
+    want = oracle.linear(x, oracle.rtn_group_dequantize(q, sm, group_shift=shift), norm_weights=nw, eps=1e-5,
+                         residual=res, out_dtype=dtype)
+    got = ops.muillm_int8_linear_forward(x.cuda(), q.cuda(), sm.cuda(), shift, norm_weights=nw.cuda(), epsilon=1e-5,
+                                         residual=res.cuda(), flags=PATHS[path])
+    _close(got, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("I,H,B,shift", [(14336, 4096, 1, 7), (1000, 4096, 4, 7), (72, 3072, 2, 5), (520, 2048, 8, 6)])
+def test_gateup_group_min_split_and_packed(dtype, I, H, B, shift):
+    g = _gen(I + H + B)
+    mk = lambda *s: (torch.randn(*s, generator=g) * 0.02 + 0.002).to(dtype)
+    gq, gsm = oracle.rtn_group_quantize(mk(I, H), group_shift=shift)
+    uq, usm = oracle.rtn_group_quantize(mk(I, H), group_shift=shift)
+    x = (torch.randn(B, H, generator=g) + 0.1).to(dtype)
+    nw = (1 + 0.01 * torch.randn(H, generator=g)).to(dtype)
+    want = oracle.gateup_silu(x, oracle.rtn_group_dequantize(gq, gsm, group_shift=shift),
+                              oracle.rtn_group_dequantize(uq, usm, group_shift=shift), norm_weights=nw, eps=1e-5,
+                              out_dtype=dtype)
+    xc, nwc = x.cuda(), nw.cuda()
+    split = ops.int8_gateup_silu(xc, gq.cuda(), gsm.cuda(), uq.cuda(), usm.cuda(), group_size_shift=shift,
+                                 norm_weights=nwc, epsilon=1e-5)
+    _close(split, want)
+    generic = ops.int8_gateup_silu(xc, gq.cuda(), gsm.cuda(), uq.cuda(), usm.cuda(), group_size_shift=shift,
+                                   norm_weights=nwc, epsilon=1e-5, flags=capi.MUI_FLAG_FORCE_GENERIC)
+    _close(generic, want)
+    pack, sm = _group_pack(gq, gsm, uq, usm)
+    packed = ops.int8_gateup_silu_packed(xc, pack.cuda(), sm.cuda(), shift, norm_weights=nwc, epsilon=1e-5)
+    _close(packed, want)
+
+
+def test_packed_gateup_refuses_what_the_pipeline_cannot_serve():
+    I, H, shift = 64, 64, 3  # groups of 8 weights
+    pack = torch.zeros(I, H, 2, dtype=torch.uint8).cuda()
+    sm = torch.zeros(I * (H >> shift), 2, 2, dtype=torch.float16).cuda()
+    x = torch.zeros(1, H, dtype=torch.float16).cuda()
+    with pytest.raises(RuntimeError, match="packed 8-bit gate/up"):
+        ops.int8_gateup_silu_packed(x, pack, sm, shift)
