@@ -56,9 +56,28 @@ def _tensor_core_prefill_ok(x, *weights):
         x.data_ptr() % 16 == 0
 
 
+def _not_dispatchable_on_gpu(weights):
+    """The reference's modules dispatch to their kernels only for fp16 / bf16 weights on a GPU and use torch's ops
+    otherwise (csrc/modules/linear_module.cpp:29-32, 60-80). The drop-in does the same for other dtypes ON THE GPU;
+    CPU tensors are refused by the operators themselves (this library has no CPU path)."""
+    return weights.is_cuda and weights.dtype not in (torch.float16, torch.bfloat16)
+
+
+def _torch_rmsnorm(x, norm_weights, epsilon):
+    if norm_weights is None:
+        return x
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + epsilon)).to(x.dtype) * norm_weights
+
+
 def _linear_any_rows(x, weights, norm_weights=None, epsilon=0.0, mul_bias=None, add_bias=None, residual=None):
     """Decode rows -> GEMV kernel; prefill -> RMSNorm kernel + the tcgen05 GEMM with the epilogue fused (the reference
     calls at::linear there, csrc/modules/linear_module.cpp:40-80); other dtypes / layouts -> torch GEMM."""
+    if _not_dispatchable_on_gpu(weights) and x.is_cuda:
+        y = F.linear(_torch_rmsnorm(x, norm_weights, epsilon), weights)
+        y = y * mul_bias if mul_bias is not None else y
+        y = y + add_bias if add_bias is not None else y
+        return y + residual if residual is not None else y
     if _rows(x) <= _MAX_GEMV_ROWS:
         return ops.muillm_linear_forward(None, x, weights, norm_weights=norm_weights, epsilon=epsilon,
                                          mul_bias=mul_bias, add_bias=add_bias, residual=residual)
@@ -81,6 +100,10 @@ def muillm_linear_forward(engine, x, weights, norm_weights=None, epsilon=0.0, mu
 
 
 def _mlp_any_rows(norm_weights, epsilon, gate_weights, up_weights, down_weights, residual, x):
+    if _not_dispatchable_on_gpu(gate_weights) and x.is_cuda:
+        xn = _torch_rmsnorm(x, norm_weights, epsilon)
+        y = F.linear(F.silu(F.linear(xn, gate_weights)) * F.linear(xn, up_weights), down_weights)
+        return y + residual if residual is not None else y
     if _rows(x) <= _MAX_GEMV_ROWS:
         return ops.muillm_gateupsilu_forward(None, norm_weights, epsilon, gate_weights, up_weights, down_weights,
                                              residual, x)
@@ -369,6 +392,8 @@ class muillm_embedding_module_ptr(_Handle):
         self.weights = weights
 
     def forward(self, inputs):
+        if _not_dispatchable_on_gpu(self.weights) and inputs.is_cuda:
+            return F.embedding(inputs, self.weights)
         return ops.muillm_embedding_forward(self.weights, inputs)
 
 
