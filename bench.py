@@ -247,6 +247,10 @@ def cpu_decode_sample(cfg, seconds_budget=20.0, sample_layers=2, tokens=3):
                       f"CPU oracle; layer time scaled to {cfg['layers']} layers"}
 
 
+WORKLOAD = ("Llama-3.1-8B-arch decode (BASELINE config 3): 32 layers, hidden 4096, 32q/8kv heads, head_dim 128, "
+            "intermediate 14336, vocab 128256, bs=1, 16-token prompt, static KV cache 4096")
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -259,8 +263,9 @@ def run_reference(args):
         "impl": "reference", "metric": "bs=1 decode tokens/s/user (Llama-3-8B arch)", "value": v, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / v,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "Llama-3.1-8B-arch decode, bs=1, random-init, CPU oracle (PyTorch fp32) on host cores",
-                   "seq_len": PROMPT_LEN, "parallelism": "cpu"},
+        "config": {"workload": WORKLOAD, "global_batch": 1, "seq_len": f"{PROMPT_LEN}..{PROMPT_LEN + max(1, args.steps)}",
+                   "parallelism": "host cores (PyTorch fp32 restatement of the path; the reference's own kernels are "
+                                  "HIP-only and cannot be built here)"},
         "cpu_baseline": res,
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": time.time() - t0,
@@ -398,8 +403,7 @@ def run_gpu(args):
         "scaling": "strong",
         "vs_baseline": (value / BASELINE_TOK_S[world]) if world in BASELINE_TOK_S else None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "Llama-3.1-8B-arch decode (BASELINE config 3): 32 layers, hidden 4096, 32q/8kv heads, "
-                               "head_dim 128, intermediate 14336, vocab 128256, bs=1, 16-token prompt, static KV cache 4096",
+        "config": {"workload": WORKLOAD,
                    "global_batch": users, "seq_len": f"{PROMPT_LEN + W}..{PROMPT_LEN + W + K}",
                    "parallelism": "single GPU" if world == 1 else f"tp{world} (sharded QKV/o_proj/MLP/lm_head, "
                                                                     f"GEMV + all-reduce fused over NVLink peer stores)",

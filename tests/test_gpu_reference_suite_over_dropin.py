@@ -29,6 +29,8 @@ NOT_THE_DROPIN = [
     ("must be a CUDA tensor", "CPU tensors: this library has no CPU path and refuses them, the reference falls back to torch"),
     ("KeyError: 'default'", "the reference's rotary module indexes transformers' ROPE_INIT_FUNCTIONS['default'], gone "
                             "from newer transformers releases"),
+    ("KeyError: 'factor'", "the reference's Llama-4 rotary set-up reaches transformers' llama3 RoPE initialiser with the "
+                           "older `rope_scaling` layout (raised inside transformers/modeling_rope_utils.py)"),
     ("has no attribute 'key_cache'", "the reference's caches read `key_cache` / `value_cache` of transformers' Cache "
                                      "classes, gone from newer transformers releases"),
     ("tensor_parallelism 1 is bigger than number of available devices", "no GPU visible"),
