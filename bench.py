@@ -371,6 +371,29 @@ def run_gpu(args):
                 plugin_tok_s = time_plugin_e2e(w, cfg, prompt, K, W, MAX_SEQ)
         except Exception as e:  # the headline numbers above do not depend on this leg: report it instead of dying
             plugin_error = f"{type(e).__name__}: {e}"
+    long_ctx = None
+    if world == 1:
+        # the same decode step with ~4000 tokens already in the KV cache (rows of zeros: timing only): the stack
+        # then runs the token-split attention kernel instead of the short-context one
+        try:
+            S0, steps_long = MAX_SEQ - 96, 32
+            with torch.cuda.stream(stream):
+                long_stack = LlamaDecodeStack(w, cfg, max_seq=MAX_SEQ, batch=1, max_new_tokens=64, flags=flags)
+                long_stack.reset(S0)
+                long_stack.set_tokens(prompt[:, 0].contiguous())
+                long_stack.capture()
+                long_stack.replay(8)
+                ls, le = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ls.record(stream)
+                long_stack.replay(steps_long)
+                le.record(stream)
+            torch.cuda.synchronize()
+            sec = ls.elapsed_time(le) * 1e-3 / steps_long
+            long_ctx = {"S": f"{S0 + 8}..{S0 + 8 + steps_long}", "tokens_per_s": 1.0 / sec, "ms_per_step": sec * 1e3,
+                        "kv_bytes_per_step": kv_bytes_per_token(cfg, S0 + 8 + steps_long // 2)}
+            del long_stack
+        except Exception as e:
+            long_ctx = {"error": f"{type(e).__name__}: {e}"}
     with torch.cuda.stream(stream):
         k_seconds, k_bytes = time_dominant_kernel(w, local_cfg, flags)
     status = capi.device_status()
@@ -432,6 +455,8 @@ def run_gpu(args):
                               "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 8}
     elif plugin_error is not None:
         line["e2e_plugin"] = {"error": plugin_error}
+    if long_ctx is not None:
+        line["long_context"] = long_ctx
     if parity is not None:
         line["parity"] = parity
     print(json.dumps(line), flush=True)
