@@ -280,7 +280,63 @@ def hf_llama4_model_fixture(out, head_dim=None):
         out["sd/" + name] = t.half().numpy()
 
 
+def hf_moe_and_masked_attention_fixture(out):
+    """Two pins the other fixtures do not hold directly: the Llama-4 MoE block (router, top-k sigmoid, routed experts
+    on score-scaled inputs, shared expert; the module the reference's tests/test_gateupdownmlpmoe.py compares with)
+    and eager GQA attention of one query token under an additive mask (the call of tests on masked decoding)."""
+    from types import SimpleNamespace
+
+    from transformers import Llama4TextConfig
+    from transformers.models.llama.modeling_llama import eager_attention_forward
+    from transformers.models.llama4.modeling_llama4 import Llama4TextMoe
+
+    torch.manual_seed(3)
+    g = torch.Generator().manual_seed(4)
+    cfg = Llama4TextConfig(hidden_size=64, intermediate_size=48, intermediate_size_mlp=48, num_local_experts=6,
+                           num_experts_per_tok=2, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                           head_dim=16, vocab_size=64)
+    moe = Llama4TextMoe(cfg).float().eval()
+    with torch.no_grad():
+        for p_ in moe.parameters():
+            p_.copy_(torch.randn(p_.shape, generator=g) * 0.1)
+        x = torch.randn(1, 1, 64, generator=g)
+        y, router_logits = moe(x)
+    E, H, I = 6, 64, 48
+    gu = moe.experts.gate_up_proj.detach()  # [E, H, 2I]: x @ gate_up -> (gate | up)
+    out["moe_x"] = x.numpy()
+    out["moe_router_w"] = moe.router.weight.detach().numpy()
+    out["moe_router_logits"] = router_logits.detach().numpy()
+    # row-major [rows, H] matrices, shared expert first, as the kernels take them
+    out["moe_gate"] = torch.cat([moe.shared_expert.gate_proj.weight.detach()] +
+                                [gu[e, :, :I].t().contiguous() for e in range(E)], 0).numpy()
+    out["moe_up"] = torch.cat([moe.shared_expert.up_proj.weight.detach()] +
+                              [gu[e, :, I:].t().contiguous() for e in range(E)], 0).numpy()
+    out["moe_down"] = torch.cat([moe.shared_expert.down_proj.weight.detach()] +
+                                [moe.experts.down_proj[e].detach().t().contiguous() for e in range(E)], 0).numpy()
+    out["moe_y"] = y.detach().reshape(1, 1, 64).numpy()
+    out["moe_top_k"] = np.array(2)
+
+    B, Hq, Hkv, D, S = 2, 8, 2, 32, 29
+    q = torch.randn(B, Hq, 1, D, generator=g)
+    k = torch.randn(B, Hkv, S, D, generator=g)
+    v = torch.randn(B, Hkv, S, D, generator=g)
+    keep = torch.rand(B, S, generator=g) > 0.3
+    keep[:, -1] = True  # the new token always attends itself
+    mask = torch.where(keep, 0.0, torch.finfo(torch.float32).min)[:, None, None, :]
+    module = SimpleNamespace(num_key_value_groups=Hq // Hkv, training=False)
+    o, _ = eager_attention_forward(module, q, k, v, mask, scaling=D ** -0.5, dropout=0.0)
+    out["mattn_q"], out["mattn_k"], out["mattn_v"] = q.numpy(), k.numpy(), v.numpy()
+    out["mattn_mask"] = mask[:, 0, 0, :].numpy()
+    out["mattn_out"] = o.reshape(B, 1, Hq * D).numpy()
+
+
 def main():
+    if sys.argv[1:] == ["moe_mask"]:
+        d = {}
+        hf_moe_and_masked_attention_fixture(d)
+        np.savez_compressed(os.path.join(HERE, "hf_moe_mask.npz"), **d)
+        print("hf_moe_mask.npz", os.path.getsize(os.path.join(HERE, "hf_moe_mask.npz")) // 1024, "KiB")
+        return
     if sys.argv[1:] == ["llama4_model"]:
         d = {}
         hf_llama4_model_fixture(d)

@@ -179,3 +179,28 @@ def test_add_tokens_check_finished_matches_generation_loop_semantics():
     assert u.tolist() == [0, 0, 0]
     out, u = oracle.add_tokens_check_finished(ids, nxt, unf, False, 0, torch.tensor([2]), False, -1)
     assert out[:, -1].tolist() == [11, 2, 99] and u.tolist() == [1, 1, 0]
+
+
+@pytest.fixture(scope="module")
+def moe_mask():
+    return np.load(os.path.join(GOLD, "hf_moe_mask.npz"))
+
+
+def test_moe_mlp_matches_hf_llama4_moe_block(moe_mask):
+    """Router (plain linear), top-k + sigmoid, routed experts on score-scaled inputs, shared expert: HF
+    `Llama4TextMoe` (the module tests/test_gateupdownmlpmoe.py of the reference compares with), fp32."""
+    m = moe_mask
+    x, k = T(m["moe_x"]), int(m["moe_top_k"])
+    logits = oracle.linear(x.reshape(1, -1), T(m["moe_router_w"]))
+    np.testing.assert_allclose(logits.numpy(), m["moe_router_logits"], rtol=1e-5, atol=1e-6)
+    scores, idx = oracle.topk_sigmoid(logits, k)
+    E = m["moe_router_w"].shape[0]
+    y = oracle.moe_mlp(x, T(m["moe_gate"]), T(m["moe_up"]), T(m["moe_down"]), 1, 1 + E, scores, idx)
+    np.testing.assert_allclose(y.numpy(), m["moe_y"], rtol=1e-5, atol=1e-6)
+
+
+def test_masked_decode_attention_matches_hf_eager_attention(moe_mask):
+    """One query token over a cache with masked-out rows: HF `eager_attention_forward` with an additive mask."""
+    m = moe_mask
+    o = oracle.decode_attention(T(m["mattn_q"]), T(m["mattn_k"]), T(m["mattn_v"]), mask=T(m["mattn_mask"]))
+    np.testing.assert_allclose(o.numpy(), m["mattn_out"], rtol=1e-5, atol=1e-6)
