@@ -828,7 +828,18 @@ mui_status_t mui_launch_gemv16(cudaStream_t stream, mui_dtype_t dtype, int mode,
                            (a.w8_fmt < 0 || a.w8_fmt == MUI_W8_SYM_ROW) &&
                            ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) &&
                            (a.norm_w == nullptr || (reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0);
-  if (a.B > 1 && a.moe_mode == GEMV_MOE_NONE && !pipeline_ok && (size_t)nb * (a.Kp + 8) * 2 > 150 * 1024) {
+  // per-group 8-bit format: its pipeline kernel stages whole rows; a batch that leaves it fewer than two weight stages
+  // runs as two half batches on that kernel (two passes at pipeline speed beat one pass of the plain-load kernel)
+  bool gm_split = false;
+  if (a.w8_fmt == MUI_W8_GROUP_MIN && a.B > 1 && a.moe_mode == GEMV_MOE_NONE && !a.use_comm &&
+      !(flags & MUI_FLAG_FORCE_GENERIC) && a.group_shift >= 5 && a.group_shift <= 11 && (a.K % 16) == 0 &&
+      ((reinterpret_cast<uintptr_t>(a.W) & 15) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0)) {
+    const int out_tile = (mode == 1 && a.w8_pack) ? 32 : 16;
+    const int fixed = gm_layout(0, nb, a.Kp, a.K >> a.group_shift, out_tile).total;
+    gm_split = (226 * 1024 - fixed) / GM_STAGE_BYTES < 2;
+  }
+  if (gm_split ||
+      (a.B > 1 && a.moe_mode == GEMV_MOE_NONE && !pipeline_ok && (size_t)nb * (a.Kp + 8) * 2 > 150 * 1024)) {
     const int h = a.B / 2;
     GemvArgs lo = a, hi = a;
     lo.trace = hi.trace = nullptr;

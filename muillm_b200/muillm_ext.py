@@ -173,7 +173,7 @@ def muillm_int8_gateupsilu_forward(norm_weights, epsilon, gate_up_weights, gate_
     if (rows <= 8 and 5 <= group_size_shift <= 11 and gate_up_weights.shape[1] % 16 == 0
             and gate_up_weights.is_contiguous() and gate_up_scales_min_vals.is_contiguous()
             and gate_up_weights.data_ptr() % 16 == 0 and gate_up_scales_min_vals.data_ptr() % 8 == 0
-            and _packed_gateup_fits(rows, gate_up_weights.shape[1], group_size_shift)):
+            and _packed_gateup_fits(1, gate_up_weights.shape[1], group_size_shift)):  # batches split themselves
         return ops.int8_gateup_silu_packed(x, gate_up_weights, gate_up_scales_min_vals, group_size_shift,
                                            norm_weights=norm_weights, epsilon=epsilon)
     gq, gs, uq, us = _split_gateup_pack(gate_up_weights, gate_up_scales_min_vals, group_size_shift)

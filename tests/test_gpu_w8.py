@@ -102,7 +102,9 @@ def _group_pack(gq, gsm, uq, usm):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("path", list(PATHS))
 @pytest.mark.parametrize("N,K,B,shift", [(4096, 4096, 1, 7), (515, 6144, 3, 7), (1024, 14336, 1, 7), (130, 1024, 8, 5),
-                                         (256, 8192, 2, 9), (64, 4096, 4, 11)])
+                                         (256, 8192, 2, 9), (64, 4096, 4, 11),
+                                         # batches whose whole-row staging leaves the pipeline no room: half batches
+                                         (256, 14336, 4, 7), (144, 14336, 8, 7)])
 def test_linear_group_min_both_kernels(dtype, path, N, K, B, shift):
     g = _gen(N + K + shift + B)
     W = (torch.randn(N, K, generator=g) * 0.02 + 0.003).to(dtype)
@@ -118,7 +120,8 @@ def test_linear_group_min_both_kernels(dtype, path, N, K, B, shift):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("I,H,B,shift", [(14336, 4096, 1, 7), (1000, 4096, 4, 7), (72, 3072, 2, 5), (520, 2048, 8, 6)])
+@pytest.mark.parametrize("I,H,B,shift", [(14336, 4096, 1, 7), (1000, 4096, 4, 7), (72, 3072, 2, 5), (520, 2048, 8, 6),
+                                         (264, 8192, 8, 7)])
 def test_gateup_group_min_split_and_packed(dtype, I, H, B, shift):
     g = _gen(I + H + B)
     mk = lambda *s: (torch.randn(*s, generator=g) * 0.02 + 0.002).to(dtype)
