@@ -1,0 +1,9 @@
+// fp16 instantiation of the GEMV kernels (gemv_kernels.cuh)
+#include "gemv_kernels.cuh"
+
+MUI_STATUS_ACCESSOR(gemv_f16)
+
+mui_status_t mui_launch_gemv_f16(cudaStream_t stream, int mode, const GemvArgs& a, int nb, unsigned flags,
+                                 const MuiDeviceInfo* dev) {
+  return launch_gemv_dt<__half>(stream, mode, a, nb, flags, dev);
+}

@@ -1,6 +1,6 @@
 // Bulk-copy pipeline GEMV on the reference's per-group 8-bit format: w = q * scale_g + min_g, q in 0..255, one
 // {scale, min} 16-bit pair per `group` consecutive weights of a row (muillm/quantization/rtnquantizer.py:48-88;
-// kernels csrc/int8_linear_kernels.cu:212-226, csrc/int8_gateup_kernels.cu:255,522). Included by gemv.cu.
+// kernels csrc/int8_linear_kernels.cu:212-226, csrc/int8_gateup_kernels.cu:255,522). Included by gemv_kernels.cuh.
 //
 // Inside one group  sum_k w x = scale * sum_k q x + min * sum_k x:  the first sum runs on the tensor cores with q
 // widened to 16 bits (exactly), the second is a per-group sum of the staged activations computed once per CTA.

@@ -9,7 +9,7 @@
 // read exactly once, in row chunks of 4 KiB (16-bit) or 2 KiB (8-bit), through the same mbarrier ring. The next
 // chunk of activations is loaded into registers while the current one is being multiplied, normalised (fused RMSNorm
 // with the HF roundings, from per-row rstd values computed up front) when it is stored to shared memory.
-// Included by gemv.cu inside its unnamed namespace.
+// Included by gemv_kernels.cuh inside its unnamed namespace.
 #pragma once
 
 constexpr int XC_KC = 2048;        // activation chunk (elements) = weights per row chunk

@@ -1,4 +1,4 @@
-// Weight-only 8-bit entry points: linear and gate/up+SiLU on quantised weights (kernels in gemv.cu), and the
+// Weight-only 8-bit entry points: linear and gate/up+SiLU on quantised weights (kernels in gemv_kernels.cuh), and the
 // full de-quantisation used by batched fallbacks.
 #include "gemv_common.cuh"
 
