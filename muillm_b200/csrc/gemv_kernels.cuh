@@ -235,11 +235,14 @@ __host__ __device__ inline PipeLayout pipe_layout(int stage_bytes, int stages, i
 
 #include "gemv_xchunk.cuh"
 
-// AE = 1 (8-bit weights): asynchronous epilogue. The tile loop on 8-bit weights is bound by the mma.sync issue rate
+// AE = 1 (8-bit weights, and 16-bit linear layers with the fused all-reduce): asynchronous epilogue. The tile loop on 8-bit weights is bound by the mma.sync issue rate
 // (one m16n8k16 occupies a sub-partition's tensor pipe for ~34 cycles on this part, and 8-bit weights need as many of
 // them per output as 16-bit ones for half the bytes), so every cycle the eight math warps spend at a row block's
 // barrier, in its cross-warp sum or in its epilogue is lost. With AE an extra warp owns the cross-warp sum and the
 // epilogue: the math warps drop their partial tiles into a double-buffered slot, arrive on an mbarrier and go on.
+// With the fused all-reduce the epilogue is where a row block's partial sums are pushed to the peers (eight 64-bit
+// system-scope stores per element): on the extra warp those stores no longer hold up warp 0's share of the next
+// tiles, and with it every row block's barrier.
 template <typename T, int NB, int MODE, int KC, int WB, int NPROD, int AE>
 __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * (NPROD + AE)) gemv_pipe_kernel(const GemvArgs a,
                                                                                              const int num_stages) {
@@ -362,6 +365,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * (NPROD + AE)) gem
     // per row block: the eight warps' partial tiles are summed in a fixed order, then the epilogue; the operands of
     // the epilogue (per-row scales, residual) are fetched before the wait for the tiles
     pdl_wait_prior_grid();
+    const unsigned long long eseq = (MODE == 0 && a.use_comm) ? comm_begin(a.comm) : 0ull;
     constexpr int OUTS = ROWS_PER_STAGE * NB;       // outputs per row block
     constexpr int PER_LANE = (OUTS + 31) / 32;
     const bool sym = (WB == 8) && a.w8_fmt == MUI_W8_SYM_ROW && a.moe_mode == GEMV_MOE_NONE;
@@ -400,7 +404,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * (NPROD + AE)) gem
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < MW; ++w) v += rbuf[(w * PIPE_ROWS + r) * NB + b];
-            gemv_store_linear<T>(a, b, row, v, 0ull, true, pb[i], pa[i]);
+            gemv_store_linear<T>(a, b, row, v, eseq, true, pb[i], pa[i]);
           } else {
             float g = 0.f, u = 0.f;
 #pragma unroll
@@ -606,7 +610,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * (NPROD + AE)) gem
     if (MODE == 0 && a.use_comm)
       gemv_comm_tail<T>(a, comm_seq, tid, GEMV_CONSUMER_THREADS, 1, r_end - r_begin,
                         [r_begin](int i) { return r_begin + i; });
-    if (!AE && tid == 0) trace_end(a.trace);
+    if (tid == 0) trace_end(a.trace);  // (the latest stamp of the launch is kept)
   }
 }
 
@@ -615,13 +619,10 @@ __global__ void __launch_bounds__(GEMV_CONSUMER_THREADS + 32 * (NPROD + AE)) gem
 // =============================================================================================
 // host dispatch
 // =============================================================================================
-template <typename T, int NB, int MODE, int KC, int WB>
-mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int total_rows, int x_rows,
-                         const MuiDeviceInfo* dev, bool* applicable) {
+template <typename T, int NB, int MODE, int KC, int WB, int AE>
+mui_status_t launch_pipe_ae(cudaStream_t stream, const GemvArgs& a, int pdl, int total_rows, int x_rows,
+                            const MuiDeviceInfo* dev, bool* applicable) {
   using G = PipeGeom<KC, WB>;
-  // 8-bit weights: asynchronous epilogue warp (never combined with the fused all-reduce, whose tail runs on the
-  // consumer threads after their own pushes)
-  constexpr int AE = (WB == 8) ? 1 : 0;
   // One CTA per SM with (nearly) all of its shared memory: ~190 KiB of copies in flight per SM is what keeps
   // HBM busy; with half of that the kernel runs ~25 % slower.
   // 226 KiB: with K = 14336 the staged activations (28 KiB) and three 64.25 KiB stages need 222.8 KiB
@@ -639,7 +640,7 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   const int sms = std::max(1, dev->sm_count - std::min(a.reserve_sms, dev->sm_count / 4));
   const int grid = std::max(1, std::min(units, sms));
   // one producer warp: a second one doubles the issue rate of 4 KiB copies but measured no faster end to end
-  if (AE && a.use_comm) {
+  if (WB == 8 && a.use_comm) {
     mui_set_error("8-bit weights with the fused all-reduce are not supported");
     return MUI_ERR_UNSUPPORTED;
   }
@@ -654,6 +655,21 @@ mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int to
   MUI_CUDA_CHECK(mui_launch(kern, dim3(grid), dim3(GEMV_CONSUMER_THREADS + 32 * (1 + AE)), (size_t)lay.total, stream, pdl, a,
                             stages));
   return MUI_OK;
+}
+
+// Asynchronous epilogue warp: always for 8-bit weights; for 16-bit weights where the epilogue pushes to the peers.
+template <typename T, int NB, int MODE, int KC, int WB>
+mui_status_t launch_pipe(cudaStream_t stream, const GemvArgs& a, int pdl, int total_rows, int x_rows,
+                         const MuiDeviceInfo* dev, bool* applicable) {
+  if constexpr (WB == 8) {
+    return launch_pipe_ae<T, NB, MODE, KC, WB, 1>(stream, a, pdl, total_rows, x_rows, dev, applicable);
+  } else {
+    if constexpr (MODE == 0) {
+      if (a.use_comm)
+        return launch_pipe_ae<T, NB, MODE, KC, WB, 1>(stream, a, pdl, total_rows, x_rows, dev, applicable);
+    }
+    return launch_pipe_ae<T, NB, MODE, KC, WB, 0>(stream, a, pdl, total_rows, x_rows, dev, applicable);
+  }
 }
 
 // Per-group 8-bit format on the bulk-copy pipeline (gemv_w8g.cuh); *applicable = false when the activations leave no
