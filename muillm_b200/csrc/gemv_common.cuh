@@ -214,28 +214,42 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, int rows_present
   }
 
   if (vec_ok) {
-    for (int k = tid * 8; k < Kp; k += GEMV_CONSUMER_THREADS * 8) {
-      float wv[8];
-      if (nw != nullptr) unpack8<T>(ld_cached16(nw + k), wv);
+    // UNR slices per thread are loaded back to back before any is stored: one L2 round trip per UNR slices instead
+    // of one per slice (a row of 14336 elements is seven slices per thread)
+    constexpr int UNR = (NBX == 1) ? 8 : (NBX == 2 ? 4 : (NBX <= 4 ? 2 : 1));
+    constexpr int STEP = GEMV_CONSUMER_THREADS * 8;
+    for (int k0 = tid * 8; k0 < Kp; k0 += STEP * UNR) {
+      uint4 raw[UNR][NBX], wraw[UNR];
 #pragma unroll
-      for (int b = 0; b < NBX; ++b) {
-        uint4 out = make_uint4(0, 0, 0, 0);
-        if (b < rows_present) {
-          uint4 raw = ld_act16(x + (size_t)b * K + k);
-          if (nw != nullptr) {
+      for (int u = 0; u < UNR; ++u) {
+        const int k = k0 + u * STEP;
+        wraw[u] = make_uint4(0, 0, 0, 0);
+        if (k < Kp && nw != nullptr) wraw[u] = ld_cached16(nw + k);
+#pragma unroll
+        for (int b = 0; b < NBX; ++b)
+          raw[u][b] = (k < Kp && b < rows_present) ? ld_act16(x + (size_t)b * K + k) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int k = k0 + u * STEP;
+        if (k >= Kp) break;
+        float wv[8];
+        if (nw != nullptr) unpack8<T>(wraw[u], wv);
+#pragma unroll
+        for (int b = 0; b < NBX; ++b) {
+          uint4 out = raw[u][b];  // zero for the rows past rows_present
+          if (b < rows_present && nw != nullptr) {
             float f[8];
-            unpack8<T>(raw, f);
+            unpack8<T>(raw[u][b], f);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               float n1 = Elt<T>::to_f32(Elt<T>::from_f32(f[i] * rstd[b]));
               f[i] = n1 * wv[i];
             }
             out = pack8<T>(f);
-          } else {
-            out = raw;
           }
+          *reinterpret_cast<uint4*>(x_s + (size_t)b * pitch + k) = out;
         }
-        *reinterpret_cast<uint4*>(x_s + (size_t)b * pitch + k) = out;
       }
     }
   } else {
@@ -267,9 +281,18 @@ __device__ __forceinline__ void gemv_stage_x_plain(const GemvArgs& a, int rows, 
   const T* __restrict__ x = reinterpret_cast<const T*>(a.x);
   const bool vec_ok = ((K & 7) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
   if (vec_ok) {
+    constexpr int UNR = 4;  // loads of four slices in flight before the first store
+    constexpr int STEP = GEMV_CONSUMER_THREADS * 8;
     for (int r = 0; r < rows; ++r)
-      for (int k = tid * 8; k < K; k += GEMV_CONSUMER_THREADS * 8)
-        *reinterpret_cast<uint4*>(x_s + (size_t)r * pitch + k) = ld_act16(x + (size_t)r * K + k);
+      for (int k0 = tid * 8; k0 < K; k0 += STEP * UNR) {
+        uint4 raw[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u)
+          raw[u] = (k0 + u * STEP < K) ? ld_act16(x + (size_t)r * K + k0 + u * STEP) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < UNR; ++u)
+          if (k0 + u * STEP < K) *reinterpret_cast<uint4*>(x_s + (size_t)r * pitch + k0 + u * STEP) = raw[u];
+      }
   } else {
     for (int r = 0; r < rows; ++r)
       for (int k = tid; k < Kp; k += GEMV_CONSUMER_THREADS)
