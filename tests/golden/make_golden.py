@@ -330,7 +330,39 @@ def hf_moe_and_masked_attention_fixture(out):
     out["mattn_out"] = o.reshape(B, 1, Hq * D).numpy()
 
 
+def reference_pack_fixture(out):
+    """The reference's own packing of per-group 8-bit gate / up weights (muillm/modules/quantized/
+    int8gateupdownmlp.py:211-230), run on quantised tensors made by its RTNQuantizer."""
+    from types import SimpleNamespace
+
+    sys.modules["muillm_ext"] = _Stub("muillm_ext")
+    sys.path.insert(0, REF)
+    from muillm.modules.quantized.int8gateupdownmlp import MuiInt8GateUpDownMLP
+    from muillm.quantization.rtnquantizer import RTNQuantizer
+
+    g = torch.Generator().manual_seed(5)
+    q = RTNQuantizer(n_bit=8, groupsize=128)
+    gw = (torch.randn(12, 256, generator=g) * 0.02).to(torch.float16)
+    uw = (torch.randn(12, 256, generator=g) * 0.02).to(torch.float16)
+    gq, gsm = q.group_quantize_tensor(gw)
+    uq, usm = q.group_quantize_tensor(uw)
+    me = SimpleNamespace()
+    me._pack_gateup_weights = lambda a, b: MuiInt8GateUpDownMLP._pack_gateup_weights(me, a, b)
+    pack, sm = MuiInt8GateUpDownMLP._pack_gateup_linears(
+        me, SimpleNamespace(weights_uint8=gq, scales_min_vals=gsm), SimpleNamespace(weights_uint8=uq, scales_min_vals=usm))
+    out["gate_q"], out["up_q"] = gq.numpy(), uq.numpy()
+    out["gate_scales_min"], out["up_scales_min"] = gsm.float().numpy(), usm.float().numpy()
+    out["pack"], out["pack_scales_min"] = pack.numpy(), sm.float().numpy()
+
+
 def main():
+    if sys.argv[1:] == ["pack"]:
+        d = {}
+        reference_pack_fixture(d)
+        np.savez_compressed(os.path.join(HERE, "reference_pack.npz"), **d)
+        print("reference_pack.npz", os.path.getsize(os.path.join(HERE, "reference_pack.npz")) // 1024, "KiB", d["pack"].shape,
+              d["pack_scales_min"].shape)
+        return
     if sys.argv[1:] == ["moe_mask"]:
         d = {}
         hf_moe_and_masked_attention_fixture(d)

@@ -40,3 +40,15 @@ def check_greedy_tokens(stack, w_cpu, cfg, prompt, want, max_T, use_graph, near_
                                             f"margin {margin} is no near-tie; free run equal for {same} tokens")
             flips.append(i)
     return same
+
+
+def reference_gateup_pack(gate_q, gate_scales_min, up_q, up_scales_min):
+    """Separate per-group 8-bit gate / up tensors -> the reference's pack: bytes [I, H, 2] (gate, up interleaved
+    element by element) and {scale, min} pairs [I * G, 2, 2] (gate pair, up pair), the layout built by
+    muillm/modules/quantized/int8gateupdownmlp.py:211-230 (`_pack_gateup_weights`, `_pack_gateup_linears`)."""
+    import torch
+
+    pack = torch.stack([gate_q, up_q], dim=-1).contiguous()
+    sm = torch.stack([gate_scales_min.reshape(-1, 2), up_scales_min.reshape(-1, 2)], dim=1).contiguous()
+    return pack, sm
+

@@ -91,12 +91,7 @@ def test_quantised_weights_reach_the_kernel_bit_exact():
 # the reference's per-group {scale, min} format on the bulk-copy pipeline (groups of >= 32, K % 32 == 0) and on the
 # plain-load kernel, and its element-interleaved gate/up pack
 # ---------------------------------------------------------------------------------------------------------------
-def _group_pack(gq, gsm, uq, usm):
-    """gate/up -> the reference's pack: [I, H, 2] bytes and [I * G, 2, 2] {scale, min} pairs
-    (muillm/modules/quantized/int8gateupdownmlp.py:211-230)."""
-    pack = torch.stack([gq, uq], dim=-1).contiguous()
-    sm = torch.stack([gsm.reshape(-1, 2), usm.reshape(-1, 2)], dim=1).contiguous()
-    return pack, sm
+from parity_utils import reference_gateup_pack as _group_pack  # noqa: E402  (the reference's own pack layout)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

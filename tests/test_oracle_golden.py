@@ -204,3 +204,21 @@ def test_masked_decode_attention_matches_hf_eager_attention(moe_mask):
     m = moe_mask
     o = oracle.decode_attention(T(m["mattn_q"]), T(m["mattn_k"]), T(m["mattn_v"]), mask=T(m["mattn_mask"]))
     np.testing.assert_allclose(o.numpy(), m["mattn_out"], rtol=1e-5, atol=1e-6)
+
+
+def test_packed_gateup_layout_matches_the_references_packing_code():
+    """`parity_utils.reference_gateup_pack` (what the GPU tests and benchmarks feed to the packed 8-bit gate/up kernel)
+    reproduces the tensors the reference's own packing code built from RTNQuantizer outputs (fixture
+    reference_pack.npz: muillm/modules/quantized/int8gateupdownmlp.py:211-230)."""
+    from parity_utils import reference_gateup_pack
+
+    m = np.load(os.path.join(GOLD, "reference_pack.npz"))
+    pack, sm = reference_gateup_pack(T(m["gate_q"]), T(m["gate_scales_min"]), T(m["up_q"]), T(m["up_scales_min"]))
+    assert np.array_equal(pack.numpy(), m["pack"]) and np.array_equal(sm.numpy(), m["pack_scales_min"])
+    assert tuple(pack.shape) == (12, 256, 2) and tuple(sm.shape) == (24, 2, 2)
+    # and the oracle's quantiser made the same bytes the reference's RTNQuantizer did, so packing oracle outputs
+    # gives the reference's pack
+    g = torch.Generator().manual_seed(5)
+    gw = (torch.randn(12, 256, generator=g) * 0.02).to(torch.float16)
+    gq, gsm = oracle.rtn_group_quantize(gw, group_shift=7)
+    assert np.array_equal(gq.numpy(), m["gate_q"]) and np.array_equal(gsm.float().numpy(), m["gate_scales_min"])

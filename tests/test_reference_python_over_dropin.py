@@ -63,3 +63,29 @@ def test_reference_linear_module_life_cycle_on_cpu(ref_modules, monkeypatch):
         lin(torch.randn(2, 3, 32))
     lin.finalize_deinit()
     assert handle.weights is None
+
+
+def test_packed_gateup_layout_is_the_references(ref_modules):
+    """The pack layout the GPU tests and benchmarks feed to `mui_gateup_silu_w8_packed_forward` is the one the
+    reference's own packing code produces (muillm/modules/quantized/int8gateupdownmlp.py:211-230)."""
+    from muillm.modules.quantized.int8gateupdownmlp import MuiInt8GateUpDownMLP
+    from types import SimpleNamespace
+
+    from parity_utils import reference_gateup_pack
+
+    g = torch.Generator().manual_seed(0)
+    I, H, G = 6, 256, 2
+    gq = torch.randint(0, 256, (I, H), generator=g, dtype=torch.uint8)
+    uq = torch.randint(0, 256, (I, H), generator=g, dtype=torch.uint8)
+    gsm = torch.randn(I * G, 2, generator=g).to(torch.float16)
+    usm = torch.randn(I * G, 2, generator=g).to(torch.float16)
+    gate = SimpleNamespace(weights_uint8=gq, scales_min_vals=gsm)
+    up = SimpleNamespace(weights_uint8=uq, scales_min_vals=usm)
+    # the two packing methods use no module state: run them on a stand-in instead of building a whole MLP module
+    me = SimpleNamespace()
+    me._pack_gateup_weights = lambda g_, u_: MuiInt8GateUpDownMLP._pack_gateup_weights(me, g_, u_)
+    ref_pack, ref_sm = MuiInt8GateUpDownMLP._pack_gateup_linears(me, gate, up)
+    pack, sm = reference_gateup_pack(gq, gsm, uq, usm)
+    assert torch.equal(pack, ref_pack) and torch.equal(sm, ref_sm)
+    assert ref_pack.is_contiguous() and ref_sm.is_contiguous()
+
