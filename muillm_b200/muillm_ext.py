@@ -894,10 +894,15 @@ class _FusedLayers:
         return out
 
 
+# the decoder-stack handle runs a decode step as one call into the C decode stack where the modules allow it
+FUSED_DECODER_STACK = True
+
+
 class muillm_parallel_decoder_stack_ptr(_Handle):
     """csrc/modules/parallel_decoder_stack.cpp:22-45: embedding (unless embeddings are given), the rotary tables
     once, then the decoders in order. One new token per sequence on a static cache without a mask — the decode step —
-    runs as a single call into the C decode stack (set MUILLM_B200_FUSED_STACK=0 to keep the per-module path)."""
+    runs as a single call into the C decode stack (module attribute FUSED_DECODER_STACK = False keeps the per-module
+    path, which the tests use as a cross-check)."""
 
     def __init__(self, comm, embed_tokens, rotary_embedding, decoders):
         self.comm, self.embed_tokens, self.rotary_embedding, self.decoders = (comm, embed_tokens, rotary_embedding,
@@ -905,7 +910,7 @@ class muillm_parallel_decoder_stack_ptr(_Handle):
         self._fused = None
 
     def _fused_for(self, cache, batch, q_len, m):
-        if os.environ.get("MUILLM_B200_FUSED_STACK", "1") == "0":
+        if not FUSED_DECODER_STACK:
             return None
         if q_len != 1 or m is not None or batch > 8 or cache is None or self.embed_tokens is None or \
                 self.rotary_embedding is None or cache.kind != muillm_kvcache_module_ptr.STATIC:

@@ -48,7 +48,7 @@ CFG128 = dict(layers=2, hidden=512, intermediate=768, heads=8, kv_heads=2, head_
                                                   ("static", "1", CFG128), ("static", "0", CFG128)])
 def test_decoder_stack_through_module_handles(dtype, cache_kind, fused, cfg, monkeypatch):
     """fused = 1: a decode step on a static cache is one call into the C decode stack; 0: one call per module."""
-    monkeypatch.setenv("MUILLM_B200_FUSED_STACK", fused)
+    monkeypatch.setattr(ext, "FUSED_DECODER_STACK", fused == "1")
     max_T, B = 48, 2
     w = oracle.make_llama_weights(cfg, dtype, seed=3, std=0.06)
     engine = ext.muillm_engine_init()
