@@ -7,7 +7,7 @@ csrc/linear/linear.cu:72-74).
 """
 import ctypes
 import os
-from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_longlong, c_size_t, c_uint,
+from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int64, c_longlong, c_size_t, c_uint,
                     c_void_p)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))

@@ -6,7 +6,7 @@ over a UNIX socket, and the fused sharded layers (`parallel_linear`, `parallel_m
 """
 import ctypes
 import os
-from ctypes import c_int, c_size_t, c_void_p
+from ctypes import c_size_t, c_void_p
 
 import torch
 

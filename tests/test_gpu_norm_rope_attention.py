@@ -1,5 +1,4 @@
 """GPU parity of RMSNorm, RoPE + static-cache write-out and flash decoding against the CPU oracle."""
-import math
 
 import pytest
 import torch
