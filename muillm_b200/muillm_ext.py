@@ -48,8 +48,15 @@ def _rows(x):
     return x.numel() // x.shape[-1] if x.numel() else 0
 
 
+# rows > 8 (prefill): this library's tcgen05 GEMM with the epilogue fused; False hands them to torch's GEMM, as the
+# reference does (torch's is the faster of the two at present, see the per-kernel benchmark)
+PREFILL_TENSOR_CORE_KERNEL = True
+
+
 def _tensor_core_prefill_ok(x, *weights):
     """The tcgen05 prefill GEMM takes 16-bit contiguous operands with rows that are multiples of 16 bytes."""
+    if not PREFILL_TENSOR_CORE_KERNEL:
+        return False
     if x.dtype not in (torch.float16, torch.bfloat16) or x.shape[-1] % 8 or not x.is_contiguous():
         return False
     return all(w.is_contiguous() and w.dtype == x.dtype and w.data_ptr() % 16 == 0 for w in weights) and \
